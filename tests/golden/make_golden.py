@@ -1,0 +1,226 @@
+"""Generate the golden fixtures in this directory from the UNMODIFIED reference.
+
+Run where the reference checkout is available:
+
+    python tests/golden/make_golden.py [--reference /root/reference] [--config1]
+
+The reference is imported as it lies (nothing is copied); two modules it
+imports but never uses (`exceptiongroup`, `pyparsing`) are stubbed, and
+`torch.cuda.synchronize` is made a no-op on a CUDA-less host.  Captures are
+taken by wrapping functions from the outside:
+  * bigptq.structural_guassian_distribution -> per block (W_blk, diag U_blk, masks)
+  * utils.autosearch.error_computing        -> the 49 + 81 candidate errors per block
+All inputs come from seeded CPU generators defined in this file, so the
+fixtures can be regenerated bit-for-bit.
+
+Outputs (numpy .npz, float32 unless noted):
+  blocks.npz    single-block cases: metric search + the three binarizers
+  linear.npz    a 96x256 linear: Hessian from 6 add_batch calls, fasterquant x 3 techniques
+  config1.npz   (only with --config1) the 2048x2048 / 262144-token case, compact outputs
+"""
+from __future__ import annotations
+
+import argparse
+import contextlib
+import io
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def load_reference(path):
+    for name, attr in (("exceptiongroup", "catch"), ("pyparsing", "line")):
+        if name not in sys.modules:
+            mod = types.ModuleType(name)
+            setattr(mod, attr, None)
+            sys.modules[name] = mod
+    if not torch.cuda.is_available():
+        torch.cuda.synchronize = lambda *a, **k: None
+    if path not in sys.path:
+        sys.path.insert(0, path)
+    import bigptq
+    import binary
+    import utils.autosearch as autosearch
+    return bigptq, binary, autosearch
+
+
+# ---------------------------------------------------------------- seeded inputs
+def make_block(R, seed, scale=0.02, hot_cols=3):
+    g = torch.Generator().manual_seed(seed)
+    W = torch.randn(R, 128, generator=g) * scale
+    d = 0.5 + torch.rand(128, generator=g)
+    hot = torch.randperm(128, generator=g)[:hot_cols]
+    d[hot] *= 0.2                      # small diag(U) -> large metric -> salient columns
+    return W, d
+
+
+def make_linear(R, C, T, seed, outlier_frac=0.01):
+    g = torch.Generator().manual_seed(seed)
+    W = torch.randn(R, C, generator=g) * 0.02
+    X = torch.randn(T, C, generator=g)
+    n_out = max(1, int(round(C * outlier_frac)))
+    ch = torch.randperm(C, generator=g)[:n_out]
+    X[:, ch] *= 20
+    return W, X
+
+
+class Capture:
+    """Records per-block inputs, masks and candidate errors of one fasterquant run."""
+
+    def __init__(self, bigptq, autosearch):
+        self.bigptq, self.autosearch = bigptq, autosearch
+        self.blocks = []
+        self._errs = []
+
+    def __enter__(self):
+        self._sgd = self.bigptq.structural_guassian_distribution
+        self._ec = self.autosearch.error_computing
+
+        def ec(a, b):
+            e = self._ec(a, b)
+            self._errs.append(float(e))
+            return e
+
+        def sgd(tmp, H=None, metric="magnitude", up_lim=30, orders=(1, 1, 2)):
+            self._errs = []
+            with contextlib.redirect_stdout(io.StringIO()):
+                m1, m2, m3 = self._sgd(tmp, H, metric, up_lim, orders=orders)
+            self.blocks.append(dict(W=tmp.clone(), d=torch.diag(H).clone(), m1=m1.clone(),
+                                    m2=m2.clone(), m3=m3.clone(), errs=list(self._errs)))
+            return m1, m2, m3
+
+        self.autosearch.error_computing = ec
+        self.bigptq.structural_guassian_distribution = sgd
+        return self
+
+    def __exit__(self, *exc):
+        self.autosearch.error_computing = self._ec
+        self.bigptq.structural_guassian_distribution = self._sgd
+
+
+def pack(mask):
+    return np.packbits(mask.numpy().astype(np.uint8), axis=None)
+
+
+def gen_blocks(bigptq, binary, autosearch, out):
+    cases = [(64, 11, 0.02, 3), (256, 12, 0.02, 5), (200, 13, 0.05, 0), (33, 14, 0.02, 20)]
+    data = {"n_cases": np.int64(len(cases))}
+    for ci, (R, seed, scale, hot) in enumerate(cases):
+        W, d = make_block(R, seed, scale, hot)
+        Hblk = torch.diag(d)
+        with Capture(bigptq, autosearch) as cap:
+            m1, m2, m3 = bigptq.structural_guassian_distribution(W, Hblk, "hessian", 50)
+        blk = cap.blocks[0]
+        data[f"c{ci}_W"] = W.numpy()
+        data[f"c{ci}_d"] = d.numpy()
+        data[f"c{ci}_errs"] = np.asarray(blk["errs"], dtype=np.float64)
+        for name, m in (("m1", m1), ("m2", m2), ("m3", m3)):
+            data[f"c{ci}_{name}"] = pack(m)
+        for tech in ("braq", "crbog", "crb"):
+            qz = binary.Binarization(W, method=tech, groupsize=128, corr_damp=0.1, lam=1e-5)
+            Q = torch.zeros_like(W)
+            for g, (m, order) in enumerate(zip((m1, m2, m3), (1, 1, 2))):
+                qg = qz.quantize(W, m, order=order)
+                data[f"c{ci}_{tech}_q{g}"] = qg.numpy()
+                Q += qg * m
+            data[f"c{ci}_{tech}_Q"] = Q.numpy()
+    np.savez_compressed(out, **data)
+    print("wrote", out)
+
+
+def run_reference_linear(bigptq, binary, autosearch, W, H, nsamples, tech):
+    R, C = W.shape
+    lin = nn.Linear(C, R, bias=False)
+    lin.weight.data = W.clone()
+    qz = binary.Binarization(lin.weight, method=tech, groupsize=128, corr_damp=0.1, lam=1e-5)
+    g = bigptq.BRAGPTQ(lin, qz, salient_metric="hessian")
+    g.H = H.clone()
+    g.nsamples = nsamples
+    with Capture(bigptq, autosearch) as cap, contextlib.redirect_stdout(io.StringIO()):
+        info = g.fasterquant(blocksize=128, percdamp=0.01, partition=3)
+    return lin.weight.data.clone(), info["error"], cap.blocks
+
+
+def gen_linear(bigptq, binary, autosearch, out):
+    R, C, T, nseq = 96, 256, 768, 6
+    W, X = make_linear(R, C, T, seed=21, outlier_frac=0.02)
+    lin = nn.Linear(C, R, bias=False)
+    lin.weight.data = W.clone()
+    g = bigptq.BRAGPTQ(lin, binary.Binarization(lin.weight, method="braq", groupsize=128), "hessian")
+    for j in range(nseq):
+        g.add_batch(X[j * (T // nseq):(j + 1) * (T // nseq)].unsqueeze(0), None)
+    H = g.H.clone()
+    data = dict(W=W.numpy(), X=X.numpy(), H=H.numpy(), nseq=np.int64(nseq))
+    for tech in ("braq", "crbog", "crb"):
+        Wq, err, blocks = run_reference_linear(bigptq, binary, autosearch, W, H, nseq, tech)
+        data[f"{tech}_Wq"] = Wq.numpy()
+        data[f"{tech}_error"] = np.float64(err)
+        for bi, blk in enumerate(blocks):
+            data[f"{tech}_b{bi}_Win"] = blk["W"].numpy()
+            data[f"{tech}_b{bi}_d"] = blk["d"].numpy()
+            data[f"{tech}_b{bi}_errs"] = np.asarray(blk["errs"], dtype=np.float64)
+            for name in ("m1", "m2", "m3"):
+                data[f"{tech}_b{bi}_{name}"] = pack(blk[name])
+    np.savez_compressed(out, **data)
+    print("wrote", out)
+
+
+def gen_config1(bigptq, binary, autosearch, out, keep_blocks=(0, 9)):
+    """BASELINE config 1: W 2048x2048 N(0,0.02^2); X 128x2048x2048 N(0,1), 1% channels x20; crb."""
+    R = C = 2048
+    nseq, seqlen = 128, 2048
+    g = torch.Generator().manual_seed(1)
+    W = torch.randn(R, C, generator=g) * 0.02
+    ch = torch.randperm(C, generator=g)[: C // 100]
+    lin = nn.Linear(C, R, bias=False)
+    lin.weight.data = W.clone()
+    gp = bigptq.BRAGPTQ(lin, binary.Binarization(lin.weight, method="crb", groupsize=128), "hessian")
+    G = torch.zeros(C, C, dtype=torch.float64)
+    for j in range(nseq):
+        gx = torch.Generator().manual_seed(1000 + j)
+        x = torch.randn(seqlen, C, generator=gx)
+        x[:, ch] *= 20
+        gp.add_batch(x.unsqueeze(0), None)
+        G += (x.t() @ x).double()
+    H = gp.H.clone()
+    Wq, err, blocks = run_reference_linear(bigptq, binary, autosearch, W, H, nseq, "crb")
+    D = (W - Wq).double()
+    out_err = float(torch.sqrt(torch.clamp((D @ G * D).sum(), min=0)))
+    data = dict(error=np.float64(err), out_err=np.float64(out_err),
+                Wq_rows=Wq[:32].numpy(), channels=ch.numpy(),
+                H_diag=torch.diag(H).numpy(), H_row0=H[0].numpy(),
+                Wq_colnorm=torch.linalg.norm(Wq.double(), dim=0).numpy())
+    for bi, blk in enumerate(blocks):
+        data[f"b{bi}_errs"] = np.asarray(blk["errs"], dtype=np.float64)
+        data[f"b{bi}_m3cols"] = blk["m3"][0].nonzero().flatten().numpy()
+        data[f"b{bi}_frac"] = np.asarray([blk[n].float().mean().item() for n in ("m1", "m2", "m3")])
+        if bi in keep_blocks:
+            data[f"b{bi}_Win"] = blk["W"].numpy()
+            data[f"b{bi}_d"] = blk["d"].numpy()
+            data[f"b{bi}_m1"] = pack(blk["m1"])
+            data[f"b{bi}_Qout"] = Wq[:, bi * 128:(bi + 1) * 128].numpy()
+    np.savez_compressed(out, **data)
+    print("wrote", out, "error", err, "out_err", out_err)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--config1", action="store_true")
+    args = ap.parse_args()
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    mods = load_reference(args.reference)
+    gen_blocks(*mods, os.path.join(HERE, "blocks.npz"))
+    gen_linear(*mods, os.path.join(HERE, "linear.npz"))
+    if args.config1:
+        gen_config1(*mods, os.path.join(HERE, "config1.npz"))
+
+
+if __name__ == "__main__":
+    main()
