@@ -1,0 +1,162 @@
+"""`BRAGPTQ`: drop-in for the reference class of the same name (bigptq.py:18-298).
+
+Same constructor, attributes and methods; the arithmetic runs in the sm_100a
+kernels of libcrb_b200.so:
+
+    add_batch    -> tcgen05 Hessian accumulation      (bigptq.py:37-54)
+    fasterquant  -> device factorisation + block loop  (bigptq.py:56-291)
+
+Only the path of the techniques braq / crbog / crb is implemented (partition=3,
+orders=(1,1,2), blocksize 128, Hessian salience metric); anything else raises
+NotImplementedError instead of silently taking another route.
+"""
+from __future__ import annotations
+
+import time
+
+import torch
+import torch.nn as nn
+
+from . import ops
+from ._lib import BLOCK, FLAG_NONFINITE, CrbError
+
+try:  # transformers.Conv1D weights are stored transposed (bigptq.py:28-29)
+    import transformers
+    _Conv1D = transformers.Conv1D
+except Exception:  # pragma: no cover
+    _Conv1D = ()
+
+
+class BRAGPTQ:
+    def __init__(self, layer, braq_quantizer, salient_metric, disable_gptq=False):
+        self.layer = layer
+        self.dev = self.layer.weight.device
+        if self.dev.type != "cuda":
+            raise CrbError("BRAGPTQ needs the layer on a CUDA device (no CPU fallback)")
+        shape = layer.weight.shape
+        if isinstance(layer, nn.Conv2d):
+            self.rows, self.columns = shape[0], int(shape[1:].numel())
+        elif _Conv1D and isinstance(layer, _Conv1D):
+            self.rows, self.columns = shape[1], shape[0]
+        else:
+            self.rows, self.columns = shape[0], shape[1]
+        self.nsamples = 0
+        self.braq_quantizer = braq_quantizer
+        self.salient_metric = salient_metric
+        self.disable_gptq = disable_gptq
+        # Unscaled running sum  S = sum_j X_j^T X_j  (upper-triangle tiles); H = 2/nsamples * S.
+        self._S = torch.zeros((self.columns, self.columns), device=self.dev, dtype=torch.float32)
+        self._H_set = None          # a Hessian assigned from outside (diagnostics inject g.H)
+        self._H_keep = None
+        self.last_flags = 0
+        self.last_trace = None
+        self.last_timing = {}
+
+    # ---- the Hessian as the reference exposes it ------------------------------------------
+    @property
+    def H(self):
+        """The scaled Hessian 2/n * sum X^T X as a full symmetric matrix (bigptq.py:50-53)."""
+        if self._H_set is not None:
+            return self._H_set
+        if self._S is None:
+            return None
+        H = self._S.clone()
+        ops.hessian_finalize(H, 2.0 / max(self.nsamples, 1))
+        return H
+
+    @H.setter
+    def H(self, value):
+        if value is None:
+            self._H_set, self._S = None, None
+            return
+        if value.device != self.dev:
+            value = value.to(self.dev)
+        self._H_set = value.float().contiguous()
+
+    @H.deleter
+    def H(self):
+        self._H_set, self._S = None, None
+
+    def add_batch(self, inp, out=None, blocksize=1024):
+        """Accumulates the layer input into the Hessian (bigptq.py:37-54)."""
+        if inp.dim() == 2:
+            inp = inp.unsqueeze(0)
+        batch = inp.shape[0]
+        if not isinstance(self.layer, nn.Linear) and not (_Conv1D and isinstance(self.layer, _Conv1D)):
+            raise NotImplementedError("add_batch: only nn.Linear / Conv1D layers are supported")
+        x = inp.reshape(-1, inp.shape[-1])
+        if self._H_set is not None:
+            # continue from an injected Hessian: S = H * n / 2
+            self._S = self._H_set * (self.nsamples / 2.0)
+            self._H_set = None
+        ops.hessian_accumulate(self._S, x)
+        self.nsamples += batch
+
+    def _restore_hessian(self, H):
+        if self._H_keep is not None:
+            H.copy_(self._H_keep)
+        else:
+            H.copy_(self._S)
+            ops.hessian_finalize(H, 2.0 / max(self.nsamples, 1))
+
+    def fasterquant(self, blocksize=128, percdamp=0.01, partition=3, orders=(1, 1, 2),
+                    global_scale=False):
+        technique = getattr(self.braq_quantizer, "method", None)
+        if technique not in ("braq", "crbog", "crb"):
+            raise NotImplementedError(f"technique {technique!r}: only braq, crbog and crb are implemented")
+        if partition != 3 or tuple(orders) != (1, 1, 2):
+            raise NotImplementedError("only partition=3 with orders=(1,1,2) is implemented")
+        if blocksize != BLOCK:
+            raise NotImplementedError(f"only blocksize {BLOCK} is implemented")
+        if self.disable_gptq:
+            raise NotImplementedError("disable_gptq (RTN) is not implemented")
+        if self.salient_metric != "hessian":
+            raise NotImplementedError("only salient_metric='hessian' is implemented")
+        assert self.braq_quantizer.groupsize % blocksize == 0       # bigptq.py:147
+        if self.columns % BLOCK:
+            raise NotImplementedError(f"in_features must be a multiple of {BLOCK}")
+
+        tick = time.time()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        W = self.layer.weight.data.clone()
+        if isinstance(self.layer, nn.Conv2d):
+            W = W.flatten(1)
+        if _Conv1D and isinstance(self.layer, _Conv1D):
+            W = W.t()
+        W = W.float().contiguous()
+
+        # the reference consumes H here (bigptq.py:101-102)
+        if self._H_set is not None:
+            H, self._H_keep = self._H_set.clone(), self._H_set
+        else:
+            H, self._H_keep = self._S.clone(), None
+            ops.hessian_finalize(H, 2.0 / max(self.nsamples, 1))
+        ev[0].record()
+        U = ops.hinv_upper_factor(H, W, percdamp, restore=self._restore_hessian)
+        ev[1].record()
+        self._H_set, self._S, self._H_keep = None, None, None
+
+        lam = float(getattr(self.braq_quantizer, "lam", 1e-5))
+        corr_damp = float(getattr(self.braq_quantizer, "corr_damp", 0.1))
+        out = ops.quantize_linear(W, U, technique, lam, corr_damp, self.salient_metric,
+                                  want_codes=False, want_trace=True)
+        ev[2].record()
+        error = torch.sum(out["losses"]).item()                     # synchronises
+        flags = ops.read_status(out["workspace"])
+        if flags & ~FLAG_NONFINITE:
+            raise CrbError(f"block loop reported device status flags {flags:#x}")
+        self.last_trace = out["trace"]
+        self.last_flags = flags
+        self.last_timing = {"factor_ms": ev[0].elapsed_time(ev[1]), "blocks_ms": ev[1].elapsed_time(ev[2])}
+        print("time %.2f" % (time.time() - tick))
+        print("error", error)
+
+        if _Conv1D and isinstance(self.layer, _Conv1D):
+            W = W.t()
+        self.layer.weight.data = W.reshape(self.layer.weight.shape).to(self.layer.weight.data.dtype)
+        del H, U, W
+        return {"error": error}
+
+    def free(self):
+        """Drops the Hessian (bigptq.py:293-298).  The cached allocator is left alone."""
+        self._H_set, self._S = None, None

@@ -1,0 +1,147 @@
+// extern "C" surface of libcrb_b200 (declared in include/crb_b200.h).
+#include <stdio.h>
+
+#include "common.cuh"
+
+namespace crb {
+
+unsigned long long g_launches = 0;
+
+// block_step.cu
+size_t block_workspace_bytes(int R);
+int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu, int block,
+                      int technique, float lam, float corr_damp, int metric, float* Err,
+                      float* Losses, unsigned char* codes, int64_t ld_codes, float* scales,
+                      double* trace, void* workspace, size_t workspace_bytes, cudaStream_t st);
+int binarize_group_launch(const float* W, int R, int64_t ldw, const unsigned char* mask, int64_t ldm,
+                          int order, int technique, float lam, float corr_damp, float* Q, int64_t ldq,
+                          cudaStream_t st);
+// gemm_simt.cu
+int sgemm(bool trans_b, bool lower_only, int M, int N, int K, float alpha, const float* A,
+          int64_t lda, const float* B, int64_t ldb, float beta, float* C, int64_t ldc,
+          cudaStream_t st);
+// hessian.cu
+size_t hessian_workspace_bytes(int C, int64_t T, int dtype);
+int hessian_accumulate_launch(const void* X, int dtype, int64_t T, int C, int64_t ldx, float* S,
+                              void* workspace, size_t workspace_bytes, cudaStream_t st);
+int hessian_finalize_launch(float* S, int C, float scale, cudaStream_t st);
+// factor.cu
+size_t factor_workspace_bytes(int C);
+int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp, int extra_steps,
+                  void* workspace, size_t workspace_bytes, unsigned* status, cudaStream_t st);
+
+static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+}  // namespace crb
+
+using namespace crb;
+
+extern "C" {
+
+int crb_version(void) { return 1; }
+
+const char* crb_arch(void) { return "sm_100a"; }
+
+const char* crb_status_string(int status) {
+    switch (status) {
+        case CRB_OK: return "ok";
+        case CRB_ERR_BAD_ARG: return "bad argument";
+        case CRB_ERR_WORKSPACE: return "workspace too small";
+        case CRB_ERR_LAUNCH: return "CUDA launch or API call failed";
+        case CRB_ERR_UNSUPPORTED: return "unsupported shape or option";
+        default: return status > 0 ? "device status flags" : "unknown error";
+    }
+}
+
+unsigned long long crb_launch_count(void) { return g_launches; }
+
+size_t crb_hessian_workspace_bytes(int C, int64_t T, int dtype) { return hessian_workspace_bytes(C, T, dtype); }
+
+int crb_hessian_accumulate(const void* X, int dtype, int64_t T, int C, int64_t ldx, float* S,
+                           void* workspace, size_t workspace_bytes, void* stream) {
+    return hessian_accumulate_launch(X, dtype, T, C, ldx, S, workspace, workspace_bytes,
+                                     static_cast<cudaStream_t>(stream));
+}
+
+int crb_hessian_finalize(float* S, int C, float scale, void* stream) {
+    return hessian_finalize_launch(S, C, scale, static_cast<cudaStream_t>(stream));
+}
+
+size_t crb_factor_workspace_bytes(int C) { return factor_workspace_bytes(C); }
+
+int crb_hinv_upper_factor(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
+                          int extra_damp_steps, void* workspace, size_t workspace_bytes,
+                          unsigned* status, void* stream) {
+    return factor_launch(H, C, W, R, ldw, percdamp, extra_damp_steps, workspace, workspace_bytes, status,
+                         static_cast<cudaStream_t>(stream));
+}
+
+size_t crb_block_workspace_bytes(int R) { return R > 0 ? block_workspace_bytes(R) : 0; }
+
+int crb_block_step(float* W, int R, int64_t ldw, const float* U, int64_t ldu, int block,
+                   int technique, float lam, float corr_damp, int metric, float* Err, float* Losses,
+                   uint8_t* codes, float* scales, double* trace, void* workspace,
+                   size_t workspace_bytes, void* stream) {
+    // `codes` is [R, 128] for a single block: offset the base so that column (block*128 + j)
+    // of a virtual [R, ldw]-wide buffer lands on codes[r, j].
+    uint8_t* codes_base = codes ? codes - (int64_t)block * kBlock : nullptr;
+    return block_step_launch(W, R, ldw, U, ldu, block, technique, lam, corr_damp, metric, Err, Losses,
+                             codes_base, kBlock, scales, trace, workspace, workspace_bytes,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int crb_binarize_group(const float* W, int R, int64_t ldw, const uint8_t* mask, int64_t ldm, int order,
+                       int technique, float lam, float corr_damp, float* Q, int64_t ldq, void* stream) {
+    return binarize_group_launch(W, R, ldw, mask, ldm, order, technique, lam, corr_damp, Q, ldq,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+int crb_trailing_update(float* W, int R, int C, int64_t ldw, const float* Err, const float* U,
+                        int64_t ldu, int block, void* stream) {
+    if (!W || !Err || !U || R <= 0 || C <= 0 || (C % kBlock) || block < 0) return CRB_ERR_BAD_ARG;
+    const int ed = (block + 1) * kBlock;
+    if (ed > C) return CRB_ERR_BAD_ARG;
+    if (ed == C) return CRB_OK;
+    return sgemm(false, false, R, C - ed, kBlock, -1.0f, Err, kBlock, U + (int64_t)block * kBlock * ldu + ed,
+                 ldu, 1.0f, W + ed, ldw, static_cast<cudaStream_t>(stream));
+}
+
+size_t crb_linear_workspace_bytes(int R) {
+    if (R <= 0) return 0;
+    return align256(block_workspace_bytes(R)) + align256(sizeof(float) * (size_t)R * kBlock);
+}
+
+int crb_quantize_linear(float* W, int R, int C, int64_t ldw, const float* U, int64_t ldu,
+                        int technique, float lam, float corr_damp, int metric, float* Losses,
+                        uint8_t* codes, float* scales, double* trace, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+    if (!W || !U || !Losses || !workspace || R <= 0 || C <= 0) return CRB_ERR_BAD_ARG;
+    if (C % kBlock) return CRB_ERR_UNSUPPORTED;
+    if (workspace_bytes < crb_linear_workspace_bytes(R)) return CRB_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t bws = align256(block_workspace_bytes(R));
+    float* Err = reinterpret_cast<float*>(static_cast<char*>(workspace) + bws);
+    if (cudaMemsetAsync(workspace, 0, 64, st) != cudaSuccess) return CRB_ERR_LAUNCH;   // status word
+    const int nblk = C / kBlock;
+    for (int b = 0; b < nblk; ++b) {
+        int rc = block_step_launch(W, R, ldw, U, ldu, b, technique, lam, corr_damp, metric, Err, Losses, codes,
+                                   C, scales ? scales + (size_t)b * R * 8 : nullptr,
+                                   trace ? trace + (size_t)b * CRB_TRACE_DOUBLES : nullptr, workspace, bws, st);
+        if (rc != CRB_OK) return rc;
+        rc = crb_trailing_update(W, R, C, ldw, Err, U, ldu, b, stream);
+        if (rc != CRB_OK) return rc;
+    }
+    return CRB_OK;
+}
+
+int crb_read_status(const void* workspace, void* stream) {
+    if (!workspace) return CRB_ERR_BAD_ARG;
+    unsigned flags = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemcpyAsync(&flags, workspace, sizeof(flags), cudaMemcpyDeviceToHost, st) != cudaSuccess)
+        return CRB_ERR_LAUNCH;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return CRB_ERR_LAUNCH;
+    return (int)(flags & 0x7fffffffu);
+}
+
+}  // extern "C"

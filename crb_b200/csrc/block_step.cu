@@ -1,0 +1,1126 @@
+// Block step of the CRB / BiLLM calibration loop for one 128-column block.
+//
+// Reference path restated here (paths inside the reference project):
+//   bigptq.py:142-263          block loop body (masks, three group quantisations, Q/Err/Losses)
+//   utils/structure.py:8-20    Hessian metric  M = w^2 / diag(U)^2
+//   utils/autosearch.py:28-83  salient-count search (49 candidates) and split search (81)
+//   utils/mask.py:7-18         low / mid masks from the split value
+//   binary.py:18-39            braq residual binarizer (also the evaluator of both searches)
+//   binary.py:577-687          crbog,  binary.py:1544-1638  crb (v7)
+//
+// Kernel sequence per block (stream ordered, no host synchronisation, no kernel waits on
+// another CTA: grid-wide decisions are taken by whichever CTA finishes last):
+//   k_metric_colscore  M, column scores, top-50 columns
+//   k_salient_search   49 candidates x rows, deterministic reduction, first strict minimum
+//   k_select_l1/l2/l3  exact radix selection (15+9+7 bits) of the 162 order statistics that
+//                      numpy.quantile(method="linear") interpolates between
+//   k_split_search     81 candidates x rows, deterministic reduction, first strict minimum
+//   k_finalize         masks, the technique's binarizer per group, Q, Err, Losses
+#include <math.h>
+
+#include "common.cuh"
+
+namespace crb {
+
+// float32 bit patterns of torch.linspace(0.10, 0.90, 81) (utils/autosearch.py:65).
+__constant__ unsigned c_split_probs[kSplits] = {
+    0x3dcccccdu, 0x3de147aeu, 0x3df5c290u, 0x3e051eb8u, 0x3e0f5c29u, 0x3e19999au,
+    0x3e23d70au, 0x3e2e147bu, 0x3e3851ecu, 0x3e428f5cu, 0x3e4ccccdu, 0x3e570a3du,
+    0x3e6147aeu, 0x3e6b851fu, 0x3e75c28fu, 0x3e800000u, 0x3e851eb8u, 0x3e8a3d71u,
+    0x3e8f5c29u, 0x3e947ae1u, 0x3e99999au, 0x3e9eb852u, 0x3ea3d70au, 0x3ea8f5c2u,
+    0x3eae147bu, 0x3eb33333u, 0x3eb851ebu, 0x3ebd70a4u, 0x3ec28f5cu, 0x3ec7ae14u,
+    0x3ecccccdu, 0x3ed1eb85u, 0x3ed70a3du, 0x3edc28f6u, 0x3ee147aeu, 0x3ee66666u,
+    0x3eeb851eu, 0x3ef0a3d7u, 0x3ef5c28fu, 0x3efae147u, 0x3f000000u, 0x3f028f5cu,
+    0x3f051eb8u, 0x3f07ae14u, 0x3f0a3d70u, 0x3f0ccccdu, 0x3f0f5c29u, 0x3f11eb85u,
+    0x3f147ae1u, 0x3f170a3du, 0x3f199999u, 0x3f1c28f5u, 0x3f1eb852u, 0x3f2147aeu,
+    0x3f23d70au, 0x3f266666u, 0x3f28f5c2u, 0x3f2b851eu, 0x3f2e147bu, 0x3f30a3d7u,
+    0x3f333333u, 0x3f35c28fu, 0x3f3851ebu, 0x3f3ae147u, 0x3f3d70a4u, 0x3f400000u,
+    0x3f428f5cu, 0x3f451eb8u, 0x3f47ae14u, 0x3f4a3d70u, 0x3f4cccccu, 0x3f4f5c29u,
+    0x3f51eb85u, 0x3f547ae1u, 0x3f570a3du, 0x3f599999u, 0x3f5c28f5u, 0x3f5eb852u,
+    0x3f6147aeu, 0x3f63d70au, 0x3f666666u};
+
+constexpr int kL1Bins = 32768;   // key bits 30..16
+constexpr int kL2Bins = 512;     // key bits 15..7
+constexpr int kL3Bins = 128;     // key bits 6..0
+constexpr int kMaxCtas1 = 148;   // CTAs of the metric kernel (one per SM at most)
+constexpr int kMaxTiles = 256;   // row tiles of the search kernels
+constexpr int kSearchThreads = 256;
+
+// Device workspace of the block step, carved by carve_block_ws().
+struct BlockWs {
+    unsigned* status;        // [16]   persistent status word (+ padding)
+    // ---- zeroed before every block (one memset) ----
+    unsigned char* zero_begin;
+    size_t zero_bytes;
+    unsigned* counters;      // [16]   last-CTA tickets, one per kernel
+    unsigned* hist1;         // [kL1Bins]
+    unsigned char* slot1;    // [kL1Bins] 0 = not a target bin, else level-1 slot + 1
+    unsigned* hist2;         // [kTargets][kL2Bins]
+    unsigned* hist3;         // [kTargets][kL3Bins]
+    // ---- scratch ----
+    float* M;                // [R][128] metric
+    double* colpart;         // [kMaxCtas1][128]
+    double* partial;         // [kSplits + 1][tile_stride]
+    unsigned char* rank;     // [128] position of each column in the score order (>= 50: never salient)
+    int* sel;                // [8]   0: i*   1: k*   2: level-1 slots   3: level-2 slots
+    float* pvals;            // [kSplits + 1]  the 81 split candidates, [81] = chosen split
+    unsigned* tgt_rank;      // [kTargets]
+    unsigned* tgt_bin1;      // [kTargets]
+    unsigned* tgt_bin2;      // [kTargets]
+    unsigned* tgt_rem;       // [kTargets] rank left inside the current bin
+    unsigned* tgt_slot;      // [kTargets] slot of the target at the current level
+    float* tgt_frac;         // [kSplits]  interpolation weight
+    unsigned* l2_start;      // [kTargets + 1] per level-1 slot: first level-2 slot
+    unsigned* l2_bin;        // [kTargets]     level-2 bin of each level-2 slot
+    double* trace_dummy;     // [CRB_TRACE_DOUBLES] sink when the caller passes no trace
+    int tile_stride;
+};
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static size_t carve_block_ws(void* base, int R, BlockWs* ws) {
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        void* p = base ? static_cast<char*>(base) + off : nullptr;
+        off += align_up(bytes, 256);
+        return p;
+    };
+    BlockWs w;
+    w.status = static_cast<unsigned*>(take(64));
+    const size_t z0 = off;
+    w.counters = static_cast<unsigned*>(take(64));
+    w.hist1 = static_cast<unsigned*>(take(sizeof(unsigned) * kL1Bins));
+    w.slot1 = static_cast<unsigned char*>(take(kL1Bins));
+    w.hist2 = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets * kL2Bins));
+    w.hist3 = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets * kL3Bins));
+    w.zero_begin = base ? static_cast<unsigned char*>(base) + z0 : nullptr;
+    w.zero_bytes = off - z0;
+    w.M = static_cast<float*>(take(sizeof(float) * (size_t)R * kBlock));
+    w.colpart = static_cast<double*>(take(sizeof(double) * kMaxCtas1 * kBlock));
+    w.tile_stride = kMaxTiles;
+    w.partial = static_cast<double*>(take(sizeof(double) * (kSplits + 1) * kMaxTiles));
+    w.rank = static_cast<unsigned char*>(take(kBlock));
+    w.sel = static_cast<int*>(take(sizeof(int) * 8));
+    w.pvals = static_cast<float*>(take(sizeof(float) * (kSplits + 1)));
+    w.tgt_rank = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets));
+    w.tgt_bin1 = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets));
+    w.tgt_bin2 = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets));
+    w.tgt_rem = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets));
+    w.tgt_slot = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets));
+    w.tgt_frac = static_cast<float*>(take(sizeof(float) * kSplits));
+    w.l2_start = static_cast<unsigned*>(take(sizeof(unsigned) * (kTargets + 1)));
+    w.l2_bin = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets));
+    w.trace_dummy = static_cast<double*>(take(sizeof(double) * CRB_TRACE_DOUBLES));
+    if (ws) *ws = w;
+    return off;
+}
+
+// ---------------------------------------------------------------------------------------
+// K1: metric, column scores, top-50 columns                     (structure.py:10, autosearch.py:37-42)
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
+                  const float* __restrict__ U, int64_t ldu, int rows_per_cta,
+                  float* __restrict__ M, double* __restrict__ colpart, unsigned* counters,
+                  unsigned char* __restrict__ rank_out, double* __restrict__ trace,
+                  unsigned* status) {
+    __shared__ float s_d2[kBlock];
+    __shared__ double s_wcol[8][kBlock];
+    __shared__ double s_score[kBlock];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = row_in_warp(lane), l = lane_in_row(lane);
+    if (tid < kBlock) {
+        const float d = U[(int64_t)(col0 + tid) * ldu + col0 + tid];
+        s_d2[tid] = __fmul_rn(d, d);
+    }
+    __syncthreads();
+    float d2[16], csum[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { d2[j] = s_d2[col_of(l, j)]; csum[j] = 0.f; }
+    bool bad = false;
+    const int row_base = blockIdx.x * rows_per_cta;
+    for (int p = 0; p < rows_per_cta; p += 32) {
+        const int row = row_base + p + warp * 4 + g;
+        if (row < R && row < row_base + rows_per_cta) {
+            float x[16];
+            load_row16(W + (int64_t)row * ldw + col0, l, x);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float m = __fdiv_rn(__fmul_rn(x[j], x[j]), d2[j]);
+                bad |= !isfinite(m);
+                x[j] = m;
+                csum[j] += m;          // M >= 0, so |M| = M (autosearch.py:37)
+            }
+            store_row16(M + (int64_t)row * kBlock, l, x);
+        }
+    }
+    if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(status, CRB_FLAG_NONFINITE);
+    // sum the 4 rows of the warp, then the 8 warps, in double
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        double v = (double)csum[j];
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        if (g == 0) s_wcol[warp][col_of(l, j)] = v;
+    }
+    __syncthreads();
+    if (tid < kBlock) {
+        double v = 0.0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v += s_wcol[w][tid];
+        colpart[(size_t)blockIdx.x * kBlock + tid] = v;
+    }
+    if (!last_cta_done(&counters[0], gridDim.x)) return;
+
+    if (tid < kBlock) {
+        double v = 0.0;
+        for (unsigned c = 0; c < gridDim.x; ++c) v += __ldcg(&colpart[(size_t)c * kBlock + tid]);
+        s_score[tid] = v;
+    }
+    __syncthreads();
+    if (tid < kBlock) {
+        const double mine = s_score[tid];
+        int r = 0;
+        for (int c = 0; c < kBlock; ++c) {
+            const double o = s_score[c];
+            r += (o > mine) || (o == mine && c < tid);
+        }
+        rank_out[tid] = (unsigned char)r;
+        if (r < kSalLimit) trace[6 + r] = (double)tid;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Row evaluators of the searches: squared error of the braq residual binarizer
+// (binary.py:18-39) on column sets of one row held by 8 lanes.
+// ---------------------------------------------------------------------------------------
+// Order-2 expansion on the set S = {rank < i} and on its complement; returns the squared
+// error over all 128 columns (identical in the 8 lanes of the row).
+__device__ __forceinline__ float hor2_pair_err(const float (&x)[16], const int (&rk)[16], int i) {
+    const float nS = (float)i, nN = (float)(kBlock - i);
+    float sS = 0.f, sN = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const bool in = rk[j] < i;
+        sS += in ? x[j] : 0.f;
+        sN += in ? 0.f : x[j];
+    }
+    const float muS = __fdiv_rn(red8(sS), nS), muN = __fdiv_rn(red8(sN), nN);
+    float dv[16], y1[16];
+    float aS = 0.f, aN = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const bool in = rk[j] < i;
+        dv[j] = x[j] - (in ? muS : muN);
+        const float a = fabsf(dv[j]);
+        aS += in ? a : 0.f;
+        aN += in ? 0.f : a;
+    }
+    const float alS = __fdiv_rn(red8(aS), nS), alN = __fdiv_rn(red8(aN), nN);
+    float rS = 0.f, rN = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const bool in = rk[j] < i;
+        y1[j] = __fadd_rn((in ? alS : alN) * sgnf(dv[j]), in ? muS : muN);
+        const float r = x[j] - y1[j];
+        dv[j] = r;
+        rS += in ? r : 0.f;
+        rN += in ? 0.f : r;
+    }
+    const float mu2S = __fdiv_rn(red8(rS), nS), mu2N = __fdiv_rn(red8(rN), nN);
+    aS = 0.f; aN = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const bool in = rk[j] < i;
+        dv[j] = dv[j] - (in ? mu2S : mu2N);
+        const float a = fabsf(dv[j]);
+        aS += in ? a : 0.f;
+        aN += in ? 0.f : a;
+    }
+    const float al2S = __fdiv_rn(red8(aS), nS), al2N = __fdiv_rn(red8(aN), nN);
+    float err = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const bool in = rk[j] < i;
+        const float piece = __fadd_rn((in ? al2S : al2N) * sgnf(dv[j]), in ? mu2S : mu2N);
+        const float q = __fadd_rn(y1[j], piece);
+        const float d = x[j] - q;
+        err += d * d;
+    }
+    return red8(err);
+}
+
+// Order-2 expansion on S = {rank < i} only; squared error over S.
+__device__ __forceinline__ float hor2_single_err(const float (&x)[16], const int (&rk)[16], int i) {
+    const float n = (float)i;
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) s += (rk[j] < i) ? x[j] : 0.f;
+    const float mu = __fdiv_rn(red8(s), n);
+    float dv[16], y1[16];
+    float a = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { dv[j] = x[j] - mu; a += (rk[j] < i) ? fabsf(dv[j]) : 0.f; }
+    const float al = __fdiv_rn(red8(a), n);
+    s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        y1[j] = __fadd_rn(al * sgnf(dv[j]), mu);
+        dv[j] = x[j] - y1[j];
+        s += (rk[j] < i) ? dv[j] : 0.f;
+    }
+    const float mu2 = __fdiv_rn(red8(s), n);
+    a = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { dv[j] -= mu2; a += (rk[j] < i) ? fabsf(dv[j]) : 0.f; }
+    const float al2 = __fdiv_rn(red8(a), n);
+    float err = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float q = __fadd_rn(y1[j], __fadd_rn(al2 * sgnf(dv[j]), mu2));
+        const float d = x[j] - q;
+        err += (rk[j] < i) ? d * d : 0.f;
+    }
+    return red8(err);
+}
+
+// Order-1 expansion on {non-salient, x < p} and on {non-salient, x >= p}; squared error over
+// the non-salient columns of the row (mask.py:7-18 + binary.py:18-39 with order 1).
+__device__ __forceinline__ float hor1_split_err(const float (&x)[16], const int (&rk)[16], int isal,
+                                                float p) {
+    float s1 = 0.f, s2 = 0.f;
+    int n1 = 0, n2 = 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const bool ns = rk[j] >= isal;
+        const bool lo = ns && (x[j] < p), hi = ns && (x[j] >= p);
+        s1 += lo ? x[j] : 0.f;
+        s2 += hi ? x[j] : 0.f;
+        n1 += lo; n2 += hi;
+    }
+    n1 = red8i(n1); n2 = red8i(n2);
+    s1 = red8(s1); s2 = red8(s2);               // reductions stay outside row-dependent branches
+    const float mu1 = n1 ? __fdiv_rn(s1, (float)n1) : 0.f;   // empty side: nanmean -> 0 (binary.py:29)
+    const float mu2 = n2 ? __fdiv_rn(s2, (float)n2) : 0.f;
+    float dv[16];
+    float a1 = 0.f, a2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const bool ns = rk[j] >= isal;
+        const bool lo = ns && (x[j] < p), hi = ns && (x[j] >= p);
+        dv[j] = x[j] - (lo ? mu1 : mu2);
+        const float a = fabsf(dv[j]);
+        a1 += lo ? a : 0.f;
+        a2 += hi ? a : 0.f;
+    }
+    a1 = red8(a1); a2 = red8(a2);
+    const float al1 = n1 ? __fdiv_rn(a1, (float)n1) : 0.f;
+    const float al2 = n2 ? __fdiv_rn(a2, (float)n2) : 0.f;
+    float err = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const bool ns = rk[j] >= isal;
+        const bool lo = ns && (x[j] < p), hi = ns && (x[j] >= p);
+        const float q = __fadd_rn((lo ? al1 : al2) * sgnf(dv[j]), lo ? mu1 : mu2);
+        const float d = x[j] - q;
+        // a non-salient NaN belongs to neither side and is reconstructed as 0
+        err += (lo || hi) ? d * d : (ns ? x[j] * x[j] : 0.f);
+    }
+    return red8(err);
+}
+
+// Sums partial[c][0..n_tiles) for c in [0, n_cand) with a fixed order (one warp per
+// candidate: lane-strided sequential sums, then a butterfly), result in s_out[c].
+__device__ void reduce_partials(const double* __restrict__ partial, int tile_stride, int n_tiles,
+                                int n_cand, double* s_out) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int c = warp; c < n_cand; c += nw) {
+        double v = 0.0;
+        for (int t = lane; t < n_tiles; t += 32) v += __ldcg(&partial[(size_t)c * tile_stride + t]);
+        v = warp_sum_d(v);
+        if (lane == 0) s_out[c] = v;
+    }
+    __syncthreads();
+}
+
+// First strict minimum (autosearch.py:53, :78) and the relative gap to the runner-up.
+__device__ void first_strict_min(const double* e, int n, int fallback, int* best_out, double* gap_out) {
+    int best = -1;
+    double be = INFINITY;
+    for (int c = 0; c < n; ++c)
+        if (e[c] < be) { be = e[c]; best = c; }
+    double second = INFINITY;
+    for (int c = 0; c < n; ++c)
+        if (c != best && e[c] < second) second = e[c];
+    *best_out = best < 0 ? fallback : best;
+    *gap_out = (best < 0 || !(be > 0.0)) ? 0.0 : (second - be) / be;
+}
+
+// ---------------------------------------------------------------------------------------
+// K2: salient-count search                                           (autosearch.py:44-55)
+// grid (row tiles, candidate chunks); each CTA: rows_per_cta rows x `chunk` candidates.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kSearchThreads)
+k_salient_search(const float* __restrict__ M, int R, int rows_per_cta, int chunk,
+                 const unsigned char* __restrict__ rank, double* __restrict__ partial,
+                 int tile_stride, unsigned* counters, int* __restrict__ sel,
+                 double* __restrict__ trace, unsigned* status) {
+    __shared__ double s_acc[kSalCand][32];
+    __shared__ double s_tot[kSalCand];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = row_in_warp(lane), l = lane_in_row(lane);
+    const int c0 = blockIdx.y * chunk;
+    const int nc = min(chunk, kSalCand - c0);
+    for (int k = tid; k < kSalCand * 32; k += blockDim.x) (&s_acc[0][0])[k] = 0.0;
+    int rk[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) rk[j] = rank[col_of(l, j)];
+    __syncthreads();
+    const int row_base = blockIdx.x * rows_per_cta;
+    for (int p = 0; p < rows_per_cta; p += 32) {
+        const int row = row_base + p + warp * 4 + g;
+        float x[16];
+        if (row < R) {
+            load_row16(M + (int64_t)row * kBlock, l, x);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) x[j] = 0.f;
+        }
+        for (int c = 0; c < nc; ++c) {
+            const float e = hor2_pair_err(x, rk, c0 + c + 1);
+            if (l == 0) s_acc[c][warp * 4 + g] += (double)e;
+        }
+    }
+    __syncthreads();
+    if (tid < nc) {
+        double v = 0.0;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) v += s_acc[tid][k];
+        partial[(size_t)(c0 + tid) * tile_stride + blockIdx.x] = v;
+    }
+    if (!last_cta_done(&counters[1], gridDim.x * gridDim.y)) return;
+
+    reduce_partials(partial, tile_stride, gridDim.x, kSalCand, s_tot);
+    if (tid == 0) {
+        int best; double gap;
+        first_strict_min(s_tot, kSalCand, max(1, kSalLimit / 3) - 1, &best, &gap);
+        sel[0] = best + 1;
+        trace[0] = (double)(best + 1);
+        trace[3] = gap;
+        bool bad = false;
+        const double inv = 1.0 / ((double)R * kBlock);
+        for (int c = 0; c < kSalCand; ++c) { trace[56 + c] = s_tot[c] * inv; bad |= !isfinite(s_tot[c]); }
+        if (bad) atomicOr(status, CRB_FLAG_NONFINITE);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// K3-K5: exact selection of the order statistics behind the 81 quantiles
+// (autosearch.py:62-68: numpy.quantile of |M * ~mask3| flattened, zeros at salient columns
+// included).  Keys are the float bit patterns (values are >= 0), selected by three histogram
+// levels; the salient zeros are added to bin 0 as a count.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned block_exclusive_scan_1024(unsigned v, unsigned* s_warp) {
+    // exclusive scan of one value per thread over a 1024-thread CTA
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) s_warp[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        unsigned w = s_warp[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned t = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += t;
+        }
+        s_warp[lane] = w;   // inclusive scan of the warp totals
+    }
+    __syncthreads();
+    const unsigned base = warp ? s_warp[warp - 1] : 0u;
+    return base + inc - v;
+}
+
+// Level 1: histogram of key bits 30..16 over the non-salient elements.
+__global__ void __launch_bounds__(1024)
+k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
+            const int* __restrict__ sel, BlockWs ws) {
+    extern __shared__ unsigned s_hist[];           // kL1Bins
+    __shared__ unsigned s_warp[32];
+    __shared__ unsigned s_tbin[kTargets];
+    __shared__ bool s_sal[kBlock];
+    const int tid = threadIdx.x;
+    const int isal = sel[0];
+    for (int k = tid; k < kL1Bins; k += blockDim.x) s_hist[k] = 0u;
+    if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
+    __syncthreads();
+    const size_t n4 = (size_t)R * (kBlock / 4);
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + tid; idx < n4; idx += (size_t)gridDim.x * blockDim.x) {
+        const int c4 = (int)(idx & 31) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(M + idx * 4);
+        const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (!s_sal[c4 + k]) atomicAdd(&s_hist[__float_as_uint(vv[k]) >> 16 & (kL1Bins - 1)], 1u);
+    }
+    __syncthreads();
+    for (int k = tid; k < kL1Bins; k += blockDim.x) {
+        const unsigned c = s_hist[k];
+        if (c) atomicAdd(&ws.hist1[k], c);
+    }
+    if (!last_cta_done(&ws.counters[2], gridDim.x)) return;
+
+    // ---- scan + locate the 162 target ranks ----
+    const unsigned N = (unsigned)R * kBlock;
+    const unsigned zeros = (unsigned)R * (unsigned)isal;
+    for (int k = tid; k < kL1Bins; k += blockDim.x) s_hist[k] = __ldcg(&ws.hist1[k]) + (k == 0 ? zeros : 0u);
+    __syncthreads();
+    {
+        unsigned loc = 0;
+        const int b0 = tid * (kL1Bins / 1024);
+#pragma unroll 8
+        for (int k = 0; k < kL1Bins / 1024; ++k) loc += s_hist[b0 + k];
+        unsigned run = block_exclusive_scan_1024(loc, s_warp);
+        for (int k = 0; k < kL1Bins / 1024; ++k) { const unsigned c = s_hist[b0 + k]; s_hist[b0 + k] = run; run += c; }
+    }
+    __syncthreads();
+    if (tid < kSplits) {
+        // numpy: virtual index (N-1)*p in float32, floor, fractional weight in float32
+        const float p = __uint_as_float(c_split_probs[tid]);
+        const float vi = __fmul_rn((float)(N - 1), p);
+        const float lo = floorf(vi);
+        ws.tgt_frac[tid] = __fsub_rn(vi, lo);
+        const unsigned ilo = (unsigned)lo;
+        ws.tgt_rank[2 * tid] = min(ilo, N - 1);
+        ws.tgt_rank[2 * tid + 1] = min(ilo + 1, N - 1);
+    }
+    __syncthreads();
+    if (tid < kTargets) {
+        const unsigned r = ws.tgt_rank[tid];
+        int lo = 0, hi = kL1Bins;                 // last bin with exclusive prefix <= r
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_hist[mid] <= r) lo = mid; else hi = mid;
+        }
+        s_tbin[tid] = (unsigned)lo;
+        ws.tgt_bin1[tid] = (unsigned)lo;
+        ws.tgt_rem[tid] = r - s_hist[lo];
+    }
+    __syncthreads();
+    if (tid == 0) {
+        unsigned slot = 0;
+        for (int t = 0; t < kTargets; ++t) {
+            if (t > 0 && s_tbin[t] != s_tbin[t - 1]) ++slot;
+            ws.tgt_slot[t] = slot;
+            ws.slot1[s_tbin[t]] = (unsigned char)(slot + 1);
+        }
+        ws.sel[2] = (int)slot + 1;
+    }
+}
+
+// Warp-level search of `rem` inside a histogram row of `nbins` counters (nbins = 32 * per).
+// Returns the bin holding the rem-th element (0-based) and the rank left inside that bin.
+template <int PER>
+__device__ __forceinline__ void warp_locate(const unsigned* row, unsigned rem, unsigned* bin_out,
+                                            unsigned* rem_out) {
+    const int lane = threadIdx.x & 31;
+    unsigned c[PER];
+    unsigned tot = 0;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) { c[k] = __ldcg(&row[lane * PER + k]); tot += c[k]; }
+    unsigned inc = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    const unsigned exc = inc - tot;
+    const bool mine = (exc <= rem) && (rem < inc);
+    const unsigned who = __ballot_sync(0xffffffffu, mine);
+    unsigned bin = 32 * PER - 1, left = 0;
+    if (mine) {
+        unsigned run = exc;
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            if (rem < run + c[k]) { bin = lane * PER + k; left = rem - run; break; }
+            run += c[k];
+        }
+    }
+    const int src = who ? (__ffs(who) - 1) : 0;
+    *bin_out = __shfl_sync(0xffffffffu, bin, src);
+    *rem_out = __shfl_sync(0xffffffffu, left, src);
+}
+
+// Level 2: key bits 15..7 of the elements that fall in a level-1 target bin.
+__global__ void __launch_bounds__(512)
+k_select_l2(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
+            const int* __restrict__ sel, BlockWs ws) {
+    __shared__ bool s_sal[kBlock];
+    __shared__ unsigned s_bin2[kTargets];
+    const int tid = threadIdx.x;
+    const int isal = sel[0];
+    if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
+    __syncthreads();
+    const size_t n4 = (size_t)R * (kBlock / 4);
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + tid; idx < n4; idx += (size_t)gridDim.x * blockDim.x) {
+        const int c4 = (int)(idx & 31) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(M + idx * 4);
+        const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (s_sal[c4 + k]) continue;
+            const unsigned key = __float_as_uint(vv[k]) & 0x7fffffffu;
+            const unsigned s = ws.slot1[key >> 16];
+            if (s) atomicAdd(&ws.hist2[(size_t)(s - 1) * kL2Bins + ((key >> 7) & (kL2Bins - 1))], 1u);
+        }
+    }
+    if (!last_cta_done(&ws.counters[3], gridDim.x)) return;
+
+    if (tid == 0) {
+        const unsigned s0 = ws.slot1[0];
+        if (s0) atomicAdd(&ws.hist2[(size_t)(s0 - 1) * kL2Bins], (unsigned)R * (unsigned)isal);
+    }
+    __syncthreads();
+    const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+    for (int t = warp; t < kTargets; t += nw) {
+        unsigned bin, left;
+        warp_locate<kL2Bins / 32>(ws.hist2 + (size_t)ws.tgt_slot[t] * kL2Bins, ws.tgt_rem[t], &bin, &left);
+        if (lane == 0) { s_bin2[t] = bin; ws.tgt_bin2[t] = bin; ws.tgt_rem[t] = left; }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        // level-2 slots: distinct (level-1 slot, bin2) pairs in rank order
+        unsigned slot2 = 0, prev1 = 0xffffffffu;
+        for (int t = 0; t < kTargets; ++t) {
+            const unsigned s1 = ws.tgt_slot[t];
+            const bool fresh = (t == 0) || s1 != prev1 || s_bin2[t] != s_bin2[t - 1];
+            if (t > 0 && fresh) ++slot2;
+            if (s1 != prev1) {
+                // every level-1 slot between prev1 and s1 starts here (slots are consecutive)
+                ws.l2_start[s1] = slot2;
+                prev1 = s1;
+            }
+            if (fresh) ws.l2_bin[slot2] = s_bin2[t];
+            ws.tgt_slot[t] = slot2;
+        }
+        ws.l2_start[prev1 + 1] = slot2 + 1;
+        ws.sel[3] = (int)slot2 + 1;
+    }
+}
+
+// Level 3: key bits 6..0, then the 81 interpolated split candidates.
+__global__ void __launch_bounds__(512)
+k_select_l3(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
+            const int* __restrict__ sel, BlockWs ws) {
+    __shared__ bool s_sal[kBlock];
+    __shared__ float s_val[kTargets];
+    const int tid = threadIdx.x;
+    const int isal = sel[0];
+    if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
+    __syncthreads();
+    const size_t n4 = (size_t)R * (kBlock / 4);
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + tid; idx < n4; idx += (size_t)gridDim.x * blockDim.x) {
+        const int c4 = (int)(idx & 31) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(M + idx * 4);
+        const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (s_sal[c4 + k]) continue;
+            const unsigned key = __float_as_uint(vv[k]) & 0x7fffffffu;
+            const unsigned s = ws.slot1[key >> 16];
+            if (!s) continue;
+            const unsigned b2 = (key >> 7) & (kL2Bins - 1);
+            const unsigned j1 = ws.l2_start[s];
+            for (unsigned j = ws.l2_start[s - 1]; j < j1; ++j)
+                if (ws.l2_bin[j] == b2) { atomicAdd(&ws.hist3[(size_t)j * kL3Bins + (key & (kL3Bins - 1))], 1u); break; }
+        }
+    }
+    if (!last_cta_done(&ws.counters[4], gridDim.x)) return;
+
+    if (tid == 0) {
+        const unsigned s0 = ws.slot1[0];
+        if (s0) {
+            const unsigned j = ws.l2_start[s0 - 1];
+            if (ws.l2_bin[j] == 0u) atomicAdd(&ws.hist3[(size_t)j * kL3Bins], (unsigned)R * (unsigned)isal);
+        }
+    }
+    __syncthreads();
+    const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+    for (int t = warp; t < kTargets; t += nw) {
+        unsigned bin, left;
+        warp_locate<kL3Bins / 32>(ws.hist3 + (size_t)ws.tgt_slot[t] * kL3Bins, ws.tgt_rem[t], &bin, &left);
+        if (lane == 0)
+            s_val[t] = __uint_as_float((ws.tgt_bin1[t] << 16) | (ws.tgt_bin2[t] << 7) | bin);
+    }
+    __syncthreads();
+    if (tid < kSplits) {
+        // numpy _lerp: a + (b-a)*t, replaced by b - (b-a)*(1-t) when t >= 0.5; float32, unfused
+        const float a = s_val[2 * tid], b = s_val[2 * tid + 1], t = ws.tgt_frac[tid];
+        const float diff = __fsub_rn(b, a);
+        const float v0 = __fadd_rn(a, __fmul_rn(diff, t));
+        const float v1 = __fsub_rn(b, __fmul_rn(diff, __fsub_rn(1.0f, t)));
+        ws.pvals[tid] = (t >= 0.5f) ? v1 : v0;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// K6: split search                                                    (autosearch.py:72-81)
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kSearchThreads)
+k_split_search(const float* __restrict__ M, int R, int rows_per_cta, int chunk,
+               const unsigned char* __restrict__ rank, const float* __restrict__ pvals_in,
+               double* __restrict__ partial, int tile_stride, unsigned* counters,
+               int* __restrict__ sel, float* __restrict__ pvals_out, double* __restrict__ trace,
+               unsigned* status) {
+    __shared__ double s_acc[kSplits + 1][32];
+    __shared__ double s_tot[kSplits + 1];
+    __shared__ float s_p[kSplits];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = row_in_warp(lane), l = lane_in_row(lane);
+    const int isal = sel[0];
+    const int c0 = blockIdx.y * chunk;
+    const int nc = min(chunk, kSplits - c0);
+    const bool do_sal = (blockIdx.y == 0);      // the constant salient-group term, once per row
+    for (int k = tid; k < (kSplits + 1) * 32; k += blockDim.x) (&s_acc[0][0])[k] = 0.0;
+    if (tid < kSplits) s_p[tid] = pvals_in[tid];
+    int rk[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) rk[j] = rank[col_of(l, j)];
+    __syncthreads();
+    const int row_base = blockIdx.x * rows_per_cta;
+    for (int p = 0; p < rows_per_cta; p += 32) {
+        const int row = row_base + p + warp * 4 + g;
+        float x[16];
+        if (row < R) {
+            load_row16(M + (int64_t)row * kBlock, l, x);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) x[j] = 0.f;
+        }
+        for (int c = 0; c < nc; ++c) {
+            const float e = hor1_split_err(x, rk, isal, s_p[c0 + c]);
+            if (l == 0) s_acc[c][warp * 4 + g] += (double)e;
+        }
+        if (do_sal) {
+            const float e = hor2_single_err(x, rk, isal);
+            if (l == 0) s_acc[kSplits][warp * 4 + g] += (double)e;
+        }
+    }
+    __syncthreads();
+    if (tid < nc) {
+        double v = 0.0;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) v += s_acc[tid][k];
+        partial[(size_t)(c0 + tid) * tile_stride + blockIdx.x] = v;
+    }
+    if (do_sal && tid == kSearchThreads - 1) {
+        double v = 0.0;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) v += s_acc[kSplits][k];
+        partial[(size_t)kSplits * tile_stride + blockIdx.x] = v;
+    }
+    if (!last_cta_done(&counters[5], gridDim.x * gridDim.y)) return;
+
+    reduce_partials(partial, tile_stride, gridDim.x, kSplits + 1, s_tot);
+    if (tid == 0) {
+        int best; double gap;
+        const double e3 = s_tot[kSplits];
+        for (int c = 0; c < kSplits; ++c) s_tot[c] += e3;
+        first_strict_min(s_tot, kSplits, kSplits / 2, &best, &gap);
+        sel[1] = best;
+        const float p = s_p[best];
+        pvals_out[kSplits] = p;
+        trace[1] = (double)best;
+        trace[2] = (double)p;
+        trace[4] = gap;
+        const double inv = 1.0 / ((double)R * kBlock);
+        trace[5] = e3 * inv;
+        bool bad = false;
+        for (int c = 0; c < kSplits; ++c) { trace[105 + c] = s_tot[c] * inv; bad |= !isfinite(s_tot[c]); }
+        if (bad) atomicOr(status, CRB_FLAG_NONFINITE);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Group binarizers on one row held by 8 lanes (16 values per lane, `in` = membership).
+// Shared by the block step (K7) and by the stand-alone Binarization.quantize entry point.
+// (binary.py:18-39 braq, 577-687 crbog, 1544-1638 crb)
+// ---------------------------------------------------------------------------------------
+// CRB v7 joint scale solve (binary.py:1582-1596), float32 like the reference.
+__device__ __forceinline__ void crb_solve(float c12, float c1w, float c2w, float d, float lam,
+                                          float corr_damp, float* a1, float* a2) {
+    if (c12 > 0.f) c12 = __fmul_rn(c12, __fsub_rn(1.0f, corr_damp));
+    const float A = __fadd_rn(d, lam);
+    const float den = __fsub_rn(__fmul_rn(A, A), __fmul_rn(c12, c12));
+    const bool ok = fabsf(den) > 1e-12f;
+    const float dn = ok ? den : 1.0f;
+    const float x1 = fmaxf(__fdiv_rn(__fsub_rn(__fmul_rn(A, c1w), __fmul_rn(c12, c2w)), dn), 0.f);
+    const float x2 = fmaxf(__fdiv_rn(__fsub_rn(__fmul_rn(A, c2w), __fmul_rn(c12, c1w)), dn), 0.f);
+    *a1 = ok ? x1 : 0.f;
+    *a2 = ok ? x2 : 0.f;
+}
+
+// One expansion: q = mu + alpha * sign(w - mu) on the members.  The three techniques share
+// this arithmetic (binary.py:24-36, 595-630, 1570-1576).  n = member count of the row.
+__device__ __forceinline__ void group_order1(const float (&w)[16], const bool (&in)[16], int n,
+                                             float (&q)[16], int (&b1)[16], float* mu_out,
+                                             float* al_out) {
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) s += in[j] ? w[j] : 0.f;
+    s = red8(s);
+    const float nf = (float)n;
+    const float mu = n ? __fdiv_rn(s, nf) : 0.f;
+    float a = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) a += in[j] ? fabsf(w[j] - mu) : 0.f;
+    a = red8(a);
+    const float al = n ? __fdiv_rn(a, nf) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+        if (in[j]) {
+            const float sg = sgnf(w[j] - mu);
+            q[j] = __fadd_rn(al * sg, mu);
+            b1[j] = (int)sg;
+        }
+    *mu_out = mu;
+    *al_out = al;
+}
+
+// Two expansions with the technique's coupling.  sc[0..3] receives the row's scales:
+// braq mu1, alpha1, mu2, alpha2;  crbog mu, alpha1, alpha2, 0;  crb mu + mu_fix, alpha1, alpha2, 0.
+__device__ __forceinline__ void group_order2(const float (&w)[16], const bool (&in)[16], int n,
+                                             int technique, float lam, float corr_damp,
+                                             float (&q)[16], int (&b1)[16], int (&b2)[16],
+                                             float (&sc)[4]) {
+    const float d = (float)n;
+    const float ds = fmaxf(d, 1.0f);                  // rows without members produce nothing
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) s += in[j] ? w[j] : 0.f;
+    const float mu = __fdiv_rn(red8(s), ds);
+    float c[16], B1[16], B2[16];
+    float a = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { c[j] = in[j] ? (w[j] - mu) : 0.f; a += fabsf(c[j]); B1[j] = sgnf(c[j]); }
+    const float a_init = __fdiv_rn(red8(a), ds);
+    sc[0] = sc[1] = sc[2] = sc[3] = 0.f;
+
+    if (technique == CRB_TECH_BRAQ) {
+        // binary.py:18-39 with order 2
+        float y1[16], r[16];
+        s = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            y1[j] = __fadd_rn(a_init * B1[j], mu);
+            r[j] = in[j] ? (w[j] - y1[j]) : 0.f;
+            s += r[j];
+        }
+        const float mu2 = __fdiv_rn(red8(s), ds);
+        a = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { r[j] = in[j] ? (r[j] - mu2) : 0.f; a += fabsf(r[j]); }
+        const float al2 = __fdiv_rn(red8(a), ds);
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (in[j]) {
+                B2[j] = sgnf(r[j]);
+                q[j] = __fadd_rn(y1[j], __fadd_rn(al2 * B2[j], mu2));
+                b1[j] = (int)B1[j]; b2[j] = (int)B2[j];
+            }
+        sc[0] = mu; sc[1] = a_init; sc[2] = mu2; sc[3] = al2;
+    } else if (technique == CRB_TECH_CRBOG) {
+        // binary.py:644-685: no re-centring of the residual, float64 2x2 solve
+        float r[16];
+        a = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { r[j] = c[j] - a_init * B1[j]; B2[j] = sgnf(r[j]); a += fabsf(r[j]); }
+        float al1 = a_init, al2 = __fdiv_rn(red8(a), ds);
+        float f12 = 0.f, f1w = 0.f, f2w = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { f12 += B1[j] * B2[j]; f1w += c[j] * B1[j]; f2w += c[j] * B2[j]; }
+        const double c12 = (double)red8(f12), c1w = (double)red8(f1w), c2w = (double)red8(f2w);
+        const double D = (double)d;
+        const double det = D * D - c12 * c12;
+        if (fabs(det) > 1e-12) {
+            al1 = (float)fmax((c1w * D - c2w * c12) / det, 0.0);
+            al2 = (float)fmax((c2w * D - c1w * c12) / det, 0.0);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (in[j]) {
+                q[j] = __fadd_rn(__fadd_rn(mu, __fmul_rn(al1, B1[j])), __fmul_rn(al2, B2[j]));
+                b1[j] = (int)B1[j]; b2[j] = (int)B2[j];
+            }
+        sc[0] = mu; sc[1] = al1; sc[2] = al2;
+    } else {
+        // CRB v7, binary.py:1598-1636 (d_safe = max(count, 1), A = count + lam)
+        float t[16];
+        auto centred_sign = [&](float (&B)[16]) {
+            float ts = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) ts += t[j];
+            const float tm = __fdiv_rn(red8(ts), ds);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) B[j] = in[j] ? sgnf(t[j] - tm) : 0.f;
+        };
+        auto dot_c = [&](const float (&B)[16]) {
+            float v = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v += c[j] * B[j];
+            return red8(v);
+        };
+        auto dot_b = [&]() {
+            float v = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v += B1[j] * B2[j];
+            return red8(v);
+        };
+#pragma unroll
+        for (int j = 0; j < 16; ++j) t[j] = in[j] ? (c[j] - a_init * B1[j]) : 0.f;
+        centred_sign(B2);                                         // step 3
+        float c1w = dot_c(B1), c2w = dot_c(B2), a1, a2;
+        crb_solve(dot_b(), c1w, c2w, d, lam, corr_damp, &a1, &a2);   // step 4
+#pragma unroll
+        for (int j = 0; j < 16; ++j) t[j] = in[j] ? (c[j] - a1 * B1[j]) : 0.f;
+        centred_sign(B2);                                         // step 5
+        c2w = dot_c(B2);
+        crb_solve(dot_b(), c1w, c2w, d, lam, corr_damp, &a1, &a2);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) t[j] = in[j] ? (c[j] - a2 * B2[j]) : 0.f;
+        centred_sign(B1);                                         // step 6
+        c1w = dot_c(B1);
+        crb_solve(dot_b(), c1w, c2w, d, lam, corr_damp, &a1, &a2);
+        float rs = 0.f;                                           // step 7
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            rs += in[j] ? (c[j] - __fadd_rn(__fmul_rn(a1, B1[j]), __fmul_rn(a2, B2[j]))) : 0.f;
+        const float mu_fix = __fdiv_rn(red8(rs), ds);
+        const float base = __fadd_rn(mu, mu_fix);
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (in[j]) {
+                q[j] = __fadd_rn(__fadd_rn(base, __fmul_rn(a1, B1[j])), __fmul_rn(a2, B2[j]));
+                b1[j] = (int)B1[j]; b2[j] = (int)B2[j];
+            }
+        sc[0] = base; sc[1] = a1; sc[2] = a2;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// K7: final masks, the technique's binarizer on the three groups, Q / Err / Losses
+// (bigptq.py:246-263)
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+k_finalize(float* __restrict__ W, int R, int64_t ldw, int col0, const float* __restrict__ U,
+           int64_t ldu, const unsigned char* __restrict__ rank, const int* __restrict__ sel,
+           const float* __restrict__ pvals, int technique, float lam, float corr_damp,
+           float* __restrict__ Err, float* __restrict__ Losses, unsigned char* __restrict__ codes,
+           int64_t ld_codes, float* __restrict__ scales) {
+    __shared__ float s_d[kBlock];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = row_in_warp(lane), l = lane_in_row(lane);
+    if (tid < kBlock) s_d[tid] = U[(int64_t)(col0 + tid) * ldu + col0 + tid];
+    __syncthreads();
+    const int isal = sel[0];
+    const float psplit = pvals[kSplits];
+    const int row = blockIdx.x * 32 + warp * 4 + g;
+    const bool live = row < R;
+    float w[16], dd[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) dd[j] = s_d[col_of(l, j)];
+    if (live) {
+        load_row16(W + (int64_t)row * ldw + col0, l, w);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) w[j] = 0.f;
+    }
+    // group of every element: 0 low, 1 mid, 2 salient (mask.py:7-18 on the metric); a NaN metric
+    // belongs to no group (3) and is reconstructed as 0, as in the reference
+    int grp[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float m = __fdiv_rn(__fmul_rn(w[j], w[j]), __fmul_rn(dd[j], dd[j]));
+        grp[j] = ((int)rank[col_of(l, j)] < isal) ? 2 : ((m < psplit) ? 0 : ((m >= psplit) ? 1 : 3));
+    }
+    float q[16], sc[8];
+    int b1[16], b2[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { q[j] = 0.f; b1[j] = 0; b2[j] = 0; }
+#pragma unroll
+    for (int gi = 0; gi < 2; ++gi) {
+        bool in[16];
+        int n = 0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { in[j] = grp[j] == gi; n += in[j]; }
+        n = red8i(n);
+        group_order1(w, in, n, q, b1, &sc[2 * gi], &sc[2 * gi + 1]);
+    }
+    {
+        bool in[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) in[j] = grp[j] == 2;
+        float s2[4];
+        group_order2(w, in, isal, technique, lam, corr_damp, q, b1, b2, s2);
+        sc[4] = s2[0]; sc[5] = s2[1]; sc[6] = s2[2]; sc[7] = s2[3];
+    }
+
+    // ---- column epilogue (bigptq.py:249-263) ----
+    float e[16];
+    float loss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float diff = w[j] - q[j];
+        e[j] = __fdiv_rn(diff, dd[j]);
+        loss += __fdiv_rn(__fmul_rn(diff, diff), __fmul_rn(dd[j], dd[j]));
+    }
+    loss = red8(loss);
+    if (!live) return;
+    store_row16(W + (int64_t)row * ldw + col0, l, q);
+    store_row16(Err + (int64_t)row * kBlock, l, e);
+    if (l == 0) Losses[row] += loss * 0.5f;
+    if (codes) {
+#pragma unroll
+        for (int ee = 0; ee < 4; ++ee) {
+            uchar4 cc;
+            unsigned char* pc = reinterpret_cast<unsigned char*>(&cc);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const int j = 4 * ee + v;
+                pc[v] = (unsigned char)((b1[j] + 1) | ((b2[j] + 1) << 2) | ((grp[j] & 3) << 4));
+            }
+            *reinterpret_cast<uchar4*>(codes + (int64_t)row * ld_codes + col0 + 32 * ee + 4 * l) = cc;
+        }
+    }
+    if (scales && l == 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) scales[(int64_t)row * 8 + k] = sc[k];
+    }
+}
+
+// Stand-alone group binarizer on a [R, 128] block with an arbitrary element mask:
+// Binarization.quantize (binary.py:2868-2884) for braq / crbog / crb, order 1 or 2.
+__global__ void __launch_bounds__(256)
+k_binarize_group(const float* __restrict__ W, int R, int64_t ldw, const unsigned char* __restrict__ mask,
+                 int64_t ldm, int order, int technique, float lam, float corr_damp,
+                 float* __restrict__ Q, int64_t ldq) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = row_in_warp(lane), l = lane_in_row(lane);
+    const int row = blockIdx.x * 32 + warp * 4 + g;
+    const bool live = row < R;
+    float w[16], q[16];
+    bool in[16];
+    int b1[16], b2[16];
+    int n = 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { w[j] = 0.f; q[j] = 0.f; in[j] = false; b1[j] = 0; b2[j] = 0; }
+    if (live) {
+        load_row16(W + (int64_t)row * ldw, l, w);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const uchar4 m = *reinterpret_cast<const uchar4*>(mask + (int64_t)row * ldm + 32 * e + 4 * l);
+            in[4 * e + 0] = m.x != 0; in[4 * e + 1] = m.y != 0; in[4 * e + 2] = m.z != 0; in[4 * e + 3] = m.w != 0;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) n += in[j];
+    }
+    n = red8i(n);
+    if (order == 1) {
+        float mu, al;
+        group_order1(w, in, n, q, b1, &mu, &al);
+    } else {
+        float sc[4];
+        group_order2(w, in, n, technique, lam, corr_damp, q, b1, b2, sc);
+    }
+    if (live) store_row16(Q + (int64_t)row * ldq, l, q);
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+static int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+size_t block_workspace_bytes(int R) { return carve_block_ws(nullptr, R, nullptr); }
+
+int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu, int block,
+                      int technique, float lam, float corr_damp, int metric, float* Err,
+                      float* Losses, unsigned char* codes, int64_t ld_codes, float* scales,
+                      double* trace, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+    if (!W || !U || !Err || !Losses || !workspace || R <= 0 || block < 0) return CRB_ERR_BAD_ARG;
+    if (technique < CRB_TECH_BRAQ || technique > CRB_TECH_CRB) return CRB_ERR_BAD_ARG;
+    if (metric != CRB_METRIC_HESSIAN) return CRB_ERR_UNSUPPORTED;
+    if ((ldw & 3) || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(Err) & 15))
+        return CRB_ERR_BAD_ARG;
+    if ((long long)R * kBlock >= (1ll << 31)) return CRB_ERR_UNSUPPORTED;
+    BlockWs ws;
+    if (carve_block_ws(workspace, R, &ws) > workspace_bytes) return CRB_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255) return CRB_ERR_BAD_ARG;
+    double* tr = trace ? trace : ws.trace_dummy;
+    const int col0 = block * kBlock;
+
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(k_select_l1, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kL1Bins * (int)sizeof(unsigned)) != cudaSuccess)
+            return CRB_ERR_LAUNCH;
+        attr_set = true;
+    }
+    if (cudaMemsetAsync(ws.zero_begin, 0, ws.zero_bytes, st) != cudaSuccess) return CRB_ERR_LAUNCH;
+
+    // K1
+    const int rows1 = 32 * ceil_div(R, 32 * kMaxCtas1);
+    k_metric_colscore<<<ceil_div(R, rows1), 256, 0, st>>>(W, R, ldw, col0, U, ldu, rows1, ws.M, ws.colpart,
+                                                          ws.counters, ws.rank, tr, ws.status);
+    CRB_LAUNCHED();
+    // K2 / K6 tiling: <= kMaxTiles row tiles, candidate chunks so that the grid fills the GPU
+    const int rows_s = 32 * ceil_div(R, 32 * kMaxTiles);
+    const int tiles = ceil_div(R, rows_s);
+    const int want_chunks = max(1, ceil_div(4 * 148, tiles));
+    const int chunks_sal = min(want_chunks, ceil_div(kSalCand, 4));
+    const int chunk_sal = ceil_div(kSalCand, chunks_sal);
+    k_salient_search<<<dim3(tiles, ceil_div(kSalCand, chunk_sal)), kSearchThreads, 0, st>>>(
+        ws.M, R, rows_s, chunk_sal, ws.rank, ws.partial, ws.tile_stride, ws.counters, ws.sel, tr, ws.status);
+    CRB_LAUNCHED();
+    // K3-K5
+    const int n4 = R * (kBlock / 4);
+    const int g1 = min(148, ceil_div(n4, 1024 * 4));
+    k_select_l1<<<g1, 1024, kL1Bins * sizeof(unsigned), st>>>(ws.M, R, ws.rank, ws.sel, ws);
+    CRB_LAUNCHED();
+    const int g2 = min(2 * 148, ceil_div(n4, 512 * 2));
+    k_select_l2<<<g2, 512, 0, st>>>(ws.M, R, ws.rank, ws.sel, ws);
+    CRB_LAUNCHED();
+    k_select_l3<<<g2, 512, 0, st>>>(ws.M, R, ws.rank, ws.sel, ws);
+    CRB_LAUNCHED();
+    // K6
+    const int chunks_sp = min(want_chunks, ceil_div(kSplits, 4));
+    const int chunk_sp = ceil_div(kSplits, chunks_sp);
+    k_split_search<<<dim3(tiles, ceil_div(kSplits, chunk_sp)), kSearchThreads, 0, st>>>(
+        ws.M, R, rows_s, chunk_sp, ws.rank, ws.pvals, ws.partial, ws.tile_stride, ws.counters, ws.sel,
+        ws.pvals, tr, ws.status);
+    CRB_LAUNCHED();
+    // K7
+    k_finalize<<<ceil_div(R, 32), 256, 0, st>>>(W, R, ldw, col0, U, ldu, ws.rank, ws.sel, ws.pvals, technique,
+                                               lam, corr_damp, Err, Losses, codes, ld_codes, scales);
+    CRB_LAUNCHED();
+    return CRB_OK;
+}
+
+int binarize_group_launch(const float* W, int R, int64_t ldw, const unsigned char* mask, int64_t ldm,
+                          int order, int technique, float lam, float corr_damp, float* Q, int64_t ldq,
+                          cudaStream_t st) {
+    if (!W || !mask || !Q || R <= 0) return CRB_ERR_BAD_ARG;
+    if (order != 1 && order != 2) return CRB_ERR_UNSUPPORTED;
+    if (technique < CRB_TECH_BRAQ || technique > CRB_TECH_CRB) return CRB_ERR_BAD_ARG;
+    if ((ldw & 3) || (ldq & 3) || (ldm & 3) || ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(Q)) & 15) ||
+        (reinterpret_cast<uintptr_t>(mask) & 3))
+        return CRB_ERR_BAD_ARG;
+    k_binarize_group<<<ceil_div(R, 32), 256, 0, st>>>(W, R, ldw, mask, ldm, order, technique, lam, corr_damp, Q, ldq);
+    CRB_LAUNCHED();
+    return CRB_OK;
+}
+
+}  // namespace crb

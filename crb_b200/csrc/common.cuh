@@ -1,0 +1,83 @@
+// Shared helpers for the crb_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/crb_b200.h"
+
+namespace crb {
+
+// Host-side count of kernels launched by this library (crb_launch_count()).
+extern unsigned long long g_launches;
+
+#define CRB_LAUNCHED()                                   \
+    do {                                                 \
+        ++::crb::g_launches;                             \
+        if (cudaGetLastError() != cudaSuccess) return CRB_ERR_LAUNCH; \
+    } while (0)
+
+constexpr int kBlock = CRB_BLOCK;            // 128 columns per block step
+constexpr int kSalLimit = CRB_SALIENT_LIMIT; // 50
+constexpr int kSalCand = kSalLimit - 1;      // candidates i = 1..49
+constexpr int kSplits = CRB_N_SPLITS;        // 81
+constexpr int kTargets = 2 * kSplits;        // order statistics needed by the 81 quantiles
+
+// ---- row layout used by every row-parallel kernel -------------------------------------
+// A warp covers 4 rows; the 8 lanes of a row hold 16 columns each: register 4e+v of lane l
+// is column 32e + 4l + v, so that one float4 load per e is a 128-byte coalesced segment.
+__device__ __forceinline__ int row_in_warp(int lane) { return lane >> 3; }
+__device__ __forceinline__ int lane_in_row(int lane) { return lane & 7; }
+__device__ __forceinline__ int col_of(int l, int j) { return 32 * (j >> 2) + 4 * l + (j & 3); }
+
+__device__ __forceinline__ float red8(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    return v;
+}
+__device__ __forceinline__ int red8i(int v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    return v;
+}
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+// torch.sign semantics: sign(0) = 0, sign(NaN) = 0.
+__device__ __forceinline__ float sgnf(float v) { return (v > 0.f) ? 1.f : ((v < 0.f) ? -1.f : 0.f); }
+
+// Loads the 16 values of this lane from a row of 128 floats (16-byte aligned).
+__device__ __forceinline__ void load_row16(const float* __restrict__ row, int l, float (&x)[16]) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float4 v = *reinterpret_cast<const float4*>(row + 32 * e + 4 * l);
+        x[4 * e + 0] = v.x; x[4 * e + 1] = v.y; x[4 * e + 2] = v.z; x[4 * e + 3] = v.w;
+    }
+}
+__device__ __forceinline__ void store_row16(float* __restrict__ row, int l, const float (&x)[16]) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+        *reinterpret_cast<float4*>(row + 32 * e + 4 * l) =
+            make_float4(x[4 * e + 0], x[4 * e + 1], x[4 * e + 2], x[4 * e + 3]);
+}
+
+// "Last CTA done" election: returns true in exactly one CTA of the grid, after every other
+// CTA's global writes (made before the call) are visible to it.  No CTA waits on another.
+__device__ __forceinline__ bool last_cta_done(unsigned* counter, unsigned total) {
+    __shared__ bool s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned t = atomicAdd(counter, 1u);
+        s_last = (t == total - 1);
+    }
+    __syncthreads();
+    if (s_last) __threadfence();
+    return s_last;
+}
+
+}  // namespace crb

@@ -1,0 +1,504 @@
+// Hessian accumulation  S += X^T X  on the 5th-generation tensor cores (tcgen05 + TMEM),
+// operands staged by TMA.  Replaces BRAGPTQ.add_batch (bigptq.py:37-54).
+//
+// X is [T, C] row-major (channel contiguous), so both MMA operands are "MN-major": a TMA box
+// of 64 channels x 64 tokens with 128-byte swizzle lands in shared memory as 8-token x 128-byte
+// swizzle atoms, which is the canonical MN-major SWIZZLE_128B operand layout of tcgen05.mma
+// (leading-dimension offset = one 64-channel box, stride offset = 1024 bytes per 8 tokens).
+//
+// One persistent CTA per SM walks the upper-triangle output tiles (128 rows x 256 columns).
+// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (owns the TMEM allocation),
+// warps 2..5 = epilogue (TMEM -> registers -> S += acc).  Two 256-column accumulators
+// alternate so that the epilogue of one tile / token chunk overlaps the MMAs of the next.
+// The token dimension is cut into chunks; each chunk is accumulated in TMEM and then added
+// to S in float32 by the CUDA cores, which bounds the length of any tensor-core running sum.
+//
+// float32 X (the single-linear configuration) is split by a pre-pass into two fp16 planes
+// x*s = hi + lo (s a power of two); the tile then accumulates hi^T hi + hi^T lo + lo^T hi,
+// which carries 22 significand bits of every product.
+//
+// Every mbarrier wait is bounded; on expiry the kernel raises CRB_FLAG_WAIT_LIMIT, all roles
+// leave their loops, TMEM is released and the kernel returns.
+#include <cuda.h>
+#include <stdlib.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace crb {
+
+constexpr int HT_M = 128;              // output rows per tile (UMMA M)
+constexpr int HT_N = 256;              // output columns per tile (UMMA N)
+constexpr int HT_K = 64;               // tokens per pipeline stage
+constexpr int HT_BOX = 64;             // channels per TMA box (128 bytes of 16-bit elements)
+constexpr int HT_STAGES = 4;
+constexpr int HT_BOX_BYTES = HT_BOX * HT_K * 2;                          // 8 KiB
+constexpr int HT_A_BYTES = (HT_M / HT_BOX) * HT_BOX_BYTES;               // 16 KiB
+constexpr int HT_B_BYTES = (HT_N / HT_BOX) * HT_BOX_BYTES;               // 32 KiB
+constexpr int HT_STAGE_BYTES = HT_A_BYTES + HT_B_BYTES;                  // 48 KiB
+constexpr int HT_SMEM = HT_STAGES * HT_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int HT_THREADS = 192;
+constexpr unsigned long long HT_WAIT_NS = 2000000000ull;   // a single barrier wait gives up after 2 s
+
+// ---- PTX wrappers ----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if the limit ran out or another role already gave up.
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int it = 0; it < 256; ++it)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_ns() - t0 > HT_WAIT_NS) break;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of an MN-major, 128-byte-swizzled operand:
+//   bits 0-13 start address >> 4, 16-29 leading-dimension byte offset >> 4 (between 64-element
+//   boxes along M/N), 32-45 stride byte offset >> 4 (between 8-token groups), 46-47 version 1,
+//   61-63 layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t mn_sw128_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3fffu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor, kind::f16: D = f32, A/B = f16 (0) or bf16 (1), both MN-major.
+__host__ __device__ constexpr uint32_t f16_idesc(int ab_format, int M, int N) {
+    return (1u << 4) | ((uint32_t)ab_format << 7) | ((uint32_t)ab_format << 10) | (1u << 15) | (1u << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+struct HessArgs {
+    float* S;            // [C, C] accumulator (upper-triangle tiles are updated)
+    const float* inv_scale2;   // device scalar multiplying every accumulator (NULL = 1)
+    unsigned* status;
+    int C;
+    int64_t T;
+    int chunk_tokens;    // tokens accumulated in TMEM before they are added to S
+    int n_pass;          // 1: X^T X from plane 0;  3: hi^T hi + hi^T lo + lo^T hi
+    int ab_format;       // 0 f16, 1 bf16
+    int n_tiles, n_col_tiles;
+};
+
+// Linear upper-triangle tile index -> (row tile of 128, column tile of 256).  Row tiles 2h and
+// 2h+1 both need column tiles h .. n_col_tiles-1.
+__device__ __forceinline__ void tile_coords(int t, int n_col_tiles, int* mi, int* nj) {
+    int h = 0;
+    for (;;) {
+        const int per_row = n_col_tiles - h;
+        if (t < 2 * per_row) { *mi = 2 * h + (t >= per_row); *nj = h + (t >= per_row ? t - per_row : t); return; }
+        t -= 2 * per_row;
+        ++h;
+    }
+}
+
+__global__ void __launch_bounds__(HT_THREADS, 1)
+k_hessian_umma(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
+               const HessArgs args) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + HT_STAGES * HT_STAGE_BYTES);
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * HT_STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * HT_STAGES;
+    const uint32_t tfull0 = empty0 + 8 * HT_STAGES, tempty0 = tfull0 + 16;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < HT_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int n_chunks = (int)((args.T + args.chunk_tokens - 1) / args.chunk_tokens);
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            uint32_t armed = 0, armed_phase = 0;      // per stage: was it armed, and with which parity
+            bool ok = true;
+            for (int t = blockIdx.x; t < args.n_tiles && ok; t += gridDim.x) {
+                int mi, nj;
+                tile_coords(t, args.n_col_tiles, &mi, &nj);
+                for (int ch = 0; ch < n_chunks && ok; ++ch) {
+                    const int64_t t0 = (int64_t)ch * args.chunk_tokens;
+                    const int64_t t1 = min(args.T, t0 + args.chunk_tokens);
+                    for (int p = 0; p < args.n_pass && ok; ++p) {
+                        const CUtensorMap* ma = (p == 2) ? &map1 : &map0;     // hi, hi, lo
+                        const CUtensorMap* mb = (p == 1) ? &map1 : &map0;     // hi, lo, hi
+                        for (int64_t tk = t0; tk < t1; tk += HT_K) {
+                            ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag);
+                            if (!ok) break;
+                            const uint32_t sa = smem_u32(smem + stage * HT_STAGE_BYTES);
+                            const uint32_t sb = sa + HT_A_BYTES;
+                            const uint32_t fb = full0 + 8 * stage;
+                            mbar_expect_tx(fb, HT_STAGE_BYTES);
+                            armed |= 1u << stage;
+                            armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
+#pragma unroll
+                            for (int b = 0; b < HT_M / HT_BOX; ++b)
+                                tma_load_2d(sa + b * HT_BOX_BYTES, ma, mi * HT_M + b * HT_BOX, (int)tk, fb);
+#pragma unroll
+                            for (int b = 0; b < HT_N / HT_BOX; ++b)
+                                tma_load_2d(sb + b * HT_BOX_BYTES, mb, nj * HT_N + b * HT_BOX, (int)tk, fb);
+                            if (++stage == HT_STAGES) { stage = 0; phase ^= 1; }
+                        }
+                    }
+                }
+            }
+            // drain: the copies of every armed stage must have landed before shared memory goes away
+            // (immediate on the normal path, where the MMA warp has consumed them all)
+            for (int s = 0; s < HT_STAGES; ++s) {
+                if (!(armed >> s & 1u)) continue;
+                const unsigned long long t0 = global_ns();
+                while (!mbar_try_wait(full0 + 8 * s, (armed_phase >> s) & 1u))
+                    if (global_ns() - t0 > HT_WAIT_NS) { *abort_flag = 1; break; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = f16_idesc(args.ab_format, HT_M, HT_N);
+            uint32_t stage = 0, phase = 0, unit = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < args.n_tiles && ok; t += gridDim.x) {
+                for (int ch = 0; ch < n_chunks && ok; ++ch, ++unit) {
+                    const uint32_t buf = unit & 1, use = unit >> 1;
+                    ok = mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + buf * HT_N;
+                    const int64_t t0 = (int64_t)ch * args.chunk_tokens;
+                    const int64_t t1 = min(args.T, t0 + args.chunk_tokens);
+                    bool first = true;
+                    for (int p = 0; p < args.n_pass && ok; ++p) {
+                        for (int64_t tk = t0; tk < t1; tk += HT_K) {
+                            ok = mbar_wait(full0 + 8 * stage, phase, abort_flag);
+                            if (!ok) break;
+                            tc_fence_after();
+                            const uint32_t sa = smem_u32(smem + stage * HT_STAGE_BYTES);
+                            const uint32_t sb = sa + HT_A_BYTES;
+#pragma unroll
+                            for (int k = 0; k < HT_K / 16; ++k) {
+                                // 16 tokens = two 8-token swizzle atoms = 2048 bytes further along K
+                                const uint64_t da = mn_sw128_desc(sa + k * 2048, HT_BOX_BYTES, 1024);
+                                const uint64_t db = mn_sw128_desc(sb + k * 2048, HT_BOX_BYTES, 1024);
+                                umma_f16(d_tmem, da, db, idesc, !first);
+                                first = false;
+                            }
+                            umma_commit(empty0 + 8 * stage);          // frees the stage when the MMAs retire
+                            if (++stage == HT_STAGES) { stage = 0; phase ^= 1; }
+                        }
+                    }
+                    if (ok) umma_commit(tfull0 + 8 * buf);             // accumulator ready for the epilogue
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 own TMEM lanes 32*(warp % 4) .. +31 ----------------
+        const int q = warp & 3;
+        const float scale = args.inv_scale2 ? *args.inv_scale2 : 1.0f;
+        uint32_t unit = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < args.n_tiles && ok; t += gridDim.x) {
+            int mi, nj;
+            tile_coords(t, args.n_col_tiles, &mi, &nj);
+            const int row = mi * HT_M + q * 32 + lane;
+            for (int ch = 0; ch < n_chunks && ok; ++ch, ++unit) {
+                const uint32_t buf = unit & 1, use = unit >> 1;
+                ok = mbar_wait(tfull0 + 8 * buf, use & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * HT_N;
+#pragma unroll 1
+                for (int c0 = 0; c0 < HT_N; c0 += 32) {
+                    float v[32];
+                    tmem_ld32(taddr + c0, v);
+                    const int col = nj * HT_N + c0;
+                    // only columns at or right of this row's diagonal are ever read back
+                    if (row < args.C && col < args.C && col + 31 >= row) {
+                        float4* dst = reinterpret_cast<float4*>(args.S + (int64_t)row * args.C + col);
+                        float4 o[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) o[j] = dst[j];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            o[j].x = fmaf(v[4 * j + 0], scale, o[j].x); o[j].y = fmaf(v[4 * j + 1], scale, o[j].y);
+                            o[j].z = fmaf(v[4 * j + 2], scale, o[j].z); o[j].w = fmaf(v[4 * j + 3], scale, o[j].w);
+                            dst[j] = o[j];
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(args.status, CRB_FLAG_WAIT_LIMIT);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---- float32 input: amax, then split into two fp16 planes ------------------------------------
+__global__ void k_amax(const float* __restrict__ X, int64_t T, int C, int64_t ldx, unsigned* amax_bits) {
+    float m = 0.f;
+    const int64_t n = T * C;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const float v = fabsf(X[(i / C) * ldx + (i % C)]);
+        m = fmaxf(m, isfinite(v) ? v : 0.f);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(amax_bits, __float_as_uint(m));
+}
+
+// scale s = 2^e with amax * s in [2^13, 2^14); planes hi = fp16(x s), lo = fp16(x s - hi).
+__global__ void k_split_f32(const float* __restrict__ X, int64_t T, int C, int64_t ldx,
+                            const unsigned* __restrict__ amax_bits, __half* __restrict__ hi,
+                            __half* __restrict__ lo, float* __restrict__ inv_scale2) {
+    const float amax = __uint_as_float(*amax_bits);
+    int e = 0;
+    if (amax > 0.f) { int ex; frexpf(amax, &ex); e = 14 - ex; }     // amax = f * 2^ex, f in [0.5, 1)
+    e = max(-60, min(60, e));
+    const float s = ldexpf(1.0f, e);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *inv_scale2 = ldexpf(1.0f, -2 * e);
+    const int64_t n = T * C;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const float v = X[(i / C) * ldx + (i % C)] * s;
+        const __half h = __float2half_rn(v);
+        hi[i] = h;
+        lo[i] = __float2half_rn(v - __half2float(h));
+    }
+}
+
+// H = scale * S on and above the diagonal, mirrored below it.
+__global__ void k_hessian_finalize(float* __restrict__ S, int C, float scale) {
+    __shared__ float tile[32][33];
+    const int bi = blockIdx.y, bj = blockIdx.x;
+    if (bj < bi) return;
+    const int tx = threadIdx.x, ty = threadIdx.y;            // 32 x 8
+    for (int r = ty; r < 32; r += 8) {
+        const int i = bi * 32 + r, j = bj * 32 + tx;
+        float v = 0.f;
+        if (i < C && j < C) {
+            v = S[(int64_t)i * C + j] * scale;
+            if (j >= i) S[(int64_t)i * C + j] = v;
+        }
+        tile[r][tx] = v;
+    }
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8) {
+        const int i = bj * 32 + r, j = bi * 32 + tx;         // transposed position
+        if (i < C && j < C && j < i) S[(int64_t)i * C + j] = tile[tx][r];
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+static int make_map(CUtensorMap* map, const void* base, int dtype, int64_t T, int C, int64_t ld) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return CRB_ERR_LAUNCH;
+    const cuuint64_t dims[2] = {(cuuint64_t)C, (cuuint64_t)T};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {HT_BOX, HT_K};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType dt = (dtype == CRB_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? CRB_OK : CRB_ERR_BAD_ARG;
+}
+
+static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+// Tokens accumulated on the tensor cores before the running sum is folded into S by float32
+// adds (multiple of the 64-token stage).  CRB_HESSIAN_CHUNK overrides it for experiments.
+static int hessian_chunk_tokens() {
+    static int v = 0;
+    if (!v) {
+        v = 2048;
+        if (const char* e = getenv("CRB_HESSIAN_CHUNK")) {
+            const int x = atoi(e);
+            if (x >= HT_K && x % HT_K == 0) v = x;
+        }
+    }
+    return v;
+}
+
+size_t hessian_workspace_bytes(int C, int64_t T, int dtype) {
+    size_t b = 256;                                           // amax + inv_scale2 + status
+    if (dtype == CRB_F32) b += 2 * align256((size_t)T * C * sizeof(__half));
+    return b;
+}
+
+int hessian_accumulate_launch(const void* X, int dtype, int64_t T, int C, int64_t ldx, float* S,
+                              void* workspace, size_t workspace_bytes, cudaStream_t st) {
+    if (!X || !S || !workspace || T <= 0 || C <= 0 || ldx < C) return CRB_ERR_BAD_ARG;
+    if (C % kBlock) return CRB_ERR_UNSUPPORTED;
+    if (dtype != CRB_F32 && dtype != CRB_F16 && dtype != CRB_BF16) return CRB_ERR_BAD_ARG;
+    if (T >= (1ll << 31)) return CRB_ERR_UNSUPPORTED;
+    if (workspace_bytes < hessian_workspace_bytes(C, T, dtype)) return CRB_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(S) & 15) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255))
+        return CRB_ERR_BAD_ARG;
+    unsigned* status = static_cast<unsigned*>(workspace);          // word 0: sticky status flags
+    unsigned* amax = status + 1;
+    float* inv_scale2 = reinterpret_cast<float*>(status + 2);
+
+    CUtensorMap map0, map1;
+    HessArgs a;
+    a.S = S; a.status = status; a.C = C; a.T = T;
+    a.chunk_tokens = hessian_chunk_tokens();
+    a.n_col_tiles = (C + HT_N - 1) / HT_N;
+    {
+        int n = 0;
+        for (int h = 0; h < a.n_col_tiles; ++h) n += 2 * (a.n_col_tiles - h);
+        if ((C / HT_M) & 1) n -= (a.n_col_tiles - (C / HT_M) / 2);   // odd number of row tiles: last pair is half
+        a.n_tiles = n;
+    }
+    if (dtype == CRB_F32) {
+        if (ldx & 3) return CRB_ERR_BAD_ARG;
+        __half* hi = reinterpret_cast<__half*>(static_cast<char*>(workspace) + 256);
+        __half* lo = reinterpret_cast<__half*>(static_cast<char*>(workspace) + 256 + align256((size_t)T * C * sizeof(__half)));
+        if (cudaMemsetAsync(amax, 0, 8, st) != cudaSuccess) return CRB_ERR_LAUNCH;
+        k_amax<<<296, 256, 0, st>>>(static_cast<const float*>(X), T, C, ldx, amax);
+        CRB_LAUNCHED();
+        k_split_f32<<<592, 256, 0, st>>>(static_cast<const float*>(X), T, C, ldx, amax, hi, lo, inv_scale2);
+        CRB_LAUNCHED();
+        int rc = make_map(&map0, hi, CRB_F16, T, C, C);
+        if (rc == CRB_OK) rc = make_map(&map1, lo, CRB_F16, T, C, C);
+        if (rc != CRB_OK) return rc;
+        a.n_pass = 3; a.ab_format = 0; a.inv_scale2 = inv_scale2;
+    } else {
+        if (ldx & 7) return CRB_ERR_BAD_ARG;
+        int rc = make_map(&map0, X, dtype, T, C, ldx);
+        if (rc != CRB_OK) return rc;
+        map1 = map0;
+        a.n_pass = 1; a.ab_format = (dtype == CRB_BF16) ? 1 : 0; a.inv_scale2 = nullptr;
+    }
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(k_hessian_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, HT_SMEM) != cudaSuccess)
+            return CRB_ERR_LAUNCH;
+        attr_set = true;
+    }
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = a.n_tiles < sms ? a.n_tiles : sms;
+    k_hessian_umma<<<grid, HT_THREADS, HT_SMEM, st>>>(map0, map1, a);
+    CRB_LAUNCHED();
+    return CRB_OK;
+}
+
+int hessian_finalize_launch(float* S, int C, float scale, cudaStream_t st) {
+    if (!S || C <= 0) return CRB_ERR_BAD_ARG;
+    const int nb = (C + 31) / 32;
+    k_hessian_finalize<<<dim3(nb, nb), dim3(32, 8), 0, st>>>(S, C, scale);
+    CRB_LAUNCHED();
+    return CRB_OK;
+}
+
+}  // namespace crb

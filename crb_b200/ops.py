@@ -1,0 +1,202 @@
+"""Tensor-level wrappers around the C ABI (device tensors in, device tensors out).
+
+Every function here runs hand-written sm_100a kernels from libcrb_b200.so on the
+current CUDA stream.  There is no CPU or PyTorch fallback: a non-CUDA tensor or a
+missing library raises.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from . import _lib
+from ._lib import BLOCK, TRACE_DOUBLES, CrbError, check, lib, ptr, stream_ptr
+
+_workspaces: Dict[tuple, torch.Tensor] = {}
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise CrbError("crb_b200 runs on CUDA tensors only (no CPU fallback)")
+
+
+def _workspace(kind: str, nbytes: int, device) -> torch.Tensor:
+    """Zero-initialised, cached scratch buffer per (kind, device); grows on demand."""
+    key = (kind, torch.device(device).index)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def release_workspaces():
+    _workspaces.clear()
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    name = str(t.dtype).replace("torch.", "")
+    if name not in _lib.DTYPES:
+        raise CrbError(f"unsupported activation dtype {t.dtype}")
+    return _lib.DTYPES[name]
+
+
+# ------------------------------------------------------------------------------------------
+def hessian_accumulate(S: torch.Tensor, X: torch.Tensor) -> None:
+    """S += X^T X.  S [C, C] float32 (upper-triangle tiles are maintained), X [T, C]."""
+    _need_cuda(S, X)
+    if X.dim() != 2 or S.shape != (X.shape[1], X.shape[1]) or S.dtype != torch.float32:
+        raise CrbError("hessian_accumulate: X must be [T, C] and S [C, C] float32")
+    if X.stride(1) != 1:
+        X = X.contiguous()
+    if not S.is_contiguous():
+        raise CrbError("S must be contiguous")
+    T, Cc = X.shape
+    code = _dtype_code(X)
+    L = lib()
+    nbytes = L.crb_hessian_workspace_bytes(Cc, T, code)
+    ws = _workspace("hessian", nbytes, S.device)
+    check(L.crb_hessian_accumulate(ptr(X), code, T, Cc, X.stride(0), ptr(S), ptr(ws), ws.numel(),
+                                   stream_ptr()), "crb_hessian_accumulate")
+
+
+def hessian_finalize(S: torch.Tensor, scale: float) -> None:
+    """In place: H = scale * S, lower triangle mirrored from the upper one."""
+    _need_cuda(S)
+    check(lib().crb_hessian_finalize(ptr(S), S.shape[0], float(scale), stream_ptr()), "crb_hessian_finalize")
+
+
+def hessian_status(device) -> int:
+    ws = _workspaces.get(("hessian", torch.device(device).index))
+    return 0 if ws is None else lib().crb_read_status(ptr(ws), stream_ptr())
+
+
+def hinv_upper_factor(H: torch.Tensor, W: Optional[torch.Tensor], percdamp: float,
+                      max_retries: int = 10, restore=None) -> torch.Tensor:
+    """Dead-column fix, damping and U = chol(inv(H), upper), written over H (returned).
+
+    Mirrors bigptq.py:101-129 including the retry with extra damping: the device
+    factorisation reports a failed pivot through a status word, and the host then
+    rebuilds from the saved H with one more damping step, up to 10 times; after that
+    the diagonal fallback of bigptq.py:124-126 is used.  `restore(H)` refills H with the
+    undamped Hessian for a retry; without it a copy of H is kept for that purpose.
+    """
+    _need_cuda(H, W)
+    Cc = H.shape[0]
+    if H.dtype != torch.float32 or not H.is_contiguous() or H.shape != (Cc, Cc):
+        raise CrbError("H must be a contiguous [C, C] float32 tensor")
+    if W is not None and (W.dtype != torch.float32 or W.stride(1) != 1):
+        raise CrbError("W must be float32 with unit column stride")
+    L = lib()
+    ws = _workspace("factor", L.crb_factor_workspace_bytes(Cc), H.device)
+    status = torch.zeros(4, dtype=torch.int32, device=H.device)
+    saved = H.clone() if restore is None else None
+    diag0 = torch.diagonal(H).clone()
+    for attempt in range(max_retries + 1):
+        if attempt > 0:
+            if restore is None:
+                H.copy_(saved)
+            else:
+                restore(H)
+            status.zero_()
+        check(L.crb_hinv_upper_factor(ptr(H), Cc, ptr(W), 0 if W is None else W.shape[0],
+                                      0 if W is None else W.stride(0), float(percdamp), attempt,
+                                      ptr(ws), ws.numel(), ptr(status), stream_ptr()),
+              "crb_hinv_upper_factor")
+        if not (int(status[0].item()) & _lib.FLAG_BAD_PIVOT):
+            return H
+    # last resort (bigptq.py:124-126): H_chol = diag(sqrt(clamp(diag H, 1e-8))) -> U = diag(1/sqrt)
+    diag = diag0
+    diag[diag == 0] = 1
+    mean = diag.mean()
+    damp = percdamp * mean
+    mean = mean + damp
+    for _ in range(max_retries):
+        extra = 1e-3 * mean
+        damp = damp + extra
+        mean = mean + extra
+    H.zero_()
+    torch.diagonal(H).copy_(torch.rsqrt(torch.clamp(diag + damp, min=1e-8)))
+    return H
+
+
+def block_step(W: torch.Tensor, U: torch.Tensor, block: int, technique: str = "crb",
+               lam: float = 1e-5, corr_damp: float = 0.1, metric: str = "hessian",
+               losses: Optional[torch.Tensor] = None, want_codes: bool = True) -> dict:
+    """One 128-column block in place on W; returns Err, losses, codes, scales, trace."""
+    _need_cuda(W, U)
+    R = W.shape[0]
+    L = lib()
+    ws = _workspace("block", L.crb_block_workspace_bytes(R), W.device)
+    dev = W.device
+    Err = torch.empty(R, BLOCK, dtype=torch.float32, device=dev)
+    if losses is None:
+        losses = torch.zeros(R, dtype=torch.float32, device=dev)
+    codes = torch.zeros(R, BLOCK, dtype=torch.uint8, device=dev) if want_codes else None
+    scales = torch.zeros(R, 8, dtype=torch.float32, device=dev) if want_codes else None
+    trace = torch.zeros(TRACE_DOUBLES, dtype=torch.float64, device=dev)
+    check(L.crb_block_step(ptr(W), R, W.stride(0), ptr(U), U.stride(0), block,
+                           _lib.TECHNIQUES[technique], lam, corr_damp, _lib.METRICS[metric],
+                           ptr(Err), ptr(losses), ptr(codes), ptr(scales), ptr(trace), ptr(ws),
+                           ws.numel(), stream_ptr()), "crb_block_step")
+    return dict(Err=Err, losses=losses, codes=codes, scales=scales, trace=trace, workspace=ws)
+
+
+def binarize_group(w: torch.Tensor, mask: torch.Tensor, order: int, technique: str,
+                   lam: float = 1e-5, corr_damp: float = 0.1) -> torch.Tensor:
+    """Binarization.quantize on a [R, 128] block with an arbitrary boolean mask."""
+    _need_cuda(w, mask)
+    if w.dim() != 2 or w.shape[1] != BLOCK or mask.shape != w.shape:
+        raise CrbError(f"binarize_group works on [R, {BLOCK}] blocks")
+    wf = w.float().contiguous()
+    m8 = mask.to(torch.uint8).contiguous()
+    q = torch.empty_like(wf)
+    check(lib().crb_binarize_group(ptr(wf), wf.shape[0], wf.stride(0), ptr(m8), m8.stride(0), int(order),
+                                   _lib.TECHNIQUES[technique], lam, corr_damp, ptr(q), q.stride(0),
+                                   stream_ptr()), "crb_binarize_group")
+    return q.to(w.dtype)
+
+
+def trailing_update(W: torch.Tensor, Err: torch.Tensor, U: torch.Tensor, block: int) -> None:
+    """W[:, (block+1)*128:] -= Err @ U[block*128:(block+1)*128, (block+1)*128:]  (bigptq.py:264)."""
+    _need_cuda(W, Err, U)
+    check(lib().crb_trailing_update(ptr(W), W.shape[0], W.shape[1], W.stride(0), ptr(Err), ptr(U),
+                                    U.stride(0), block, stream_ptr()), "crb_trailing_update")
+
+
+def quantize_linear(W: torch.Tensor, U: torch.Tensor, technique: str = "crb", lam: float = 1e-5,
+                    corr_damp: float = 0.1, metric: str = "hessian", want_codes: bool = False,
+                    want_trace: bool = True) -> dict:
+    """The whole block loop of fasterquant on W [R, C] float32 in place, given U."""
+    _need_cuda(W, U)
+    R, Cc = W.shape
+    if W.dtype != torch.float32 or W.stride(1) != 1 or U.dtype != torch.float32 or U.stride(1) != 1:
+        raise CrbError("W and U must be float32 with unit column stride")
+    if Cc % BLOCK:
+        raise CrbError(f"in_features must be a multiple of {BLOCK}")
+    L = lib()
+    dev = W.device
+    ws = _workspace("linear", L.crb_linear_workspace_bytes(R), dev)
+    nblk = Cc // BLOCK
+    losses = torch.zeros(R, dtype=torch.float32, device=dev)
+    codes = torch.zeros(R, Cc, dtype=torch.uint8, device=dev) if want_codes else None
+    scales = torch.zeros(nblk, R, 8, dtype=torch.float32, device=dev) if want_codes else None
+    trace = torch.zeros(nblk, TRACE_DOUBLES, dtype=torch.float64, device=dev) if want_trace else None
+    check(L.crb_quantize_linear(ptr(W), R, Cc, W.stride(0), ptr(U), U.stride(0),
+                                _lib.TECHNIQUES[technique], lam, corr_damp, _lib.METRICS[metric],
+                                ptr(losses), ptr(codes), ptr(scales), ptr(trace), ptr(ws), ws.numel(),
+                                stream_ptr()), "crb_quantize_linear")
+    return dict(losses=losses, codes=codes, scales=scales, trace=trace, workspace=ws)
+
+
+def read_status(workspace: torch.Tensor) -> int:
+    rc = lib().crb_read_status(ptr(workspace), stream_ptr())
+    if rc < 0:
+        check(rc, "crb_read_status")
+    return rc
+
+
+def launch_count() -> int:
+    return int(lib().crb_launch_count())

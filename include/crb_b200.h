@@ -1,0 +1,141 @@
+/*
+ * crb_b200 -- C ABI of the B200 (sm_100a) implementation of the CRB / BiLLM
+ * calibration-time binarization path.
+ *
+ * Conventions
+ *   - every pointer named *_dev / documented "device" is a CUDA device pointer
+ *     on the current device; `stream` is a cudaStream_t passed as void*;
+ *   - matrices are row-major float32 unless a dtype argument says otherwise;
+ *   - all calls are asynchronous on `stream`, take caller-allocated workspace
+ *     and return a crbStatus (0 = ok, <0 = bad arguments / launch failure);
+ *     data-dependent conditions (non-finite input, failed pivot) are written
+ *     to a device status word that crb_read_status() copies back;
+ *   - the block width is fixed at 128 columns (the reference's --blocksize 128)
+ *     and the column count must be a multiple of 128.
+ *
+ * The reference has no FFI on this path; each entry point names the Python
+ * code of the reference that it replaces (paths inside the reference project).
+ */
+#ifndef CRB_B200_H
+#define CRB_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CRB_BLOCK 128          /* columns per block step                       */
+#define CRB_SALIENT_LIMIT 50   /* utils/structure.py:16 (up_lim)               */
+#define CRB_N_SPLITS 81        /* utils/autosearch.py:65                       */
+#define CRB_TRACE_DOUBLES 192  /* doubles per block in the search trace        */
+
+typedef enum {
+    CRB_OK = 0,
+    CRB_ERR_BAD_ARG = -1,
+    CRB_ERR_WORKSPACE = -2,    /* workspace too small                          */
+    CRB_ERR_LAUNCH = -3,       /* a CUDA launch / API call failed              */
+    CRB_ERR_UNSUPPORTED = -4   /* shape or option outside what is implemented  */
+} crbStatus;
+
+typedef enum { CRB_TECH_BRAQ = 0, CRB_TECH_CRBOG = 1, CRB_TECH_CRB = 2 } crbTechnique;
+typedef enum { CRB_METRIC_HESSIAN = 0, CRB_METRIC_MAGNITUDE = 1 } crbMetric;
+typedef enum { CRB_F32 = 0, CRB_F16 = 1, CRB_BF16 = 2 } crbDtype;
+
+/* bits of the device status word (crb_read_status) */
+#define CRB_FLAG_NONFINITE   1u   /* a non-finite metric / error was seen       */
+#define CRB_FLAG_BAD_PIVOT   2u   /* factorisation met a non-positive pivot     */
+#define CRB_FLAG_WAIT_LIMIT  4u   /* a bounded wait in a kernel ran out         */
+
+/* Layout of one block's search trace (CRB_TRACE_DOUBLES doubles):
+ *   [0] salient column count i*        [1] split index k*      [2] split value p*
+ *   [3] relative gap to the runner-up salient count            [4] same for the split
+ *   [5] mean squared error of the salient group (constant term of the split search)
+ *   [6..55]   the 50 highest-score columns, best first
+ *   [56..104] mean squared error of salient candidates i = 1..49
+ *   [105..185] mean squared error of split candidates k = 0..80
+ */
+
+int crb_version(void);
+/* compiled architecture string, e.g. "sm_100a" */
+const char *crb_arch(void);
+const char *crb_status_string(int status);
+
+/* ---- (1) Hessian accumulation --------------------------------------------------
+ * Replaces BRAGPTQ.add_batch (bigptq.py:37-54).  S += X^T X for X [T, C] (row
+ * major, leading dimension ldx elements) of dtype f16/bf16/f32, accumulated in
+ * float32.  S is the UNSCALED sum; crb_hessian_finalize applies 2/N once, which
+ * equals the reference's running rescale (bigptq.py:50-53) up to rounding.     */
+size_t crb_hessian_workspace_bytes(int C, int64_t T, int dtype);
+int crb_hessian_accumulate(const void *X_dev, int dtype, int64_t T, int C, int64_t ldx,
+                           float *S_dev, void *workspace_dev, size_t workspace_bytes,
+                           void *stream);
+/* H = scale * S, both triangles written (S holds the upper-triangle tiles). */
+int crb_hessian_finalize(float *S_dev, int C, float scale, void *stream);
+
+/* ---- (2) damping + inverse factor ----------------------------------------------
+ * Replaces bigptq.py:101-129: dead columns (diag == 0 -> H[d,d] = 1, W[:,d] = 0),
+ * H += percdamp * mean(diag) * I, then U = chol(inv(H), upper) written over H.
+ * `extra_damp_steps` >= 0 adds that many times 1e-3 * mean(diag) first (the
+ * reference's retry, bigptq.py:115-123, driven by the host after it reads
+ * CRB_FLAG_BAD_PIVOT).  W may be NULL.                                          */
+size_t crb_factor_workspace_bytes(int C);
+int crb_hinv_upper_factor(float *H_dev, int C, float *W_dev, int R, int64_t ldw, float percdamp,
+                          int extra_damp_steps, void *workspace_dev, size_t workspace_bytes,
+                          unsigned *status_dev, void *stream);
+
+/* ---- (3) block step -------------------------------------------------------------
+ * Replaces one iteration of the block loop, bigptq.py:142-263 with
+ * utils/structure.py:8-20, utils/autosearch.py:28-83, utils/mask.py:7-18 and the
+ * binarizers binary.py:18-39 (braq), :577-687 (crbog), :1544-1638 (crb).
+ *   W     [R, ldw]  in: current weights; out: columns of the block replaced by Q
+ *   U     [C, ldu]  upper factor; only diag of the block is read
+ *   Err   [R, 128]  out: (w - q) / d
+ *   Losses[R]       in/out: += sum_j (w - q)^2 / d^2 / 2
+ *   codes [R, 128]  optional (NULL): bits 0-1 B1+1, bits 2-3 B2+1, bits 4-5 group
+ *   scales[R, 8]    optional (NULL): per-row scales, see the Python docs
+ *   trace [192]     optional (NULL): doubles, layout above                       */
+size_t crb_block_workspace_bytes(int R);
+int crb_block_step(float *W_dev, int R, int64_t ldw, const float *U_dev, int64_t ldu, int block,
+                   int technique, float lam, float corr_damp, int metric, float *Err_dev,
+                   float *Losses_dev, uint8_t *codes_dev, float *scales_dev, double *trace_dev,
+                   void *workspace_dev, size_t workspace_bytes, void *stream);
+
+/* ---- group binarizer ---------------------------------------------------------------
+ * Replaces Binarization.quantize (binary.py:2868-2884) for braq / crbog / crb on one
+ * [R, 128] block: Q = binarizer(W on mask, order in {1, 2}), zero outside the mask.
+ * mask [R, ldm] bytes (non-zero = member).  The block step applies the same device
+ * code to its three groups; this entry point serves callers that bring their own mask. */
+int crb_binarize_group(const float *W_dev, int R, int64_t ldw, const uint8_t *mask_dev, int64_t ldm,
+                       int order, int technique, float lam, float corr_damp, float *Q_dev,
+                       int64_t ldq, void *stream);
+
+/* ---- (4) trailing update -------------------------------------------------------
+ * Replaces bigptq.py:264:  W[:, (block+1)*128:] -= Err @ U[block rows, (block+1)*128:]. */
+int crb_trailing_update(float *W_dev, int R, int C, int64_t ldw, const float *Err_dev,
+                        const float *U_dev, int64_t ldu, int block, void *stream);
+
+/* ---- whole linear ----------------------------------------------------------------
+ * The block loop of BRAGPTQ.fasterquant (bigptq.py:131-264) for all C/128 blocks:
+ * block step + trailing update, no host synchronisation.  Buffers as above;
+ * codes [R, C], scales [C/128, R, 8], trace [C/128, 192] are optional.
+ * Workspace: crb_linear_workspace_bytes(R).                                       */
+size_t crb_linear_workspace_bytes(int R);
+int crb_quantize_linear(float *W_dev, int R, int C, int64_t ldw, const float *U_dev, int64_t ldu,
+                        int technique, float lam, float corr_damp, int metric,
+                        float *Losses_dev, uint8_t *codes_dev, float *scales_dev,
+                        double *trace_dev, void *workspace_dev, size_t workspace_bytes,
+                        void *stream);
+
+/* Copies the status word at the start of a block/linear workspace to the host
+ * (synchronises `stream`).  Returns the flags (>= 0) or a negative crbStatus.    */
+int crb_read_status(const void *workspace_dev, void *stream);
+
+/* Number of kernels this library has launched since load (for launch accounting). */
+unsigned long long crb_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CRB_B200_H */
