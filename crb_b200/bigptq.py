@@ -51,6 +51,7 @@ class BRAGPTQ:
         self.last_flags = 0
         self.last_trace = None
         self.last_timing = {}
+        self.verbose = True         # the reference prints time and error per linear (bigptq.py:273-274)
 
     # ---- the Hessian as the reference exposes it ------------------------------------------
     @property
@@ -148,8 +149,9 @@ class BRAGPTQ:
         self.last_trace = out["trace"]
         self.last_flags = flags
         self.last_timing = {"factor_ms": ev[0].elapsed_time(ev[1]), "blocks_ms": ev[1].elapsed_time(ev[2])}
-        print("time %.2f" % (time.time() - tick))
-        print("error", error)
+        if self.verbose:
+            print("time %.2f" % (time.time() - tick))
+            print("error", error)
 
         if _Conv1D and isinstance(self.layer, _Conv1D):
             W = W.t()

@@ -172,8 +172,10 @@ def quantize_linear(W: torch.Tensor, U: torch.Tensor, technique: str = "crb", la
     """The whole block loop of fasterquant on W [R, C] float32 in place, given U."""
     _need_cuda(W, U)
     R, Cc = W.shape
-    if W.dtype != torch.float32 or W.stride(1) != 1 or U.dtype != torch.float32 or U.stride(1) != 1:
-        raise CrbError("W and U must be float32 with unit column stride")
+    if W.dtype != torch.float32 or W.stride(1) != 1 or U.dtype != torch.float32:
+        raise CrbError("W must be float32 with unit column stride and U float32")
+    if U.stride(1) != 1:
+        U = U.contiguous()
     if Cc % BLOCK:
         raise CrbError(f"in_features must be a multiple of {BLOCK}")
     L = lib()

@@ -1,0 +1,84 @@
+"""Sharding of the calibration path across the GPUs of one box (one process per GPU).
+
+Two independent splits, neither of which exists in the single-device reference:
+
+* calibration sequences are split across ranks; each rank accumulates an unscaled partial
+  S_r = sum X^T X over its sequences and the partials are summed with one all-reduce per
+  distinct layer input (H is a sum over sequences, bigptq.py:50-53);
+* the linears of a decoder layer are independent problems once their Hessians exist (all
+  hooks see the layer's original weights, run.py:341-353), so each linear is quantized by
+  one owner rank and the result is broadcast.
+
+Everything here is host logic on top of torch.distributed and is backend-agnostic (NCCL on
+GPUs, gloo in the CPU tests).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def world() -> Tuple[int, int]:
+    """(rank, world_size); (0, 1) outside a process group."""
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(), dist.get_world_size()
+    return 0, 1
+
+
+def shard_range(n: int, rank: int, world_size: int) -> range:
+    """Contiguous, balanced slice of range(n) owned by `rank` (first n % world ranks get one more)."""
+    base, extra = divmod(n, world_size)
+    start = rank * base + min(rank, extra)
+    return range(start, start + base + (1 if rank < extra else 0))
+
+
+def linear_cost(rows: int, cols: int) -> float:
+    """Relative cost of quantizing one linear: factorisation ~ cols^3, block loop ~ rows*cols."""
+    return (2.0 / 3.0) * cols ** 3 / 2.5e13 + rows * cols * 2.0e-9 + (cols / 128) * 6.0e-5
+
+
+def assign_owners(shapes: Dict[str, Tuple[int, int]], world_size: int) -> Dict[str, int]:
+    """Greedy longest-processing-time assignment of linears to ranks; deterministic on every rank."""
+    load = [0.0] * world_size
+    owners: Dict[str, int] = {}
+    for name in sorted(shapes, key=lambda n: (-linear_cost(*shapes[n]), n)):
+        r = min(range(world_size), key=lambda k: (load[k], k))
+        owners[name] = r
+        load[r] += linear_cost(*shapes[name])
+    return owners
+
+
+def allreduce_sum_(tensors: Sequence[torch.Tensor]) -> None:
+    """In-place sum over ranks of every tensor in the list (no-op for a single rank)."""
+    _, ws = world()
+    if ws == 1:
+        return
+    handles = [dist.all_reduce(t, op=dist.ReduceOp.SUM, async_op=True) for t in tensors]
+    for h in handles:
+        h.wait()
+
+
+def broadcast_(tensor: torch.Tensor, src: int) -> None:
+    _, ws = world()
+    if ws > 1:
+        dist.broadcast(tensor, src=src)
+
+
+def max_over_ranks(value: float, device) -> float:
+    _, ws = world()
+    if ws == 1:
+        return value
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(value: float, device) -> float:
+    _, ws = world()
+    if ws == 1:
+        return value
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())

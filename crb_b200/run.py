@@ -1,0 +1,409 @@
+"""Layer-by-layer calibration and binarization: the caller side of the hot path.
+
+Mirrors the reference's `run.py` for the techniques braq / crbog / crb:
+
+    python -m crb_b200.run MODEL DATASET {crb,crbog,braq} --blocksize 128 --salient_metric hessian
+
+* `quant_sequential(model, dataloader, dev, args)` follows run.py:122-387: capture the
+  inputs of layer 0, then per decoder layer hook every linear, run the calibration
+  sequences, quantize each linear with `BRAGPTQ.fasterquant`, re-propagate with the
+  quantized weights and hand the outputs to the next layer.
+* Differences that do not change results: the sequences are pushed through a layer in
+  batches (`--forward_batch`) instead of one by one; linears that receive the same input
+  tensor (q/k/v, gate/up) share one Hessian accumulator instead of computing it three times;
+  under torch.distributed (one process per GPU) every rank runs its share of the sequences,
+  the partial Hessians are summed with one all-reduce, each linear is quantized by one owner
+  rank and the quantized weights are broadcast.
+
+Checkpoints and datasets are not reachable offline: model names resolve to seeded
+random-init models of the same shape (`crb_b200.synth`) unless a local checkpoint directory
+is given, and the calibration set is uniform random token ids unless a cached loader file
+of the reference's format exists under $BILLM_DOWNLOADS_DIR.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import time
+from types import SimpleNamespace
+from typing import Dict, List, Optional
+
+import torch
+import torch.nn as nn
+
+from . import parallel
+from .bigptq import BRAGPTQ
+from .binary import Binarization
+from .synth import build_synthetic_model, resolve_shape, synthetic_calibration
+
+TECHNIQUES = ("braq", "crbog", "crb")
+
+
+def find_layers(module, layers=(nn.Conv2d, nn.Linear), name=""):
+    """All quantizable sub-modules of `module` by dotted name (modelutils.py:8-16)."""
+    if type(module) in layers:
+        return {name: module}
+    res = {}
+    for child_name, child in module.named_children():
+        res.update(find_layers(child, layers, name + "." + child_name if name else child_name))
+    return res
+
+
+def default_args(**overrides) -> SimpleNamespace:
+    """The reference's argparse defaults for this path (run.py:764-944)."""
+    a = SimpleNamespace(model="synthetic:opt-tiny", dataset="wikitext2", low_quant_method="crb",
+                        nsamples=128, seed=0, percdamp=0.01, blocksize=128, salient_metric="hessian",
+                        partition=3, global_scale=False, disable_gptq=False, minlayer=-1, maxlayer=1000,
+                        quant_only="", invert=False, corr_damp=0.1, lam=1e-5, coupling=0.5,
+                        device="cuda:0", seqlen=None, forward_batch=8, act_offload_gib=64.0, verbose=True)
+    for k, v in overrides.items():
+        setattr(a, k, v)
+    return a
+
+
+def get_model(model_name: str, fill_device: Optional[str] = None, n_layers: Optional[int] = None,
+              attn: str = "sdpa"):
+    """A local checkpoint directory is loaded as is; any other name gives the seeded random-init
+    model of that shape (run.py:19-71 downloads instead, which is impossible offline)."""
+    if os.path.isdir(model_name):
+        from transformers import AutoModelForCausalLM
+        model = AutoModelForCausalLM.from_pretrained(model_name, dtype="auto", local_files_only=True,
+                                                     attn_implementation=attn)
+        model.seqlen = min(model.config.max_position_embeddings, 2048)
+        model.eval()
+        return model
+    if resolve_shape(model_name) is None:
+        raise ValueError(f"{model_name!r} is neither a local checkpoint nor a known synthetic shape")
+    return build_synthetic_model(model_name, n_layers=n_layers, fill_device=fill_device, attn=attn)
+
+
+def get_loaders(name: str, nsamples: int, seed: int, seqlen: int, model, model_name: str = ""):
+    """The reference's cached calibration loader if one exists locally, else uniform token ids."""
+    downloads = os.environ.get("BILLM_DOWNLOADS_DIR", "./downloads")
+    cache = f"{downloads}/DOWNLOAD_{name}_{nsamples}_{seed}_{seqlen}_{model_name}.pt"
+    if os.path.exists(cache):
+        return torch.load(cache)
+    return synthetic_calibration(model.config.vocab_size, nsamples, seqlen, seed), None
+
+
+# ---------------------------------------------------------------------------------------------
+def _decoder_parts(model):
+    """(layers, modules that must sit on the device while layer-0 inputs are captured)."""
+    inner = model.model
+    if hasattr(inner, "decoder"):                                   # OPT (run.py:132-147)
+        dec = inner.decoder
+        pre = [dec.embed_tokens, dec.embed_positions]
+        for opt_name in ("project_in", "project_out"):
+            if getattr(dec, opt_name, None) is not None:
+                pre.append(getattr(dec, opt_name))
+        return dec.layers, pre
+    pre = [inner.embed_tokens, inner.norm]                          # Llama family (run.py:148-153)
+    if hasattr(inner, "rotary_emb"):
+        pre.append(inner.rotary_emb)
+    return inner.layers, pre
+
+
+class _Resident:
+    """Moves a module's parameters to the device and back without losing the pinned host copies."""
+
+    def __init__(self, module: nn.Module, dev):
+        self.module, self.dev, self.host = module, dev, {}
+
+    def __enter__(self):
+        for name, p in list(self.module.named_parameters()) + list(self.module.named_buffers()):
+            if p.device.type != "cuda":
+                self.host[name] = p.data
+                p.data = p.data.to(self.dev, non_blocking=True)
+        return self.module
+
+    def __exit__(self, *exc):
+        tensors = dict(list(self.module.named_parameters()) + list(self.module.named_buffers()))
+        for name, host in self.host.items():
+            p = tensors[name]
+            host.copy_(p.data, non_blocking=True)
+            p.data = host
+        torch.cuda.current_stream().synchronize()
+        self.host.clear()
+
+
+class _Catcher(nn.Module):
+    """Stands in for layer 0, records its input and keyword arguments, then aborts the forward
+    (run.py:175-201)."""
+
+    def __init__(self, module, sink):
+        super().__init__()
+        self.module, self.sink = module, sink
+
+    def __getattr__(self, name):
+        if name in ("module", "sink"):
+            return super().__getattr__(name)
+        try:
+            return super().__getattr__(name)
+        except AttributeError:
+            return getattr(self.module, name)
+
+    def forward(self, inp, **kwargs):
+        self.sink["inps"].append(inp)
+        self.sink["kwargs"] = kwargs
+        raise ValueError
+
+
+def _replay_kwargs(kwargs: dict, batch: int) -> dict:
+    """Layer keyword arguments captured with batch 1, widened to `batch` sequences."""
+    out = {}
+    for k, v in kwargs.items():
+        if k in ("past_key_values", "past_key_value", "use_cache"):
+            continue
+        if torch.is_tensor(v) and v.dim() >= 1 and v.shape[0] == 1 and batch > 1:
+            v = v.expand(batch, *v.shape[1:])
+        elif isinstance(v, tuple) and all(torch.is_tensor(t) for t in v):
+            v = tuple(t.expand(batch, *t.shape[1:]) if t.dim() >= 1 and t.shape[0] == 1 and batch > 1 else t
+                      for t in v)
+        out[k] = v
+    out["use_cache"] = False
+    return out
+
+
+def _layer_out(res):
+    return res[0] if isinstance(res, (tuple, list)) else res
+
+
+class _Timer:
+    def __init__(self):
+        self.ms: Dict[str, float] = {}
+        self._pending = []
+
+    def span(self, name):
+        timer = self
+
+        class _Span:
+            def __enter__(self):
+                self.a = torch.cuda.Event(enable_timing=True)
+                self.b = torch.cuda.Event(enable_timing=True)
+                self.a.record()
+
+            def __exit__(self, *exc):
+                self.b.record()
+                timer._pending.append((name, self.a, self.b))
+
+        return _Span()
+
+    def collect(self):
+        torch.cuda.synchronize()
+        for name, a, b in self._pending:
+            self.ms[name] = self.ms.get(name, 0.0) + a.elapsed_time(b)
+        self._pending.clear()
+        return self.ms
+
+
+@torch.no_grad()
+def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch.Tensor,
+                   layer_kwargs: dict, args, dev, timer: Optional[_Timer] = None) -> Dict[str, float]:
+    """One iteration of the layer loop (run.py:236-385) for a layer already on `dev`.
+
+    `inps` / `outs` hold this rank's sequences [n_local, seqlen, hidden] (device or pinned host).
+    Returns the per-linear `error` values (only the owner rank's are non-zero before the sum).
+    """
+    timer = timer or _Timer()
+    rank, ws = parallel.world()
+    subset = find_layers(layer)
+    gptq: Dict[str, BRAGPTQ] = {}
+    for name in subset:
+        if (not (args.minlayer <= index < args.maxlayer and args.quant_only in name)) == (not args.invert):
+            continue
+        quantizer = Binarization(subset[name].weight, method=args.low_quant_method, groupsize=args.blocksize,
+                                 corr_damp=args.corr_damp, lam=args.lam, coupling=args.coupling)
+        gptq[name] = BRAGPTQ(subset[name], quantizer, salient_metric=args.salient_metric,
+                             disable_gptq=args.disable_gptq)
+        gptq[name].verbose = bool(args.verbose)
+
+    # ---- pass 1: Hessians.  Linears fed by the very same tensor share one accumulator. ----
+    alias: Dict[str, str] = {}
+    seen: Dict[tuple, tuple] = {}
+
+    def make_hook(name):
+        def hook(_, inp, out):
+            x = inp[0].data
+            key = (x.data_ptr(), tuple(x.shape), x.dtype)
+            if name in alias:
+                return
+            if key in seen and seen[key][0] != name:
+                alias[name] = seen[key][0]
+                return
+            seen[key] = (name, x)              # keeps x alive so that its address stays unique
+            gptq[name].add_batch(x, out.data)
+        return hook
+
+    handles = [subset[name].register_forward_hook(make_hook(name)) for name in gptq]
+    n_local = inps.shape[0]
+    fb = max(1, int(args.forward_batch))
+    with timer.span("forward_hessian"):
+        for j in range(0, n_local, fb):
+            x = inps[j:j + fb].to(dev, non_blocking=True)
+            seen.clear()
+            layer(x, **_replay_kwargs(layer_kwargs, x.shape[0]))
+        seen.clear()
+    for h in handles:
+        h.remove()
+    leaders = [n for n in gptq if n not in alias]
+    with timer.span("hessian_allreduce"):
+        if ws > 1:
+            parallel.allreduce_sum_([gptq[n]._S for n in leaders])
+            total = int(parallel.sum_over_ranks(float(n_local), dev))
+            for n in leaders:
+                gptq[n].nsamples = total
+    for name, lead in alias.items():
+        gptq[name]._S = gptq[lead]._S
+        gptq[name].nsamples = gptq[lead].nsamples
+
+    # ---- quantization: each linear on its owner rank, result broadcast ----
+    shapes = {n: (gptq[n].rows, gptq[n].columns) for n in gptq}
+    owners = parallel.assign_owners(shapes, ws)
+    errors: Dict[str, float] = {}
+    with timer.span("fasterquant"):
+        for name in gptq:
+            if owners[name] == rank:
+                if args.verbose:
+                    print(index, name)
+                    print("Quantizing ...")
+                info = gptq[name].fasterquant(percdamp=args.percdamp, blocksize=args.blocksize,
+                                              partition=args.partition, global_scale=args.global_scale)
+                errors[name] = info["error"]
+                for k, v in gptq[name].last_timing.items():
+                    timer.ms[k] = timer.ms.get(k, 0.0) + v
+            else:
+                errors[name] = 0.0
+            gptq[name].free()
+    with timer.span("weight_broadcast"):
+        if ws > 1:
+            for name in gptq:
+                parallel.broadcast_(subset[name].weight.data, owners[name])
+
+    # ---- pass 2: re-propagate with the quantized weights (run.py:376-377) ----
+    with timer.span("forward_repropagate"):
+        for j in range(0, n_local, fb):
+            x = inps[j:j + fb].to(dev, non_blocking=True)
+            y = _layer_out(layer(x, **_replay_kwargs(layer_kwargs, x.shape[0])))
+            outs[j:j + fb].copy_(y.reshape(x.shape), non_blocking=True)
+    del gptq
+    return errors
+
+
+@torch.no_grad()
+def quant_sequential(model, dataloader, dev, args=None) -> dict:
+    """Calibrate and binarize every decoder layer in turn (run.py:122-387)."""
+    args = args or default_args()
+    args.low_quant_method = str(args.low_quant_method).lower()
+    if args.low_quant_method not in TECHNIQUES:
+        raise NotImplementedError(f"technique {args.low_quant_method!r}: implemented are {TECHNIQUES}")
+    dev = torch.device(dev)
+    rank, ws = parallel.world()
+    if args.verbose:
+        print("Starting ...")
+    use_cache = model.config.use_cache
+    model.config.use_cache = False
+    layers, pre = _decoder_parts(model)
+    dtype = next(iter(model.parameters())).dtype
+    hidden = model.config.hidden_size
+    batches = list(dataloader)[: args.nsamples]
+    mine = parallel.shard_range(len(batches), rank, ws)
+
+    # ---- capture the inputs of layer 0 for this rank's sequences (run.py:175-201) ----
+    sink = {"inps": [], "kwargs": {}}
+    residents = [_Resident(m, dev) for m in pre] + [_Resident(layers[0], dev)]
+    for r in residents:
+        r.__enter__()
+    layers[0] = _Catcher(layers[0], sink)
+    for j in mine:
+        try:
+            model(batches[j][0].to(dev))
+        except ValueError:
+            pass
+    layers[0] = layers[0].module
+    for r in reversed(residents):
+        r.__exit__()
+    n_local = len(sink["inps"])
+    act_bytes = n_local * model.seqlen * hidden * 2
+    on_host = act_bytes > args.act_offload_gib * (1024 ** 3)         # run.py:166-172 uses 8 GiB
+    kw = dict(dtype=dtype, device="cpu", pin_memory=True) if on_host else dict(dtype=dtype, device=dev)
+    inps = torch.zeros((n_local, model.seqlen, hidden), **kw)
+    for j, x in enumerate(sink["inps"]):
+        inps[j].copy_(x.reshape(model.seqlen, hidden))
+    outs = torch.zeros_like(inps, pin_memory=True) if on_host else torch.zeros_like(inps)
+    layer_kwargs = sink["kwargs"]
+    sink["inps"].clear()
+    if args.verbose:
+        print("Ready.")
+
+    timer = _Timer()
+    all_errors: List[Dict[str, float]] = []
+    t0 = time.time()
+    for i in range(len(layers)):
+        with _Resident(layers[i], dev) as layer:
+            errs = quantize_layer(layer, i, inps, outs, layer_kwargs, args, dev, timer)
+        all_errors.append(errs)
+        inps, outs = outs, inps
+    timing = timer.collect()
+    timing["wall_s"] = time.time() - t0
+    model.config.use_cache = use_cache
+    total = sum(sum(e.values()) for e in all_errors)
+    total = parallel.sum_over_ranks(total, dev)
+    return {"errors": all_errors, "error_sum": total, "timing_ms": timing, "final_hidden": inps}
+
+
+# ---------------------------------------------------------------------------------------------
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(description="CRB / BiLLM calibration-time binarization on B200")
+    p.add_argument("model", type=str, help="local checkpoint directory or a model name whose shape is known")
+    p.add_argument("dataset", type=str, choices=["wikitext2", "ptb", "c4"])
+    p.add_argument("low_quant_method", type=str.lower, choices=list(TECHNIQUES))
+    p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--nsamples", type=int, default=128)
+    p.add_argument("--seqlen", type=int, default=None)
+    p.add_argument("--percdamp", type=float, default=0.01)
+    p.add_argument("--blocksize", type=int, default=128)
+    p.add_argument("--salient_metric", type=str, default="magnitude", choices=["magnitude", "hessian"])
+    p.add_argument("--partition", type=int, default=3)
+    p.add_argument("--global_scale", action="store_true")
+    p.add_argument("--device", type=str, default="cuda:0")
+    p.add_argument("--disable_gptq", action="store_true")
+    p.add_argument("--minlayer", type=int, default=-1)
+    p.add_argument("--maxlayer", type=int, default=1000)
+    p.add_argument("--quant_only", type=str, default="")
+    p.add_argument("--invert", action="store_true")
+    p.add_argument("--corr_damp", type=float, default=0.1)
+    p.add_argument("--lam", type=float, default=1e-5)
+    p.add_argument("--coupling", type=float, default=0.5)
+    p.add_argument("--layers", type=int, default=None, help="synthetic models only: number of decoder layers")
+    p.add_argument("--forward_batch", type=int, default=8, help="sequences per layer forward")
+    p.add_argument("--act_offload_gib", type=float, default=64.0)
+    p.add_argument("--quiet", action="store_true")
+    return p
+
+
+def main(argv=None):
+    args = build_parser().parse_args(argv)
+    args.verbose = not args.quiet
+    if "RANK" in os.environ and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        import torch.distributed as dist
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        args.device = f"cuda:{local}"
+    rank, ws = parallel.world()
+    args.verbose = args.verbose and rank == 0
+    model = get_model(args.model, fill_device=args.device, n_layers=args.layers)
+    if args.seqlen:
+        model.seqlen = args.seqlen
+    loader, _ = get_loaders(args.dataset, args.nsamples, args.seed, model.seqlen, model, args.model)
+    tick = time.time()
+    out = quant_sequential(model, loader, args.device, args)
+    if rank == 0:
+        print("quantization time:", time.time() - tick, "s")
+        print("sum of block errors:", out["error_sum"])
+        print({k: round(v, 1) for k, v in out["timing_ms"].items()})
+    return out
+
+
+if __name__ == "__main__":
+    main()
