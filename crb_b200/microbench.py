@@ -1,0 +1,120 @@
+"""Times one entry point of the library on synthetic inputs of a chosen size.
+
+    python -m crb_b200.microbench hessian  --T 16384 --C 4096 [--dtype float16]
+    python -m crb_b200.microbench factor   --C 4096
+    python -m crb_b200.microbench block    --R 4096 --technique crb
+    python -m crb_b200.microbench trailing --R 4096 --C 4096
+    python -m crb_b200.microbench linear   --R 4096 --C 4096 --technique crb
+
+Each run does `--warmup` untimed and `--iters` timed calls bracketed by CUDA events on the
+launching stream and prints one JSON line with the time per call and the algorithmic
+throughput (bytes or flop per call as documented per subcommand).  Small sizes make these
+commands suitable for profiler captures.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import ops
+
+
+def _time(fn, warmup, iters, setup=None):
+    for _ in range(warmup):
+        if setup:
+            setup()
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if setup:
+            setup()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    return total / iters
+
+
+def _synthetic_factor(C, dev, seed=0):
+    """An upper factor with the structure the block loop sees: positive diagonal, small off-diagonal."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    U = torch.randn(C, C, generator=g, device=dev) * (0.02 / C ** 0.5)
+    U = torch.triu(U, 1)
+    U += torch.diag(0.5 + torch.rand(C, generator=g, device=dev))
+    return U.contiguous()
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["hessian", "factor", "block", "trailing", "linear"])
+    ap.add_argument("--R", type=int, default=4096)
+    ap.add_argument("--C", type=int, default=4096)
+    ap.add_argument("--T", type=int, default=16384)
+    ap.add_argument("--dtype", default="float16", choices=["float16", "bfloat16", "float32"])
+    ap.add_argument("--technique", default="crb", choices=["crb", "crbog", "braq"])
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--iters", type=int, default=5)
+    a = ap.parse_args(argv)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(1)
+    out = {"what": a.what, "R": a.R, "C": a.C, "T": a.T}
+    launches0 = ops.launch_count()
+
+    if a.what == "hessian":
+        X = torch.randn(a.T, a.C, generator=g, device=dev).to(getattr(torch, a.dtype))
+        S = torch.zeros(a.C, a.C, device=dev)
+        ms = _time(lambda: ops.hessian_accumulate(S, X), a.warmup, a.iters)
+        ncol = (a.C + 255) // 256
+        rows = a.C // 128
+        tiles = sum(2 * (ncol - h) for h in range(ncol)) - ((ncol - rows // 2) if rows % 2 else 0)
+        passes = 3 if a.dtype == "float32" else 1
+        issued = tiles * 128 * 256 * 2.0 * a.T * passes
+        out.update(ms=ms, dtype=a.dtype, tflops_issued=issued / ms / 1e9,
+                   tflops_full_product=2.0 * a.T * a.C * a.C / ms / 1e9,
+                   note="flop issued on upper-triangle 128x256 tiles; full product = 2*T*C^2")
+    elif a.what == "factor":
+        X = torch.randn(2 * a.C, a.C, generator=g, device=dev)
+        H0 = (X.t() @ X) / a.C
+        H = H0.clone()
+        ms = _time(lambda: ops.hinv_upper_factor(H, None, 0.01, restore=lambda h: h.copy_(H0)), a.warmup, a.iters,
+                   setup=lambda: H.copy_(H0))
+        out.update(ms=ms, gflops=(2.0 / 3.0) * a.C ** 3 / ms / 1e6,
+                   note="2*C^3/3 flop (one factorisation + one triangular inverse), includes the status read")
+    elif a.what == "block":
+        W = torch.randn(a.R, 256, generator=g, device=dev) * 0.02
+        U = _synthetic_factor(256, dev)
+        W0 = W.clone()
+        ms = _time(lambda: ops.block_step(W, U, 0, a.technique, want_codes=False), a.warmup, a.iters,
+                   setup=lambda: W.copy_(W0))
+        bytes_alg = 1536.0 * a.R + 65536
+        out.update(ms=ms, gbs=bytes_alg / ms / 1e6, technique=a.technique,
+                   note="algorithmic bytes per block = 1536*R + 64 KiB (read W block, write Q and Err, U block, losses)")
+    elif a.what == "trailing":
+        W = torch.randn(a.R, a.C, generator=g, device=dev)
+        Err = torch.randn(a.R, 128, generator=g, device=dev)
+        U = _synthetic_factor(a.C, dev)
+        ms = _time(lambda: ops.trailing_update(W, Err, U, 0), a.warmup, a.iters)
+        n = a.C - 128
+        out.update(ms=ms, tflops=2.0 * a.R * 128 * n / ms / 1e9, gbs=(8.0 * a.R * n + 4 * a.R * 128 + 4 * 128 * n) / ms / 1e6,
+                   note="first block of the loop: flop 2*R*128*(C-128); bytes read+write W[:,128:] + Err + U rows")
+    else:
+        W = torch.randn(a.R, a.C, generator=g, device=dev) * 0.02
+        U = _synthetic_factor(a.C, dev)
+        W0 = W.clone()
+        ms = _time(lambda: ops.quantize_linear(W, U, a.technique, want_trace=False), a.warmup, a.iters,
+                   setup=lambda: W.copy_(W0))
+        nblk = a.C // 128
+        out.update(ms=ms, ms_per_block=ms / nblk, technique=a.technique,
+                   block_gbs=(1536.0 * a.R + 65536) * nblk / ms / 1e6,
+                   note="whole block loop incl. trailing updates; block_gbs counts the block-step bytes only")
+    out["launches_per_call"] = (ops.launch_count() - launches0) / (a.warmup + a.iters)
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
