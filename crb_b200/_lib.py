@@ -36,6 +36,9 @@ SIGNATURES = {
     "crb_block_workspace_bytes": (_sz, [_i]),
     "crb_block_step": (_i, [_vp, _i, _i64, _vp, _i64, _i, _i, _f, _f, _i, _vp, _vp, _vp, _vp, _vp,
                             _vp, _sz, _vp]),
+    "crb_block_step_static_max_rows": (_i, []),
+    "crb_block_step_static": (_i, [_vp, _i, _i64, _vp, _i64, _i, _i, _f, _f, _i, _vp, _vp, _vp, _vp, _vp,
+                                   _vp, _vp]),
     "crb_binarize_group": (_i, [_vp, _i, _i64, _vp, _i64, _i, _i, _f, _f, _vp, _i64, _vp]),
     "crb_trailing_update": (_i, [_vp, _i, _i, _i64, _vp, _vp, _i64, _i, _vp]),
     "crb_linear_workspace_bytes": (_sz, [_i]),

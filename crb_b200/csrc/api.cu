@@ -49,6 +49,7 @@ const char* crb_status_string(int status) {
         case CRB_ERR_WORKSPACE: return "workspace too small";
         case CRB_ERR_LAUNCH: return "CUDA launch or API call failed";
         case CRB_ERR_UNSUPPORTED: return "unsupported shape or option";
+        case CRB_ERR_STATIC_LIMIT: return "row count exceeds the built-in scratch of crb_block_step_static";
         default: return status > 0 ? "device status flags" : "unknown error";
     }
 }

@@ -144,6 +144,26 @@ def block_step(W: torch.Tensor, U: torch.Tensor, block: int, technique: str = "c
     return dict(Err=Err, losses=losses, codes=codes, scales=scales, trace=trace, workspace=ws)
 
 
+def block_step_static(W: torch.Tensor, U: torch.Tensor, block: int, technique: str = "crb",
+                      lam: float = 1e-5, corr_damp: float = 0.1, metric: str = "hessian", *,
+                      Err: torch.Tensor, losses: torch.Tensor, codes: Optional[torch.Tensor] = None,
+                      scales: Optional[torch.Tensor] = None, trace: Optional[torch.Tensor] = None,
+                      flags: Optional[torch.Tensor] = None) -> None:
+    """`block_step` for callers that may not allocate: every buffer, outputs included, is passed
+    in, and the scratch memory is the library's built-in array (at most
+    `crb_block_step_static_max_rows()` rows; calls on one device must not overlap)."""
+    _need_cuda(W, U, Err, losses)
+    R = W.shape[0]
+    L = lib()
+    limit = L.crb_block_step_static_max_rows()
+    if R > limit:
+        raise CrbError(f"block_step_static serves at most {limit} rows per call, got {R}")
+    check(L.crb_block_step_static(ptr(W), R, W.stride(0), ptr(U), U.stride(0), block,
+                                  _lib.TECHNIQUES[technique], lam, corr_damp, _lib.METRICS[metric],
+                                  ptr(Err), ptr(losses), ptr(codes), ptr(scales), ptr(trace), ptr(flags),
+                                  stream_ptr()), "crb_block_step_static")
+
+
 def binarize_group(w: torch.Tensor, mask: torch.Tensor, order: int, technique: str,
                    lam: float = 1e-5, corr_damp: float = 0.1) -> torch.Tensor:
     """Binarization.quantize on a [R, 128] block with an arbitrary boolean mask."""

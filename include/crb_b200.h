@@ -36,7 +36,8 @@ typedef enum {
     CRB_ERR_BAD_ARG = -1,
     CRB_ERR_WORKSPACE = -2,    /* workspace too small                          */
     CRB_ERR_LAUNCH = -3,       /* a CUDA launch / API call failed              */
-    CRB_ERR_UNSUPPORTED = -4   /* shape or option outside what is implemented  */
+    CRB_ERR_UNSUPPORTED = -4,  /* shape or option outside what is implemented  */
+    CRB_ERR_STATIC_LIMIT = -5  /* more rows than the built-in scratch can serve */
 } crbStatus;
 
 typedef enum { CRB_TECH_BRAQ = 0, CRB_TECH_CRBOG = 1, CRB_TECH_CRB = 2 } crbTechnique;
@@ -101,6 +102,27 @@ int crb_block_step(float *W_dev, int R, int64_t ldw, const float *U_dev, int64_t
                    int technique, float lam, float corr_damp, int metric, float *Err_dev,
                    float *Losses_dev, uint8_t *codes_dev, float *scales_dev, double *trace_dev,
                    void *workspace_dev, size_t workspace_bytes, void *stream);
+
+/* ---- block step without a workspace ----------------------------------------------------
+ * No counterpart in the reference: an addition for callers that cannot allocate device
+ * memory when they need a block step (an operator hook inside a framework that owns the
+ * whole GPU through its own memory pool; a latency-critical loop that cannot take the
+ * device-wide synchronisation of cudaMalloc / cudaFree).  Same arithmetic, arguments and
+ * outputs as crb_block_step, but the scratch memory is an array inside the library image
+ * (9 MiB on every GPU that loads the library) instead of a caller workspace, and the call
+ * performs no allocation of any kind.
+ *   - R <= CRB_STATIC_MAX_ROWS, otherwise CRB_ERR_STATIC_LIMIT and nothing is launched;
+ *   - flags_out (optional, device): receives this call's status flags (CRB_FLAG_*);
+ *   - all calls on one device share the array: calls that overlap on the GPU race, so order
+ *     them on one stream (or with events);
+ *   - the first call on each device looks up the array's device address; make that call
+ *     before starting any stream capture.                                                   */
+#define CRB_STATIC_MAX_ROWS 16384
+int crb_block_step_static_max_rows(void);
+int crb_block_step_static(float *W_dev, int R, int64_t ldw, const float *U_dev, int64_t ldu, int block,
+                          int technique, float lam, float corr_damp, int metric, float *Err_dev,
+                          float *Losses_dev, uint8_t *codes_dev, float *scales_dev, double *trace_dev,
+                          unsigned *flags_out_dev, void *stream);
 
 /* ---- group binarizer ---------------------------------------------------------------
  * Replaces Binarization.quantize (binary.py:2868-2884) for braq / crbog / crb on one
