@@ -110,6 +110,8 @@ class _Resident:
         self.module, self.dev, self.host = module, dev, {}
 
     def __enter__(self):
+        if torch.device(self.dev).type != "cuda":
+            return self.module
         for name, p in list(self.module.named_parameters()) + list(self.module.named_buffers()):
             if p.device.type != "cuda":
                 self.host[name] = p.data
@@ -122,7 +124,8 @@ class _Resident:
             p = tensors[name]
             host.copy_(p.data, non_blocking=True)
             p.data = host
-        torch.cuda.current_stream().synchronize()
+        if self.host:
+            torch.cuda.current_stream().synchronize()
         self.host.clear()
 
 
@@ -169,27 +172,37 @@ def _layer_out(res):
 
 
 class _Timer:
+    """Per-phase device time (CUDA events on the current stream; host clock without CUDA)."""
+
     def __init__(self):
         self.ms: Dict[str, float] = {}
         self._pending = []
+        self.cuda = torch.cuda.is_available()
 
     def span(self, name):
         timer = self
 
         class _Span:
             def __enter__(self):
-                self.a = torch.cuda.Event(enable_timing=True)
-                self.b = torch.cuda.Event(enable_timing=True)
-                self.a.record()
+                if timer.cuda:
+                    self.a = torch.cuda.Event(enable_timing=True)
+                    self.b = torch.cuda.Event(enable_timing=True)
+                    self.a.record()
+                else:
+                    self.t0 = time.perf_counter()
 
             def __exit__(self, *exc):
-                self.b.record()
-                timer._pending.append((name, self.a, self.b))
+                if timer.cuda:
+                    self.b.record()
+                    timer._pending.append((name, self.a, self.b))
+                else:
+                    timer.ms[name] = timer.ms.get(name, 0.0) + (time.perf_counter() - self.t0) * 1e3
 
         return _Span()
 
     def collect(self):
-        torch.cuda.synchronize()
+        if self.cuda:
+            torch.cuda.synchronize()
         for name, a, b in self._pending:
             self.ms[name] = self.ms.get(name, 0.0) + a.elapsed_time(b)
         self._pending.clear()
@@ -220,10 +233,15 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
     # ---- pass 1: Hessians.  Linears fed by the very same tensor share one accumulator. ----
     alias: Dict[str, str] = {}
     seen: Dict[tuple, tuple] = {}
+    cur = {"batch": 1}
 
     def make_hook(name):
         def hook(_, inp, out):
             x = inp[0].data
+            if x.dim() == 2 and cur["batch"] > 1:
+                # some layers flatten [batch, tokens, C] before their linears (OPT fc1 / fc2); the
+                # sample count of add_batch is the number of sequences (bigptq.py:41-49)
+                x = x.reshape(cur["batch"], -1, x.shape[-1])
             key = (x.data_ptr(), tuple(x.shape), x.dtype)
             if name in alias:
                 return
@@ -241,6 +259,7 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
         for j in range(0, n_local, fb):
             x = inps[j:j + fb].to(dev, non_blocking=True)
             seen.clear()
+            cur["batch"] = x.shape[0]
             layer(x, **_replay_kwargs(layer_kwargs, x.shape[0]))
         seen.clear()
     for h in handles:
@@ -325,11 +344,12 @@ def quant_sequential(model, dataloader, dev, args=None) -> dict:
     n_local = len(sink["inps"])
     act_bytes = n_local * model.seqlen * hidden * 2
     on_host = act_bytes > args.act_offload_gib * (1024 ** 3)         # run.py:166-172 uses 8 GiB
-    kw = dict(dtype=dtype, device="cpu", pin_memory=True) if on_host else dict(dtype=dtype, device=dev)
+    pin = on_host and torch.cuda.is_available()
+    kw = dict(dtype=dtype, device="cpu", pin_memory=pin) if on_host else dict(dtype=dtype, device=dev)
     inps = torch.zeros((n_local, model.seqlen, hidden), **kw)
     for j, x in enumerate(sink["inps"]):
         inps[j].copy_(x.reshape(model.seqlen, hidden))
-    outs = torch.zeros_like(inps, pin_memory=True) if on_host else torch.zeros_like(inps)
+    outs = torch.zeros((n_local, model.seqlen, hidden), **kw)
     layer_kwargs = sink["kwargs"]
     sink["inps"].clear()
     if args.verbose:
