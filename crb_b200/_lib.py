@@ -41,6 +41,7 @@ SIGNATURES = {
                                    _vp, _vp]),
     "crb_binarize_group": (_i, [_vp, _i, _i64, _vp, _i64, _i, _i, _f, _f, _vp, _i64, _vp]),
     "crb_trailing_update": (_i, [_vp, _i, _i, _i64, _vp, _vp, _i64, _i, _vp]),
+    "crb_gemm_f32": (_i, [_i, _i, _i, _i, _i, _f, _vp, _i64, _vp, _i64, _f, _vp, _i64, _vp, _vp]),
     "crb_linear_workspace_bytes": (_sz, [_i]),
     "crb_quantize_linear": (_i, [_vp, _i, _i, _i64, _vp, _i64, _i, _f, _f, _i, _vp, _vp, _vp, _vp,
                                  _vp, _sz, _vp]),

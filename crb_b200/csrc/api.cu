@@ -16,10 +16,10 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
 int binarize_group_launch(const float* W, int R, int64_t ldw, const unsigned char* mask, int64_t ldm,
                           int order, int technique, float lam, float corr_damp, float* Q, int64_t ldq,
                           cudaStream_t st);
-// gemm_simt.cu
-int sgemm(bool trans_b, bool lower_only, int M, int N, int K, float alpha, const float* A,
-          int64_t lda, const float* B, int64_t ldb, float beta, float* C, int64_t ldc,
-          cudaStream_t st);
+// gemm_tc.cu
+int gemm_tf32x3(bool b_is_nk, bool lower_only, int M, int N, int K, float alpha, const float* A, int64_t lda,
+                const float* B, int64_t ldb, float beta, float* C, int64_t ldc, unsigned* status,
+                cudaStream_t st);
 // hessian.cu
 size_t hessian_workspace_bytes(int C, int64_t T, int dtype);
 int hessian_accumulate_launch(const void* X, int dtype, int64_t T, int C, int64_t ldx, float* S,
@@ -97,14 +97,25 @@ int crb_binarize_group(const float* W, int R, int64_t ldw, const uint8_t* mask, 
                                  static_cast<cudaStream_t>(stream));
 }
 
-int crb_trailing_update(float* W, int R, int C, int64_t ldw, const float* Err, const float* U,
-                        int64_t ldu, int block, void* stream) {
+static int trailing_update_impl(float* W, int R, int C, int64_t ldw, const float* Err, const float* U,
+                                int64_t ldu, int block, unsigned* status, cudaStream_t st) {
     if (!W || !Err || !U || R <= 0 || C <= 0 || (C % kBlock) || block < 0) return CRB_ERR_BAD_ARG;
     const int ed = (block + 1) * kBlock;
     if (ed > C) return CRB_ERR_BAD_ARG;
     if (ed == C) return CRB_OK;
-    return sgemm(false, false, R, C - ed, kBlock, -1.0f, Err, kBlock, U + (int64_t)block * kBlock * ldu + ed,
-                 ldu, 1.0f, W + ed, ldw, static_cast<cudaStream_t>(stream));
+    return gemm_tf32x3(false, false, R, C - ed, kBlock, -1.0f, Err, kBlock, U + (int64_t)block * kBlock * ldu + ed,
+                       ldu, 1.0f, W + ed, ldw, status, st);
+}
+
+int crb_trailing_update(float* W, int R, int C, int64_t ldw, const float* Err, const float* U,
+                        int64_t ldu, int block, void* stream) {
+    return trailing_update_impl(W, R, C, ldw, Err, U, ldu, block, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int crb_gemm_f32(int b_is_nk, int lower_only, int M, int N, int K, float alpha, const float* A, int64_t lda,
+                 const float* B, int64_t ldb, float beta, float* C, int64_t ldc, unsigned* status, void* stream) {
+    return gemm_tf32x3(b_is_nk != 0, lower_only != 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, status,
+                       static_cast<cudaStream_t>(stream));
 }
 
 size_t crb_linear_workspace_bytes(int R) {
@@ -129,7 +140,7 @@ int crb_quantize_linear(float* W, int R, int C, int64_t ldw, const float* U, int
                                    C, scales ? scales + (size_t)b * R * 8 : nullptr,
                                    trace ? trace + (size_t)b * CRB_TRACE_DOUBLES : nullptr, workspace, bws, st);
         if (rc != CRB_OK) return rc;
-        rc = crb_trailing_update(W, R, C, ldw, Err, U, ldu, b, stream);
+        rc = trailing_update_impl(W, R, C, ldw, Err, U, ldu, b, static_cast<unsigned*>(workspace), st);
         if (rc != CRB_OK) return rc;
     }
     return CRB_OK;

@@ -10,7 +10,7 @@
 //
 // Blocked with 128-wide panels.  Per panel: one CTA factors the 128x128 diagonal block in
 // shared memory and inverts it; the panel below is multiplied by that inverse and the trailing
-// matrix gets a rank-128 update, both through the float32 GEMM.  The triangular inverse
+// matrix gets a rank-128 update, both through the split-TF32 tensor-core GEMM (gemm_tc.cu).  The triangular inverse
 // merges neighbouring diagonal blocks recursively: [[A,0],[B,D]]^-1 = [[A^-1,0],[-D^-1 B A^-1, D^-1]].
 // A non-positive pivot sets CRB_FLAG_BAD_PIVOT (the host re-damps and calls again, like the
 // retry loop at bigptq.py:115-123) and is replaced by 1 so that nothing non-finite spreads.
@@ -18,9 +18,9 @@
 
 namespace crb {
 
-int sgemm(bool trans_b, bool lower_only, int M, int N, int K, float alpha, const float* A,
-          int64_t lda, const float* B, int64_t ldb, float beta, float* C, int64_t ldc,
-          cudaStream_t st);
+int gemm_tf32x3(bool b_is_nk, bool lower_only, int M, int N, int K, float alpha, const float* A, int64_t lda,
+                const float* B, int64_t ldb, float beta, float* C, int64_t ldc, unsigned* status,
+                cudaStream_t st);
 
 constexpr int FB = 128;    // panel width
 
@@ -78,49 +78,64 @@ __global__ void k_reverse_copy(const float* __restrict__ H, int C, const float* 
     A[(int64_t)i * C + j] = v;
 }
 
-// Factor one 128x128 diagonal block (lower Cholesky, left-looking, one thread per row) and
-// overwrite it with the inverse of its factor (zeros above the diagonal).
-__global__ void __launch_bounds__(FB)
+// Factor one 128x128 diagonal block (lower Cholesky, left-looking) and overwrite it with the
+// inverse of its factor (zeros above the diagonal).  512 threads: four lanes share a row (or a
+// column of the inverse) and split every dot product four ways, so that the serial chain per
+// column is a quarter of the row length plus two shuffles.
+constexpr int kDiagThreads = 4 * FB;
+
+__device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    return v;
+}
+
+__global__ void __launch_bounds__(kDiagThreads)
 k_chol_diag(float* __restrict__ Akk, int64_t ld, unsigned* status) {
     extern __shared__ float s_diag[];
     float (*a)[FB + 1] = reinterpret_cast<float (*)[FB + 1]>(s_diag);
     float (*x)[FB + 1] = reinterpret_cast<float (*)[FB + 1]>(s_diag + FB * (FB + 1));
-    const int i = threadIdx.x;
-    for (int j = 0; j < FB; ++j) a[j][i] = Akk[(int64_t)j * ld + i];    // coalesced: row j, column i
+    const int tid = threadIdx.x;
+    const int i = tid >> 2, s = tid & 3;               // row (phase 1) / column (phase 2), quarter
+    for (int e = tid; e < FB * FB; e += kDiagThreads) a[e >> 7][e & 127] = Akk[(int64_t)(e >> 7) * ld + (e & 127)];
     __syncthreads();
     bool bad = false;
     for (int k = 0; k < FB; ++k) {
-        // column k: a[i][k] -= sum_{j<k} a[i][j] * a[k][j]  for i >= k
-        float acc = a[i][k];
-        if (i >= k)
-            for (int j = 0; j < k; ++j) acc = fmaf(-a[i][j], a[k][j], acc);
-        __syncthreads();
-        if (i == k) {
-            if (!(acc > 0.f) || !isfinite(acc)) { bad = true; acc = 1.f; }
-            a[k][k] = sqrtf(acc);
+        // column k: acc = a[i][k] - sum_{j<k} a[i][j] * a[k][j]   for rows i >= k
+        float p0 = 0.f, p1 = 0.f;
+        if (i >= k) {
+            int j = s;
+            for (; j + 4 < k; j += 8) {
+                p0 = fmaf(a[i][j], a[k][j], p0);
+                p1 = fmaf(a[i][j + 4], a[k][j + 4], p1);
+            }
+            if (j < k) p0 = fmaf(a[i][j], a[k][j], p0);
+        }
+        const float acc = a[i][k] - quad_sum(p0 + p1);
+        if (i == k && s == 0) {
+            float piv = acc;
+            if (!(piv > 0.f) || !isfinite(piv)) { bad = true; piv = 1.f; }
+            a[k][k] = sqrtf(piv);
         }
         __syncthreads();
-        if (i > k) a[i][k] = __fdiv_rn(acc, a[k][k]);
+        if (i > k && s == 0) a[i][k] = __fdiv_rn(acc, a[k][k]);
         __syncthreads();
     }
     if (bad) atomicOr(status, CRB_FLAG_BAD_PIVOT);
-    // inverse of the lower factor, one thread per column j: forward substitution
-    const int j = threadIdx.x;
+    // inverse of the lower factor by forward substitution, column j = tid / 4:
+    //   x[r][j] = (delta_rj - sum_{m=j}^{r-1} a[r][m] x[m][j]) / a[r][r]
+    // rows are produced in order; the four lanes of a column split the sum over m.
+    const int j = i;
     for (int r = 0; r < FB; ++r) {
-        float v;
-        if (r < j) {
-            v = 0.f;
-        } else if (r == j) {
-            v = __fdiv_rn(1.f, a[r][r]);
-        } else {
-            float acc = 0.f;
-            for (int m = j; m < r; ++m) acc = fmaf(a[r][m], x[m][j], acc);
-            v = __fdiv_rn(-acc, a[r][r]);
-        }
-        x[r][j] = v;
+        float p = 0.f;
+        if (r > j)
+            for (int m = j + s; m < r; m += 4) p = fmaf(a[r][m], x[m][j], p);
+        p = quad_sum(p);
+        if (s == 0) x[r][j] = (r < j) ? 0.f : ((r == j) ? __fdiv_rn(1.f, a[r][r]) : __fdiv_rn(-p, a[r][r]));
+        __syncwarp();
     }
     __syncthreads();
-    for (int r = 0; r < FB; ++r) Akk[(int64_t)r * ld + i] = x[r][i];
+    for (int e = tid; e < FB * FB; e += kDiagThreads) Akk[(int64_t)(e >> 7) * ld + (e & 127)] = x[e >> 7][e & 127];
 }
 
 // U = index-reversed copy of the lower-triangular X (upper triangle and diagonal; zeros below).
@@ -138,20 +153,20 @@ size_t factor_workspace_bytes(int C) {
     return align256(sizeof(float) * (size_t)C * C) + 256 + align256((size_t)C);
 }
 
-static int invert_range(float* A, int C, int lo, int hi, float* tmp, cudaStream_t st) {
+static int invert_range(float* A, int C, int lo, int hi, float* tmp, unsigned* status, cudaStream_t st) {
     if (hi - lo <= 1) return CRB_OK;
     const int mid = lo + (hi - lo) / 2;
-    int rc = invert_range(A, C, lo, mid, tmp, st);
+    int rc = invert_range(A, C, lo, mid, tmp, status, st);
     if (rc != CRB_OK) return rc;
-    rc = invert_range(A, C, mid, hi, tmp, st);
+    rc = invert_range(A, C, mid, hi, tmp, status, st);
     if (rc != CRB_OK) return rc;
     const int s1 = (mid - lo) * FB, s2 = (hi - mid) * FB;
     float* B = A + (int64_t)mid * FB * C + (int64_t)lo * FB;
     const float* Ainv = A + (int64_t)lo * FB * (C + 1);
     const float* Dinv = A + (int64_t)mid * FB * (C + 1);
-    rc = sgemm(false, false, s2, s1, s1, 1.0f, B, C, Ainv, C, 0.0f, tmp, s1, st);          // T = B A^-1
+    rc = gemm_tf32x3(false, false, s2, s1, s1, 1.0f, B, C, Ainv, C, 0.0f, tmp, s1, status, st);      // T = B A^-1
     if (rc != CRB_OK) return rc;
-    return sgemm(false, false, s2, s1, s2, -1.0f, Dinv, C, tmp, s1, 0.0f, B, C, st);        // B = -D^-1 T
+    return gemm_tf32x3(false, false, s2, s1, s2, -1.0f, Dinv, C, tmp, s1, 0.0f, B, C, status, st);   // B = -D^-1 T
 }
 
 int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp, int extra_steps,
@@ -184,17 +199,17 @@ int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
     }
     for (int k = 0; k < nb; ++k) {
         float* Akk = A + (int64_t)k * FB * (C + 1);
-        k_chol_diag<<<1, FB, kDiagSmem, st>>>(Akk, C, status);
+        k_chol_diag<<<1, kDiagThreads, kDiagSmem, st>>>(Akk, C, status);
         CRB_LAUNCHED();
         const int rem = C - (k + 1) * FB;
         if (rem <= 0) break;
         float* panel = Akk + (int64_t)FB * C;
-        int rc = sgemm(true, false, rem, FB, FB, 1.0f, panel, C, Akk, C, 0.0f, panel, C, st);   // P = A21 L^-T
+        int rc = gemm_tf32x3(true, false, rem, FB, FB, 1.0f, panel, C, Akk, C, 0.0f, panel, C, status, st);   // P = A21 L^-T
         if (rc != CRB_OK) return rc;
-        rc = sgemm(true, true, rem, rem, FB, -1.0f, panel, C, panel, C, 1.0f, panel + FB, C, st);  // A22 -= P P^T
+        rc = gemm_tf32x3(true, true, rem, rem, FB, -1.0f, panel, C, panel, C, 1.0f, panel + FB, C, status, st);  // A22 -= P P^T
         if (rc != CRB_OK) return rc;
     }
-    int rc = invert_range(A, C, 0, nb, H, st);          // H is free to serve as scratch now
+    int rc = invert_range(A, C, 0, nb, H, status, st);          // H is free to serve as scratch now
     if (rc != CRB_OK) return rc;
     k_reverse_upper<<<dim3((C + 255) / 256, C), 256, 0, st>>>(A, C, H);
     CRB_LAUNCHED();

@@ -1,0 +1,323 @@
+// float32-faithful GEMM on the tensor cores:  C = alpha * A * op(B) + beta * C,  all float32.
+//
+// The reference multiplies in full float32 (TF32 is switched off, bigptq.py:11-12), so a plain
+// TF32 product (10-bit mantissa) would not do.  Every operand tile is split in shared memory
+// into hi = x with the low 13 mantissa bits cleared (exactly a TF32 number) and lo = x - hi
+// (exact in float32), and three tcgen05.mma kind::tf32 products hi*hi + hi*lo + lo*hi are
+// accumulated in float32 in TMEM: 21-22 significand bits per product, float32 accumulation.
+//
+// Used by the trailing update W[:, i2:] -= Err @ U[i1:i2, i2:] (bigptq.py:264) and by the
+// panel / rank-128 / inverse-merge products of the blocked factorisation.
+//
+// One persistent CTA per SM over 128 x 256 output tiles.  Warp roles: warp 0 TMA producer
+// (float32 tiles, 128-byte swizzle), warp 1 MMA issuer (owns TMEM), warps 2-5 split the
+// landed tiles into hi / lo in place, warps 6-9 epilogue (TMEM -> registers -> C).  Two
+// shared-memory stages of K = 32, two 256-column TMEM accumulators.  A is [M, K] row-major
+// (K-major operand); B is [N, K] row-major (K-major) or [K, N] row-major (MN-major operand).
+// All mbarrier waits are bounded (2 s); on expiry CRB_FLAG_WAIT_LIMIT is raised and the kernel
+// drains and returns.
+#include "common.cuh"
+#include "umma.cuh"
+
+namespace crb {
+
+constexpr int GT_M = 128, GT_N = 256, GT_K = 32;          // K = 32 float32 = one 128-byte swizzle row
+constexpr int GT_STAGES = 2;
+constexpr int GT_A_BYTES = GT_M * GT_K * 4;                 // 16 KiB
+constexpr int GT_B_BYTES = GT_N * GT_K * 4;                 // 32 KiB
+constexpr int GT_RAW_BYTES = GT_A_BYTES + GT_B_BYTES;       // 48 KiB: hi planes (TMA destination)
+constexpr int GT_STAGE_BYTES = 2 * GT_RAW_BYTES;            // + lo planes
+constexpr int GT_SMEM = GT_STAGES * GT_STAGE_BYTES + 1024 + 256;
+constexpr int GT_THREADS = 320;
+
+struct GemmArgs {
+    float* C;
+    int64_t ldc;
+    int M, N, K;
+    float alpha, beta;
+    int b_is_nk;          // 1: B is [N, K] row-major (K-major operand); 0: B is [K, N] row-major (MN-major)
+    int lower_only;       // write only 128 x 128 blocks on or below the diagonal (tiles above it are skipped)
+    int m_tiles, n_tiles;
+    unsigned* status;
+};
+
+// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3fffu);
+    d |= (uint64_t)1 << 16;                               // leading offset: unused for swizzled K-major
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride between 8-row groups
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// MN-major 32-bit operand: the only shared-memory layout the tensor core accepts is the 128-byte
+// swizzle with 32-byte atoms (layout type 1; TMA mode SWIZZLE_128B_ATOM_32B): rows of 128 bytes
+// (32 columns), swizzle period 4 k-rows (512 bytes).  Boxes of 32 columns x 32 k-rows (4 KiB) sit
+// side by side: leading offset = one box, stride offset = 512 bytes between 4-row k groups.
+__device__ __forceinline__ uint64_t mnmajor_sw128_desc(uint32_t saddr, uint32_t box_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3fffu);
+    d |= (uint64_t)((box_bytes >> 4) & 0x3fffu) << 16;    // between 32-column boxes
+    d |= (uint64_t)(512 >> 4) << 32;                      // between 4-row k groups
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)1 << 61;                               // SWIZZLE_128B_BASE32B
+    return d;
+}
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)acc) : "memory");
+}
+// kind::tf32: D = f32 (1 << 4), A and B formats TF32 (2), A K-major, B major per call.
+__device__ __forceinline__ uint32_t tf32_idesc(int b_mn_major) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(GT_N >> 3) << 17) | ((uint32_t)(GT_M >> 4) << 24);
+}
+
+__device__ __forceinline__ bool tile_skipped(const GemmArgs& g, int mi, int nj) {
+    return g.lower_only && (nj * GT_N > mi * GT_M + GT_M - 1);
+}
+
+__global__ void __launch_bounds__(GT_THREADS, 1)
+k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+              const GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GT_STAGES * GT_STAGE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * GT_STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t full0 = smem_u32(bars);                 // TMA landed          (count 1 + tx)
+    const uint32_t ready0 = full0 + 8 * GT_STAGES;         // hi / lo split done  (count 4 warps)
+    const uint32_t empty0 = ready0 + 8 * GT_STAGES;        // MMAs retired        (count 1)
+    const uint32_t tfull0 = empty0 + 8 * GT_STAGES, tempty0 = tfull0 + 16;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < GT_STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1); mbar_init(ready0 + 8 * s, 4); mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total = g.m_tiles * g.n_tiles;
+    const int k_steps = g.K / GT_K;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, armed = 0, armed_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                const int mi = t / g.n_tiles, nj = t % g.n_tiles;
+                if (tile_skipped(g, mi, nj)) continue;
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag);
+                    if (!ok) break;
+                    const uint32_t sa = smem_u32(smem + stage * GT_STAGE_BYTES);
+                    const uint32_t sb = sa + GT_A_BYTES;
+                    const uint32_t fb = full0 + 8 * stage;
+                    mbar_expect_tx(fb, GT_RAW_BYTES);
+                    armed |= 1u << stage;
+                    armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
+                    tma_load_2d(sa, &map_a, ks * GT_K, mi * GT_M, fb);                    // 32 k x 128 rows
+                    if (g.b_is_nk) {
+                        tma_load_2d(sb, &map_b, ks * GT_K, nj * GT_N, fb);                // 32 k x 256 rows
+                    } else {
+#pragma unroll
+                        for (int b = 0; b < GT_N / 32; ++b)                               // 32 cols x 32 k-rows each
+                            tma_load_2d(sb + b * 4096, &map_b, nj * GT_N + b * 32, ks * GT_K, fb);
+                    }
+                    if (++stage == GT_STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            for (int s = 0; s < GT_STAGES; ++s) {          // drain copies in flight before smem goes away
+                if (!(armed >> s & 1u)) continue;
+                const unsigned long long t0 = global_ns();
+                while (!mbar_try_wait(full0 + 8 * s, (armed_phase >> s) & 1u))
+                    if (global_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; break; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = tf32_idesc(g.b_is_nk ? 0 : 1);
+            uint32_t stage = 0, phase = 0, unit = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                const int mi = t / g.n_tiles, nj = t % g.n_tiles;
+                if (tile_skipped(g, mi, nj)) continue;
+                const uint32_t buf = unit & 1, use = unit >> 1;
+                ++unit;
+                ok = mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * GT_N;
+                bool first = true;
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    ok = mbar_wait(ready0 + 8 * stage, phase, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_hi = smem_u32(smem + stage * GT_STAGE_BYTES), b_hi = a_hi + GT_A_BYTES;
+                    const uint32_t a_lo = a_hi + GT_RAW_BYTES, b_lo = b_hi + GT_RAW_BYTES;
+#pragma unroll
+                    for (int k = 0; k < GT_K / 8; ++k) {
+                        // one MMA consumes K = 8 float32: 32 bytes along a K-major row, or one
+                        // 8-row group (1024 bytes) of an MN-major box
+                        const uint32_t ao = k * 32, bo = g.b_is_nk ? k * 32 : k * 1024;
+                        const uint64_t dah = kmajor_sw128_desc(a_hi + ao), dal = kmajor_sw128_desc(a_lo + ao);
+                        const uint64_t dbh = g.b_is_nk ? kmajor_sw128_desc(b_hi + bo) : mnmajor_sw128_desc(b_hi + bo, 4096);
+                        const uint64_t dbl = g.b_is_nk ? kmajor_sw128_desc(b_lo + bo) : mnmajor_sw128_desc(b_lo + bo, 4096);
+                        umma_tf32(d_tmem, dal, dbh, idesc, !first);      // small terms first
+                        umma_tf32(d_tmem, dah, dbl, idesc, true);
+                        umma_tf32(d_tmem, dah, dbh, idesc, true);
+                        first = false;
+                    }
+                    umma_commit(empty0 + 8 * stage);
+                    if (++stage == GT_STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit(tfull0 + 8 * buf);
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------- splitter: hi = x with 13 low mantissa bits cleared, lo = x - hi ----------------
+        const int ctid = threadIdx.x - 64;                  // 0..127
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+            const int mi = t / g.n_tiles, nj = t % g.n_tiles;
+            if (tile_skipped(g, mi, nj)) continue;
+            for (int ks = 0; ks < k_steps; ++ks) {
+                ok = mbar_wait(full0 + 8 * stage, phase, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                float4* hi = reinterpret_cast<float4*>(smem + stage * GT_STAGE_BYTES);
+                float4* lo = reinterpret_cast<float4*>(smem + stage * GT_STAGE_BYTES + GT_RAW_BYTES);
+#pragma unroll 4
+                for (int i = ctid; i < GT_RAW_BYTES / 16; i += 128) {
+                    const float4 x = hi[i];
+                    float4 h, l;
+                    h.x = __uint_as_float(__float_as_uint(x.x) & 0xffffe000u); l.x = x.x - h.x;
+                    h.y = __uint_as_float(__float_as_uint(x.y) & 0xffffe000u); l.y = x.y - h.y;
+                    h.z = __uint_as_float(__float_as_uint(x.z) & 0xffffe000u); l.z = x.z - h.z;
+                    h.w = __uint_as_float(__float_as_uint(x.w) & 0xffffe000u); l.w = x.w - h.w;
+                    hi[i] = h;
+                    lo[i] = l;
+                }
+                // make the generic-proxy writes visible to the tensor core (async proxy)
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(ready0 + 8 * stage);
+                if (++stage == GT_STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 6..9 own TMEM lanes 32 * (warp % 4) .. +31 ----------------
+        const int q = warp & 3;
+        uint32_t unit = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+            const int mi = t / g.n_tiles, nj = t % g.n_tiles;
+            if (tile_skipped(g, mi, nj)) continue;
+            const uint32_t buf = unit & 1, use = unit >> 1;
+            ++unit;
+            ok = mbar_wait(tfull0 + 8 * buf, use & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int row = mi * GT_M + q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * GT_N;
+#pragma unroll 1
+            for (int c0 = 0; c0 < GT_N; c0 += 32) {
+                float v[32];
+                tmem_ld32(taddr + c0, v);
+                const int col = nj * GT_N + c0;
+                // lower_only: nothing is written above the 128 x 128 block that holds the diagonal,
+                // so that a triangular matrix updated this way keeps exact zeros there
+                if (row < g.M && col < g.N && !(g.lower_only && col > (row | 127))) {
+                    float4* dst = reinterpret_cast<float4*>(g.C + (int64_t)row * g.ldc + col);
+                    float4 o[8];
+                    if (g.beta != 0.f) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) o[j] = dst[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) o[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        o[j].x = fmaf(g.alpha, v[4 * j + 0], g.beta * o[j].x);
+                        o[j].y = fmaf(g.alpha, v[4 * j + 1], g.beta * o[j].y);
+                        o[j].z = fmaf(g.alpha, v[4 * j + 2], g.beta * o[j].z);
+                        o[j].w = fmaf(g.alpha, v[4 * j + 3], g.beta * o[j].w);
+                        dst[j] = o[j];
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && g.status) atomicOr(g.status, CRB_FLAG_WAIT_LIMIT);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// C[M,N] = alpha * A[M,K] * op(B) + beta * C on the tensor cores.
+// Requirements: K % 32 == 0, N % 32 == 0, leading dimensions % 4 == 0, 16-byte aligned bases.
+// `status` (device, may be NULL) receives CRB_FLAG_WAIT_LIMIT if a bounded wait ran out.
+int gemm_tf32x3(bool b_is_nk, bool lower_only, int M, int N, int K, float alpha, const float* A, int64_t lda,
+                const float* B, int64_t ldb, float beta, float* C, int64_t ldc, unsigned* status,
+                cudaStream_t st) {
+    if (M <= 0 || N <= 0) return CRB_OK;
+    if (K <= 0 || (K % GT_K) || (N % 32) || (lda & 3) || (ldb & 3) || (ldc & 3)) return CRB_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
+        return CRB_ERR_BAD_ARG;
+    CUtensorMap map_a, map_b;
+    int rc = make_tensor_map_2d(&map_a, A, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)K, (uint64_t)M, (uint64_t)lda,
+                                GT_K, GT_M);
+    if (rc != CRB_OK) return rc;
+    if (b_is_nk)
+        rc = make_tensor_map_2d(&map_b, B, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)K, (uint64_t)N, (uint64_t)ldb,
+                                GT_K, GT_N);
+    else
+        rc = make_tensor_map_2d(&map_b, B, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)N, (uint64_t)K, (uint64_t)ldb,
+                                32, GT_K, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    if (rc != CRB_OK) return rc;
+    GemmArgs g;
+    g.C = C; g.ldc = ldc; g.M = M; g.N = N; g.K = K; g.alpha = alpha; g.beta = beta;
+    g.b_is_nk = b_is_nk ? 1 : 0; g.lower_only = lower_only ? 1 : 0;
+    g.m_tiles = (M + GT_M - 1) / GT_M; g.n_tiles = (N + GT_N - 1) / GT_N;
+    g.status = status;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(k_gemm_tf32x3, cudaFuncAttributeMaxDynamicSharedMemorySize, GT_SMEM) != cudaSuccess)
+            return CRB_ERR_LAUNCH;
+        attr_set = true;
+    }
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    const int total = g.m_tiles * g.n_tiles;
+    k_gemm_tf32x3<<<total < sms ? total : sms, GT_THREADS, GT_SMEM, st>>>(map_a, map_b, g);
+    CRB_LAUNCHED();
+    return CRB_OK;
+}
+
+}  // namespace crb

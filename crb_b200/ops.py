@@ -186,6 +186,18 @@ def trailing_update(W: torch.Tensor, Err: torch.Tensor, U: torch.Tensor, block: 
                                     U.stride(0), block, stream_ptr()), "crb_trailing_update")
 
 
+def gemm_f32(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, alpha: float = 1.0, beta: float = 0.0,
+             b_is_nk: bool = False, lower_only: bool = False) -> torch.Tensor:
+    """C = alpha * A @ (B.T if b_is_nk else B) + beta * C on the tensor cores (hi/lo TF32 split)."""
+    _need_cuda(A, B, C)
+    M, K = A.shape
+    N = B.shape[0] if b_is_nk else B.shape[1]
+    status = torch.zeros(1, dtype=torch.int32, device=A.device)
+    check(lib().crb_gemm_f32(int(b_is_nk), int(lower_only), M, N, K, alpha, ptr(A), A.stride(0), ptr(B),
+                             B.stride(0), beta, ptr(C), C.stride(0), ptr(status), stream_ptr()), "crb_gemm_f32")
+    return C
+
+
 def quantize_linear(W: torch.Tensor, U: torch.Tensor, technique: str = "crb", lam: float = 1e-5,
                     corr_damp: float = 0.1, metric: str = "hessian", want_codes: bool = False,
                     want_trace: bool = True) -> dict:

@@ -138,6 +138,17 @@ int crb_binarize_group(const float *W_dev, int R, int64_t ldw, const uint8_t *ma
 int crb_trailing_update(float *W_dev, int R, int C, int64_t ldw, const float *Err_dev,
                         const float *U_dev, int64_t ldu, int block, void *stream);
 
+/* ---- float32 GEMM building block ------------------------------------------------------
+ * C[M,N] = alpha * A[M,K] * op(B) + beta * C, all float32 row-major, computed on the tensor
+ * cores with a hi/lo TF32 split of both operands (three products per term, float32
+ * accumulation), which keeps float32-level accuracy; this is what stands in for the
+ * reference's TF32-disabled torch matmuls (bigptq.py:11-12, :264 and the factorisation).
+ * b_is_nk != 0: B is [N, K]; else B is [K, N].  lower_only != 0 skips tiles above the diagonal.
+ * K % 32 == 0, N % 32 == 0, leading dimensions % 4 == 0; status (device, may be NULL).   */
+int crb_gemm_f32(int b_is_nk, int lower_only, int M, int N, int K, float alpha, const float *A_dev,
+                 int64_t lda, const float *B_dev, int64_t ldb, float beta, float *C_dev, int64_t ldc,
+                 unsigned *status_dev, void *stream);
+
 /* ---- whole linear ----------------------------------------------------------------
  * The block loop of BRAGPTQ.fasterquant (bigptq.py:131-264) for all C/128 blocks:
  * block step + trailing update, no host synchronisation.  Buffers as above;

@@ -112,6 +112,30 @@ def test_binarize_group_matches_reference(ops, blocks, ci, tech):
     assert bool((q[::7] == 0).all())
 
 
+def test_gemm_f32_keeps_float32_accuracy(ops):
+    """The split-TF32 tensor-core GEMM against float64, in every operand layout the path uses."""
+    g = torch.Generator().manual_seed(11)
+    cases = [(96, 384, 128, False, False), (300, 256, 256, True, False), (512, 512, 128, True, True),
+             (128, 640, 384, False, False), (33, 128, 128, True, False)]
+    for M, N, K, b_is_nk, lower in cases:
+        A = torch.randn(M, K, generator=g) * torch.logspace(-3, 3, K)[None, :]      # wide dynamic range
+        B = (torch.randn(N, K, generator=g) if b_is_nk else torch.randn(K, N, generator=g))
+        C0 = torch.randn(M, N, generator=g)
+        ref = (-0.5 * (A.double() @ (B.double().t() if b_is_nk else B.double())) + 2.0 * C0.double())
+        mag = (A.double().abs() @ (B.double().abs().t() if b_is_nk else B.double().abs())) + C0.double().abs()
+        Cd = C0.to(DEV).clone()
+        ops.gemm_f32(A.to(DEV), B.to(DEV), Cd, alpha=-0.5, beta=2.0, b_is_nk=b_is_nk, lower_only=lower)
+        got = Cd.cpu().double()
+        err = ((got - ref).abs() / mag)
+        if lower:   # 128 x 128 blocks above the diagonal are left untouched
+            keep = torch.zeros(M, N, dtype=torch.bool)
+            for mi in range(0, M, 128):
+                keep[mi:mi + 128, mi + 128:] = True
+            assert torch.equal(Cd.cpu()[keep], C0[keep])
+            err = err[~keep]
+        assert float(err.max()) < 3e-6, (M, N, K, b_is_nk, lower, float(err.max()))
+
+
 def test_trailing_update_matches_fp32_matmul(ops):
     g = torch.Generator().manual_seed(3)
     for R, C, blk in ((96, 384, 0), (257, 512, 2), (128, 256, 1)):
