@@ -18,7 +18,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
-from ._lib import BLOCK, FLAG_NONFINITE, CrbError
+from ._lib import BLOCK, FLAG_BAD_PIVOT, FLAG_NONFINITE, CrbError
 
 try:  # transformers.Conv1D weights are stored transposed (bigptq.py:28-29)
     import transformers
@@ -102,6 +102,15 @@ class BRAGPTQ:
 
     def fasterquant(self, blocksize=128, percdamp=0.01, partition=3, orders=(1, 1, 2),
                     global_scale=False):
+        """Binarizes the layer's weight in place and returns {"error": float} (bigptq.py:56-291)."""
+        state = self.fasterquant_begin(blocksize, percdamp, partition, orders, global_scale)
+        return self.fasterquant_end(state)
+
+    # The two halves below let a caller overlap several linears: `begin` only enqueues work on the
+    # current stream (factorisation attempt 0); `end` handles the rare damping retry, enqueues the
+    # block loop, synchronises and writes the weight back.
+    def fasterquant_begin(self, blocksize=128, percdamp=0.01, partition=3, orders=(1, 1, 2),
+                          global_scale=False):
         technique = getattr(self.braq_quantizer, "method", None)
         if technique not in ("braq", "crbog", "crb"):
             raise NotImplementedError(f"technique {technique!r}: only braq, crbog and crb are implemented")
@@ -117,46 +126,62 @@ class BRAGPTQ:
         if self.columns % BLOCK:
             raise NotImplementedError(f"in_features must be a multiple of {BLOCK}")
 
-        tick = time.time()
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        st = {"tick": time.time(), "percdamp": percdamp, "technique": technique,
+              "stream": torch.cuda.current_stream(self.dev),
+              "ev": [torch.cuda.Event(enable_timing=True) for _ in range(3)]}
         W = self.layer.weight.data.clone()
         if isinstance(self.layer, nn.Conv2d):
             W = W.flatten(1)
         if _Conv1D and isinstance(self.layer, _Conv1D):
             W = W.t()
-        W = W.float().contiguous()
-
+        st["W"] = W.float().contiguous()
         # the reference consumes H here (bigptq.py:101-102)
         if self._H_set is not None:
             H, self._H_keep = self._H_set.clone(), self._H_set
         else:
             H, self._H_keep = self._S.clone(), None
             ops.hessian_finalize(H, 2.0 / max(self.nsamples, 1))
-        ev[0].record()
-        U = ops.hinv_upper_factor(H, W, percdamp, restore=self._restore_hessian)
-        ev[1].record()
-        self._H_set, self._S, self._H_keep = None, None, None
+        st["H"] = H
+        st["diag0"] = torch.diagonal(H).clone()
+        st["status"] = torch.zeros(4, dtype=torch.int32, device=self.dev)
+        st["ev"][0].record()
+        ops.factor_enqueue(H, st["W"], percdamp, 0, st["status"])
+        return st
 
-        lam = float(getattr(self.braq_quantizer, "lam", 1e-5))
-        corr_damp = float(getattr(self.braq_quantizer, "corr_damp", 0.1))
-        out = ops.quantize_linear(W, U, technique, lam, corr_damp, self.salient_metric,
-                                  want_codes=False, want_trace=True)
-        ev[2].record()
-        error = torch.sum(out["losses"]).item()                     # synchronises
-        flags = ops.read_status(out["workspace"])
-        if flags & ~FLAG_NONFINITE:
-            raise CrbError(f"block loop reported device status flags {flags:#x}")
-        self.last_trace = out["trace"]
-        self.last_flags = flags
-        self.last_timing = {"factor_ms": ev[0].elapsed_time(ev[1]), "blocks_ms": ev[1].elapsed_time(ev[2])}
-        if self.verbose:
-            print("time %.2f" % (time.time() - tick))
-            print("error", error)
-
-        if _Conv1D and isinstance(self.layer, _Conv1D):
-            W = W.t()
-        self.layer.weight.data = W.reshape(self.layer.weight.shape).to(self.layer.weight.data.dtype)
-        del H, U, W
+    def fasterquant_end(self, st):
+        with torch.cuda.stream(st["stream"]):
+            H, W = st["H"], st["W"]
+            attempt = 0
+            while int(st["status"][0].item()) & FLAG_BAD_PIVOT:          # bigptq.py:115-123
+                attempt += 1
+                if attempt > 10:
+                    ops.diagonal_fallback(H, st["diag0"], st["percdamp"])   # bigptq.py:124-126
+                    break
+                self._restore_hessian(H)
+                st["status"].zero_()
+                ops.factor_enqueue(H, W, st["percdamp"], attempt, st["status"])
+            U = H
+            st["ev"][1].record()
+            self._H_set, self._S, self._H_keep = None, None, None
+            lam = float(getattr(self.braq_quantizer, "lam", 1e-5))
+            corr_damp = float(getattr(self.braq_quantizer, "corr_damp", 0.1))
+            out = ops.quantize_linear(W, U, st["technique"], lam, corr_damp, self.salient_metric,
+                                      want_codes=False, want_trace=True)
+            st["ev"][2].record()
+            error = torch.sum(out["losses"]).item()                     # synchronises this stream
+            flags = ops.read_status(out["workspace"])
+            if flags & ~FLAG_NONFINITE:
+                raise CrbError(f"block loop reported device status flags {flags:#x}")
+            self.last_trace = out["trace"]
+            self.last_flags = flags
+            ev = st["ev"]
+            self.last_timing = {"factor_ms": ev[0].elapsed_time(ev[1]), "blocks_ms": ev[1].elapsed_time(ev[2])}
+            if self.verbose:
+                print("time %.2f" % (time.time() - st["tick"]))
+                print("error", error)
+            if _Conv1D and isinstance(self.layer, _Conv1D):
+                W = W.t()
+            self.layer.weight.data = W.reshape(self.layer.weight.shape).to(self.layer.weight.data.dtype)
         return {"error": error}
 
     def free(self):

@@ -14,7 +14,8 @@
 //   k_salient_search   49 candidates x rows, deterministic reduction, first strict minimum
 //   k_select_l1/l2/l3  exact radix selection (15+9+7 bits) of the 162 order statistics that
 //                      numpy.quantile(method="linear") interpolates between
-//   k_split_search     81 candidates x rows, deterministic reduction, first strict minimum
+//   k_sort_rows        every metric row sorted (bitonic network), for the split search
+//   k_split_search_sorted  81 candidates x rows from prefix sums of the sorted rows
 //   k_finalize         masks, the technique's binarizer per group, Q, Err, Losses
 #include <math.h>
 
@@ -59,6 +60,8 @@ struct BlockWs {
     unsigned* hist3;         // [kTargets][kL3Bins]
     // ---- scratch ----
     float* M;                // [R][128] metric
+    float* sv;               // [R][128] every row of M sorted ascending
+    unsigned char* sc;       // [R][128] the column of each sorted value
     double* colpart;         // [kMaxCtas1][128]
     double* partial;         // [kSplits + 1][tile_stride]
     unsigned char* rank;     // [128] position of each column in the score order (>= 50: never salient)
@@ -96,6 +99,8 @@ static size_t carve_block_ws(void* base, int R, BlockWs* ws) {
     w.zero_begin = base ? static_cast<unsigned char*>(base) + z0 : nullptr;
     w.zero_bytes = off - z0;
     w.M = static_cast<float*>(take(sizeof(float) * (size_t)R * kBlock));
+    w.sv = static_cast<float*>(take(sizeof(float) * (size_t)R * kBlock));
+    w.sc = static_cast<unsigned char*>(take((size_t)R * kBlock));
     w.colpart = static_cast<double*>(take(sizeof(double) * kMaxCtas1 * kBlock));
     w.tile_stride = kMaxTiles;
     w.partial = static_cast<double*>(take(sizeof(double) * (kSplits + 1) * kMaxTiles));
@@ -668,62 +673,239 @@ k_select_l3(const float* __restrict__ M, int R, const unsigned char* __restrict_
 }
 
 // ---------------------------------------------------------------------------------------
-// K6: split search                                                    (autosearch.py:72-81)
+// Row sort: every row of the metric sorted ascending together with the column of each value
+// (bitonic network, one warp per row, four elements per lane; ties keep the lower column first).
+// The sorted rows turn the candidate evaluations of the split search into prefix-sum lookups.
 // ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kSearchThreads)
-k_split_search(const float* __restrict__ M, int R, int rows_per_cta, int chunk,
-               const unsigned char* __restrict__ rank, const float* __restrict__ pvals_in,
-               double* __restrict__ partial, int tile_stride, unsigned* counters,
-               int* __restrict__ sel, float* __restrict__ pvals_out, double* __restrict__ trace,
-               unsigned* status) {
-    __shared__ double s_acc[kSplits + 1][32];
-    __shared__ double s_tot[kSplits + 1];
+__device__ __forceinline__ bool key_less(unsigned ka, int ca, unsigned kb, int cb) {
+    return (ka < kb) || (ka == kb && ca < cb);
+}
+
+__global__ void __launch_bounds__(256)
+k_sort_rows(const float* __restrict__ M, int R, float* __restrict__ sv, unsigned char* __restrict__ sc) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + warp;
+    if (row >= R) return;
+    unsigned k[4];
+    int c[4];
+    {
+        const float4 v = *reinterpret_cast<const float4*>(M + (int64_t)row * kBlock + 4 * lane);
+        // the metric is >= 0, so the bit pattern orders like the value (NaN sorts last)
+        k[0] = __float_as_uint(v.x) & 0x7fffffffu; k[1] = __float_as_uint(v.y) & 0x7fffffffu;
+        k[2] = __float_as_uint(v.z) & 0x7fffffffu; k[3] = __float_as_uint(v.w) & 0x7fffffffu;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) c[q] = 4 * lane + q;
+    }
+#pragma unroll
+    for (int size = 2; size <= kBlock; size <<= 1) {
+#pragma unroll
+        for (int j = size >> 1; j >= 1; j >>= 1) {
+            if (j >= 4) {
+                const int lj = j >> 2;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int e = 4 * lane + q;
+                    const unsigned ok = __shfl_xor_sync(0xffffffffu, k[q], lj);
+                    const int oc = __shfl_xor_sync(0xffffffffu, c[q], lj);
+                    const bool up = (e & size) == 0;            // ascending segment
+                    const bool lower_half = (e & j) == 0;       // this element keeps the smaller key
+                    const bool mine_less = key_less(k[q], c[q], ok, oc);
+                    const bool keep = (lower_half == up) ? mine_less : !mine_less;
+                    if (!keep) { k[q] = ok; c[q] = oc; }
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int qq = q ^ j;
+                    if (qq > q) {
+                        const int e = 4 * lane + q;
+                        const bool up = (e & size) == 0;
+                        const bool in_order = key_less(k[q], c[q], k[qq], c[qq]);
+                        if (in_order != up) {
+                            const unsigned tk = k[q]; k[q] = k[qq]; k[qq] = tk;
+                            const int tc = c[q]; c[q] = c[qq]; c[qq] = tc;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    *reinterpret_cast<float4*>(sv + (int64_t)row * kBlock + 4 * lane) =
+        make_float4(__uint_as_float(k[0]), __uint_as_float(k[1]), __uint_as_float(k[2]), __uint_as_float(k[3]));
+    *reinterpret_cast<uchar4*>(sc + (int64_t)row * kBlock + 4 * lane) =
+        make_uchar4((unsigned char)c[0], (unsigned char)c[1], (unsigned char)c[2], (unsigned char)c[3]);
+}
+
+// ---------------------------------------------------------------------------------------
+// K6: split search on sorted rows                                      (autosearch.py:72-81)
+//
+// Per row the non-salient values are kept sorted with float64 prefix sums of x and x^2.  A split
+// candidate p cuts the row at c = #{x < p}; each side is a contiguous range [a, b) whose order-1
+// expansion (binary.py:18-39) follows from prefix sums:  mu = sum / m;  the elements below mu are
+// [a, cm), so  A = sum|x - mu| = mu (cm - a) - S[a,cm) + S[cm,b) - mu (b - cm),  alpha = A / m,
+// squared error = sum (x - mu)^2 - 2 alpha A + m alpha^2.  mu and alpha are rounded to float32
+// where the reference holds them in float32; everything else is float64, which is at least as
+// accurate as the reference's float32 element-wise evaluation (differences ~1e-7 relative).
+// One thread per (row, candidate); three binary searches per task.
+// ---------------------------------------------------------------------------------------
+constexpr int kSplitRows = 32;                   // rows per pass of a CTA
+constexpr int kRowPitch = kBlock + 1;            // odd pitch: rows start in different banks
+constexpr int kSplitSmem = kSplitRows * kRowPitch * (int)(sizeof(float) + 2 * sizeof(double)) +
+                           (kSplits + 1) * kSplitRows * (int)sizeof(double);
+
+__device__ __forceinline__ int lower_bound_f(const float* v, int a, int b, float t) {
+    int lo = a, len = b - a;                     // first index in [a, b) with v[idx] >= t
+    while (len > 0) {
+        const int half = len >> 1;
+        if (v[lo + half] < t) { lo += half + 1; len -= half + 1; } else { len = half; }
+    }
+    return lo;
+}
+
+// squared error of the one-expansion binarizer on the sorted range [a, b) of one row
+__device__ __forceinline__ double range_order1_err(const float* v, const double* P1, const double* P2, int a, int b) {
+    const int m = b - a;
+    if (m <= 0) return 0.0;
+    const double S1 = P1[b] - P1[a], S2 = P2[b] - P2[a];
+    const float mu_f = __fdiv_rn((float)S1, (float)m);
+    const double mu = (double)mu_f;
+    const int cm = lower_bound_f(v, a, b, mu_f);
+    const double below = P1[cm] - P1[a];
+    const double A = mu * (double)(cm - a) - below + (S1 - below) - mu * (double)(b - cm);
+    const double alpha = (double)__fdiv_rn((float)A, (float)m);
+    return S2 - 2.0 * mu * S1 + (double)m * mu * mu - 2.0 * alpha * A + (double)m * alpha * alpha;
+}
+
+__global__ void __launch_bounds__(256)
+k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restrict__ sc, int R,
+                      int rows_per_cta, const unsigned char* __restrict__ rank,
+                      const float* __restrict__ pvals_in, double* __restrict__ partial, int tile_stride,
+                      unsigned* counters, int* __restrict__ sel, float* __restrict__ pvals_out,
+                      double* __restrict__ trace, unsigned* status) {
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    double* s_P1 = reinterpret_cast<double*>(s_raw);                         // [rows][pitch]
+    double* s_P2 = s_P1 + kSplitRows * kRowPitch;
+    double* s_acc = s_P2 + kSplitRows * kRowPitch;                           // [kSplits + 1][rows]
+    float* s_v = reinterpret_cast<float*>(s_acc + (kSplits + 1) * kSplitRows);   // [rows][pitch]
     __shared__ float s_p[kSplits];
+    __shared__ unsigned char s_rank[kBlock];
+    __shared__ double s_tot[kSplits + 1];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = row_in_warp(lane), l = lane_in_row(lane);
     const int isal = sel[0];
-    const int c0 = blockIdx.y * chunk;
-    const int nc = min(chunk, kSplits - c0);
-    const bool do_sal = (blockIdx.y == 0);      // the constant salient-group term, once per row
-    for (int k = tid; k < (kSplits + 1) * 32; k += blockDim.x) (&s_acc[0][0])[k] = 0.0;
+    const int n = kBlock - isal;                                             // non-salient values per row
     if (tid < kSplits) s_p[tid] = pvals_in[tid];
-    int rk[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) rk[j] = rank[col_of(l, j)];
+    if (tid < kBlock) s_rank[tid] = rank[tid];
+    for (int k = tid; k < (kSplits + 1) * kSplitRows; k += blockDim.x) s_acc[k] = 0.0;
     __syncthreads();
+
     const int row_base = blockIdx.x * rows_per_cta;
-    for (int p = 0; p < rows_per_cta; p += 32) {
-        const int row = row_base + p + warp * 4 + g;
-        float x[16];
-        if (row < R) {
-            load_row16(M + (int64_t)row * kBlock, l, x);
-        } else {
+    for (int p0 = 0; p0 < rows_per_cta; p0 += kSplitRows) {
+        // ---- phase A: one warp per row: drop the salient columns, keep the order, prefix sums ----
+        for (int r = warp; r < kSplitRows; r += 8) {
+            const int row = row_base + p0 + r;
+            float x[4] = {0.f, 0.f, 0.f, 0.f};
+            bool ns[4] = {false, false, false, false};
+            if (row < R) {
+                const float4 v = *reinterpret_cast<const float4*>(sv + (int64_t)row * kBlock + 4 * lane);
+                const uchar4 c = *reinterpret_cast<const uchar4*>(sc + (int64_t)row * kBlock + 4 * lane);
+                x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+                ns[0] = s_rank[c.x] >= isal; ns[1] = s_rank[c.y] >= isal;
+                ns[2] = s_rank[c.z] >= isal; ns[3] = s_rank[c.w] >= isal;
+            }
+            // salient-group term (order-2 expansion on the isal salient values of the row), by the warp
+            {
+                const float ds = (float)max(isal, 1);
+                float s = 0.f;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) x[j] = 0.f;
-        }
-        for (int c = 0; c < nc; ++c) {
-            const float e = hor1_split_err(x, rk, isal, s_p[c0 + c]);
-            if (l == 0) s_acc[c][warp * 4 + g] += (double)e;
-        }
-        if (do_sal) {
-            const float e = hor2_single_err(x, rk, isal);
-            if (l == 0) s_acc[kSplits][warp * 4 + g] += (double)e;
-        }
-    }
-    __syncthreads();
-    if (tid < nc) {
-        double v = 0.0;
+                for (int q = 0; q < 4; ++q) s += (row < R && !ns[q]) ? x[q] : 0.f;
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                const float mu = __fdiv_rn(s, ds);
+                float dv[4], a = 0.f;
 #pragma unroll
-        for (int k = 0; k < 32; ++k) v += s_acc[tid][k];
-        partial[(size_t)(c0 + tid) * tile_stride + blockIdx.x] = v;
-    }
-    if (do_sal && tid == kSearchThreads - 1) {
-        double v = 0.0;
+                for (int q = 0; q < 4; ++q) { dv[q] = x[q] - mu; a += (row < R && !ns[q]) ? fabsf(dv[q]) : 0.f; }
+                for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                const float al = __fdiv_rn(a, ds);
+                float y1[4];
+                s = 0.f;
 #pragma unroll
-        for (int k = 0; k < 32; ++k) v += s_acc[kSplits][k];
-        partial[(size_t)kSplits * tile_stride + blockIdx.x] = v;
+                for (int q = 0; q < 4; ++q) {
+                    y1[q] = __fadd_rn(al * sgnf(dv[q]), mu);
+                    dv[q] = x[q] - y1[q];
+                    s += (row < R && !ns[q]) ? dv[q] : 0.f;
+                }
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                const float mu2 = __fdiv_rn(s, ds);
+                a = 0.f;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { dv[q] -= mu2; a += (row < R && !ns[q]) ? fabsf(dv[q]) : 0.f; }
+                for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                const float al2 = __fdiv_rn(a, ds);
+                float e = 0.f;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float qv = __fadd_rn(y1[q], __fadd_rn(al2 * sgnf(dv[q]), mu2));
+                    const float d = x[q] - qv;
+                    e += (row < R && !ns[q]) ? d * d : 0.f;
+                }
+                for (int o = 16; o > 0; o >>= 1) e += __shfl_xor_sync(0xffffffffu, e, o);
+                if (lane == 0) s_acc[kSplits * kSplitRows + r] += (double)e;
+            }
+            // compaction: position of each kept value = number of kept values before it
+            const int mine = (int)ns[0] + (int)ns[1] + (int)ns[2] + (int)ns[3];
+            int incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            int pos = incl - mine;
+            float* vrow = s_v + r * kRowPitch;
+            double l1 = 0.0, l2 = 0.0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                if (ns[q]) { vrow[pos++] = x[q]; l1 += (double)x[q]; l2 += (double)x[q] * (double)x[q]; }
+            // exclusive float64 scan of the per-lane sums, then the running prefix inside the lane
+            double i1 = l1, i2 = l2;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const double t1 = __shfl_up_sync(0xffffffffu, i1, o);
+                const double t2 = __shfl_up_sync(0xffffffffu, i2, o);
+                if (lane >= o) { i1 += t1; i2 += t2; }
+            }
+            double r1 = i1 - l1, r2 = i2 - l2;
+            double* P1 = s_P1 + r * kRowPitch;
+            double* P2 = s_P2 + r * kRowPitch;
+            pos = incl - mine;
+            if (lane == 0) { P1[0] = 0.0; P2[0] = 0.0; }
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                if (ns[q]) {
+                    r1 += (double)x[q]; r2 += (double)x[q] * (double)x[q];
+                    ++pos;
+                    P1[pos] = r1; P2[pos] = r2;
+                }
+        }
+        __syncthreads();
+        // ---- phase B: one thread per (row, candidate) ----
+        for (int task = tid; task < kSplitRows * kSplits; task += blockDim.x) {
+            const int r = task % kSplitRows, k = task / kSplitRows;
+            if (row_base + p0 + r >= R) continue;
+            const float* v = s_v + r * kRowPitch;
+            const double* P1 = s_P1 + r * kRowPitch;
+            const double* P2 = s_P2 + r * kRowPitch;
+            const int c = lower_bound_f(v, 0, n, s_p[k]);                   // low side: x < p (mask.py:11-13)
+            const double e = range_order1_err(v, P1, P2, 0, c) + range_order1_err(v, P1, P2, c, n);
+            s_acc[k * kSplitRows + r] += e;
+        }
+        __syncthreads();
     }
-    if (!last_cta_done(&counters[5], gridDim.x * gridDim.y)) return;
+    if (tid <= kSplits) {
+        double t = 0.0;
+#pragma unroll 8
+        for (int r = 0; r < kSplitRows; ++r) t += s_acc[tid * kSplitRows + r];
+        partial[(size_t)tid * tile_stride + blockIdx.x] = t;
+    }
+    if (!last_cta_done(&counters[5], gridDim.x)) return;
 
     reduce_partials(partial, tile_stride, gridDim.x, kSplits + 1, s_tot);
     if (tid == 0) {
@@ -1065,7 +1247,9 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(k_select_l1, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kL1Bins * (int)sizeof(unsigned)) != cudaSuccess)
+                                 kL1Bins * (int)sizeof(unsigned)) != cudaSuccess ||
+            cudaFuncSetAttribute(k_split_search_sorted, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kSplitSmem) != cudaSuccess)
             return CRB_ERR_LAUNCH;
         attr_set = true;
     }
@@ -1076,7 +1260,9 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
     k_metric_colscore<<<ceil_div(R, rows1), 256, 0, st>>>(W, R, ldw, col0, U, ldu, rows1, ws.M, ws.colpart,
                                                           ws.counters, ws.rank, tr, ws.status);
     CRB_LAUNCHED();
-    // K2 / K6 tiling: <= kMaxTiles row tiles, candidate chunks so that the grid fills the GPU
+    k_sort_rows<<<ceil_div(R, 8), 256, 0, st>>>(ws.M, R, ws.sv, ws.sc);
+    CRB_LAUNCHED();
+    // K2 tiling: <= kMaxTiles row tiles, candidate chunks so that the grid fills the GPU
     const int rows_s = 32 * ceil_div(R, 32 * kMaxTiles);
     const int tiles = ceil_div(R, rows_s);
     const int want_chunks = max(1, ceil_div(4 * 148, tiles));
@@ -1095,12 +1281,11 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
     CRB_LAUNCHED();
     k_select_l3<<<g2, 512, 0, st>>>(ws.M, R, ws.rank, ws.sel, ws);
     CRB_LAUNCHED();
-    // K6
-    const int chunks_sp = min(want_chunks, ceil_div(kSplits, 4));
-    const int chunk_sp = ceil_div(kSplits, chunks_sp);
-    k_split_search<<<dim3(tiles, ceil_div(kSplits, chunk_sp)), kSearchThreads, 0, st>>>(
-        ws.M, R, rows_s, chunk_sp, ws.rank, ws.pvals, ws.partial, ws.tile_stride, ws.counters, ws.sel,
-        ws.pvals, tr, ws.status);
+    // K6: split search on the sorted rows
+    const int rows_sp = kSplitRows * ceil_div(R, kSplitRows * kMaxTiles);
+    k_split_search_sorted<<<ceil_div(R, rows_sp), 256, kSplitSmem, st>>>(
+        ws.sv, ws.sc, R, rows_sp, ws.rank, ws.pvals, ws.partial, ws.tile_stride, ws.counters, ws.sel, ws.pvals,
+        tr, ws.status);
     CRB_LAUNCHED();
     // K7
     k_finalize<<<ceil_div(R, 32), 256, 0, st>>>(W, R, ldw, col0, U, ldu, ws.rank, ws.sel, ws.pvals, technique,

@@ -83,6 +83,7 @@ __global__ void k_reverse_copy(const float* __restrict__ H, int C, const float* 
 // column of the inverse) and split every dot product four ways, so that the serial chain per
 // column is a quarter of the row length plus two shuffles.
 constexpr int kDiagThreads = 4 * FB;
+constexpr int kDiagPitch = FB + 4;
 
 __device__ __forceinline__ float quad_sum(float v) {
     v += __shfl_xor_sync(0xffffffffu, v, 1);
@@ -92,9 +93,10 @@ __device__ __forceinline__ float quad_sum(float v) {
 
 __global__ void __launch_bounds__(kDiagThreads)
 k_chol_diag(float* __restrict__ Akk, int64_t ld, unsigned* status) {
+    // row pitch 132 floats: the four lanes of a row and the eight rows of a warp hit 32 distinct banks
     extern __shared__ float s_diag[];
-    float (*a)[FB + 1] = reinterpret_cast<float (*)[FB + 1]>(s_diag);
-    float (*x)[FB + 1] = reinterpret_cast<float (*)[FB + 1]>(s_diag + FB * (FB + 1));
+    float (*a)[kDiagPitch] = reinterpret_cast<float (*)[kDiagPitch]>(s_diag);
+    float (*x)[kDiagPitch] = reinterpret_cast<float (*)[kDiagPitch]>(s_diag + FB * kDiagPitch);
     const int tid = threadIdx.x;
     const int i = tid >> 2, s = tid & 3;               // row (phase 1) / column (phase 2), quarter
     for (int e = tid; e < FB * FB; e += kDiagThreads) a[e >> 7][e & 127] = Akk[(int64_t)(e >> 7) * ld + (e & 127)];
@@ -102,16 +104,18 @@ k_chol_diag(float* __restrict__ Akk, int64_t ld, unsigned* status) {
     bool bad = false;
     for (int k = 0; k < FB; ++k) {
         // column k: acc = a[i][k] - sum_{j<k} a[i][j] * a[k][j]   for rows i >= k
-        float p0 = 0.f, p1 = 0.f;
+        float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
         if (i >= k) {
             int j = s;
-            for (; j + 4 < k; j += 8) {
+            for (; j + 12 < k; j += 16) {          // four independent chains keep the loads in flight
                 p0 = fmaf(a[i][j], a[k][j], p0);
                 p1 = fmaf(a[i][j + 4], a[k][j + 4], p1);
+                p2 = fmaf(a[i][j + 8], a[k][j + 8], p2);
+                p3 = fmaf(a[i][j + 12], a[k][j + 12], p3);
             }
-            if (j < k) p0 = fmaf(a[i][j], a[k][j], p0);
+            for (; j < k; j += 4) p0 = fmaf(a[i][j], a[k][j], p0);
         }
-        const float acc = a[i][k] - quad_sum(p0 + p1);
+        const float acc = a[i][k] - quad_sum((p0 + p1) + (p2 + p3));
         if (i == k && s == 0) {
             float piv = acc;
             if (!(piv > 0.f) || !isfinite(piv)) { bad = true; piv = 1.f; }
@@ -127,10 +131,16 @@ k_chol_diag(float* __restrict__ Akk, int64_t ld, unsigned* status) {
     // rows are produced in order; the four lanes of a column split the sum over m.
     const int j = i;
     for (int r = 0; r < FB; ++r) {
-        float p = 0.f;
-        if (r > j)
-            for (int m = j + s; m < r; m += 4) p = fmaf(a[r][m], x[m][j], p);
-        p = quad_sum(p);
+        float p = 0.f, pb = 0.f;
+        if (r > j) {
+            int m = j + s;
+            for (; m + 4 < r; m += 8) {
+                p = fmaf(a[r][m], x[m][j], p);
+                pb = fmaf(a[r][m + 4], x[m + 4][j], pb);
+            }
+            if (m < r) p = fmaf(a[r][m], x[m][j], p);
+        }
+        p = quad_sum(p + pb);
         if (s == 0) x[r][j] = (r < j) ? 0.f : ((r == j) ? __fdiv_rn(1.f, a[r][r]) : __fdiv_rn(-p, a[r][r]));
         __syncwarp();
     }
@@ -190,7 +200,7 @@ int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
     k_reverse_copy<<<dim3((C + 255) / 256, C), 256, 0, st>>>(H, C, damp, dead, A);
     CRB_LAUNCHED();
     const int nb = C / FB;
-    constexpr int kDiagSmem = 2 * FB * (FB + 1) * (int)sizeof(float);
+    constexpr int kDiagSmem = 2 * FB * kDiagPitch * (int)sizeof(float);
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(k_chol_diag, cudaFuncAttributeMaxDynamicSharedMemorySize, kDiagSmem) != cudaSuccess)

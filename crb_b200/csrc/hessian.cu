@@ -8,7 +8,8 @@
 //
 // One persistent CTA per SM walks the upper-triangle output tiles (128 rows x 256 columns).
 // Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (owns the TMEM allocation),
-// warps 2..5 = epilogue (TMEM -> registers -> S += acc).  Two 256-column accumulators
+// warps 2..9 = epilogue (TMEM -> registers -> S += acc; two warps per TMEM lane quarter, one per
+// column half).  Two 256-column accumulators
 // alternate so that the epilogue of one tile / token chunk overlaps the MMAs of the next.
 // The token dimension is cut into chunks; each chunk is accumulated in TMEM and then added
 // to S in float32 by the CUDA cores, which bounds the length of any tensor-core running sum.
@@ -39,7 +40,7 @@ constexpr int HT_A_BYTES = (HT_M / HT_BOX) * HT_BOX_BYTES;               // 16 K
 constexpr int HT_B_BYTES = (HT_N / HT_BOX) * HT_BOX_BYTES;               // 32 KiB
 constexpr int HT_STAGE_BYTES = HT_A_BYTES + HT_B_BYTES;                  // 48 KiB
 constexpr int HT_SMEM = HT_STAGES * HT_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-constexpr int HT_THREADS = 192;
+constexpr int HT_THREADS = 320;          // TMA warp, MMA warp, eight epilogue warps
 
 // Shared-memory matrix descriptor of an MN-major, 128-byte-swizzled operand:
 //   bits 0-13 start address >> 4, 16-29 leading-dimension byte offset >> 4 (between 64-element
@@ -99,7 +100,7 @@ k_hessian_umma(const __grid_constant__ CUtensorMap map0, const __grid_constant__
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < HT_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 8); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -195,8 +196,10 @@ k_hessian_umma(const __grid_constant__ CUtensorMap map0, const __grid_constant__
             }
         }
     } else {
-        // ---------------- epilogue: warps 2..5 own TMEM lanes 32*(warp % 4) .. +31 ----------------
+        // ---------------- epilogue: warps 2..9; warp w reads TMEM lanes 32*(w % 4) .. +31 and the
+        // column half (w - 2) / 4 of the 256-column accumulator ----------------
         const int q = warp & 3;
+        const int c_begin = ((warp - 2) >> 2) * (HT_N / 2);
         const float scale = args.inv_scale2 ? *args.inv_scale2 : 1.0f;
         uint32_t unit = 0;
         bool ok = true;
@@ -212,7 +215,7 @@ k_hessian_umma(const __grid_constant__ CUtensorMap map0, const __grid_constant__
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * HT_N;
 #pragma unroll 1
-                for (int c0 = 0; c0 < HT_N; c0 += 32) {
+                for (int c0 = c_begin; c0 < c_begin + HT_N / 2; c0 += 32) {
                     float v[32];
                     tmem_ld32(taddr + c0, v);
                     const int col = nj * HT_N + c0;

@@ -23,8 +23,11 @@ def _need_cuda(*tensors):
 
 
 def _workspace(kind: str, nbytes: int, device) -> torch.Tensor:
-    """Zero-initialised, cached scratch buffer per (kind, device); grows on demand."""
-    key = (kind, torch.device(device).index)
+    """Zero-initialised, cached scratch buffer per (kind, device, current stream); grows on demand.
+
+    Keying by stream lets several linears be processed concurrently on different streams
+    without sharing scratch memory."""
+    key = (kind, torch.device(device).index, torch.cuda.current_stream(device).cuda_stream)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=device)
@@ -69,8 +72,41 @@ def hessian_finalize(S: torch.Tensor, scale: float) -> None:
 
 
 def hessian_status(device) -> int:
-    ws = _workspaces.get(("hessian", torch.device(device).index))
+    ws = _workspaces.get(("hessian", torch.device(device).index, torch.cuda.current_stream(device).cuda_stream))
     return 0 if ws is None else lib().crb_read_status(ptr(ws), stream_ptr())
+
+
+def factor_enqueue(H: torch.Tensor, W: Optional[torch.Tensor], percdamp: float, extra_damp_steps: int,
+                   status: torch.Tensor) -> None:
+    """Enqueues one factorisation attempt (no host synchronisation): H is overwritten by U and
+    `status[0]` receives CRB_FLAG_BAD_PIVOT if a pivot was not positive."""
+    _need_cuda(H, W, status)
+    Cc = H.shape[0]
+    if H.dtype != torch.float32 or not H.is_contiguous() or H.shape != (Cc, Cc):
+        raise CrbError("H must be a contiguous [C, C] float32 tensor")
+    if W is not None and (W.dtype != torch.float32 or W.stride(1) != 1):
+        raise CrbError("W must be float32 with unit column stride")
+    L = lib()
+    ws = _workspace("factor", L.crb_factor_workspace_bytes(Cc), H.device)
+    check(L.crb_hinv_upper_factor(ptr(H), Cc, ptr(W), 0 if W is None else W.shape[0],
+                                  0 if W is None else W.stride(0), float(percdamp), int(extra_damp_steps),
+                                  ptr(ws), ws.numel(), ptr(status), stream_ptr()), "crb_hinv_upper_factor")
+
+
+def diagonal_fallback(H: torch.Tensor, diag0: torch.Tensor, percdamp: float, max_retries: int = 10) -> torch.Tensor:
+    """Last resort of bigptq.py:124-126 after every damping retry failed: U = diag(1/sqrt(diag H))."""
+    diag = diag0.clone()
+    diag[diag == 0] = 1
+    mean = diag.mean()
+    damp = percdamp * mean
+    mean = mean + damp
+    for _ in range(max_retries):
+        extra = 1e-3 * mean
+        damp = damp + extra
+        mean = mean + extra
+    H.zero_()
+    torch.diagonal(H).copy_(torch.rsqrt(torch.clamp(diag + damp, min=1e-8)))
+    return H
 
 
 def hinv_upper_factor(H: torch.Tensor, W: Optional[torch.Tensor], percdamp: float,
@@ -83,14 +119,6 @@ def hinv_upper_factor(H: torch.Tensor, W: Optional[torch.Tensor], percdamp: floa
     the diagonal fallback of bigptq.py:124-126 is used.  `restore(H)` refills H with the
     undamped Hessian for a retry; without it a copy of H is kept for that purpose.
     """
-    _need_cuda(H, W)
-    Cc = H.shape[0]
-    if H.dtype != torch.float32 or not H.is_contiguous() or H.shape != (Cc, Cc):
-        raise CrbError("H must be a contiguous [C, C] float32 tensor")
-    if W is not None and (W.dtype != torch.float32 or W.stride(1) != 1):
-        raise CrbError("W must be float32 with unit column stride")
-    L = lib()
-    ws = _workspace("factor", L.crb_factor_workspace_bytes(Cc), H.device)
     status = torch.zeros(4, dtype=torch.int32, device=H.device)
     saved = H.clone() if restore is None else None
     diag0 = torch.diagonal(H).clone()
@@ -101,25 +129,10 @@ def hinv_upper_factor(H: torch.Tensor, W: Optional[torch.Tensor], percdamp: floa
             else:
                 restore(H)
             status.zero_()
-        check(L.crb_hinv_upper_factor(ptr(H), Cc, ptr(W), 0 if W is None else W.shape[0],
-                                      0 if W is None else W.stride(0), float(percdamp), attempt,
-                                      ptr(ws), ws.numel(), ptr(status), stream_ptr()),
-              "crb_hinv_upper_factor")
+        factor_enqueue(H, W, percdamp, attempt, status)
         if not (int(status[0].item()) & _lib.FLAG_BAD_PIVOT):
             return H
-    # last resort (bigptq.py:124-126): H_chol = diag(sqrt(clamp(diag H, 1e-8))) -> U = diag(1/sqrt)
-    diag = diag0
-    diag[diag == 0] = 1
-    mean = diag.mean()
-    damp = percdamp * mean
-    mean = mean + damp
-    for _ in range(max_retries):
-        extra = 1e-3 * mean
-        damp = damp + extra
-        mean = mean + extra
-    H.zero_()
-    torch.diagonal(H).copy_(torch.rsqrt(torch.clamp(diag + damp, min=1e-8)))
-    return H
+    return diagonal_fallback(H, diag0, percdamp, max_retries)
 
 
 def block_step(W: torch.Tensor, U: torch.Tensor, block: int, technique: str = "crb",

@@ -278,20 +278,39 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
     # ---- quantization: each linear on its owner rank, result broadcast ----
     shapes = {n: (gptq[n].rows, gptq[n].columns) for n in gptq}
     owners = parallel.assign_owners(shapes, ws)
-    errors: Dict[str, float] = {}
+    errors: Dict[str, float] = {n: 0.0 for n in gptq}        # same key order on every rank
     with timer.span("fasterquant"):
-        for name in gptq:
-            if owners[name] == rank:
-                if args.verbose:
-                    print(index, name)
-                    print("Quantizing ...")
+        mine = [n for n in gptq if owners[n] == rank]
+        # the linears are independent problems: give each its own stream so that the serial parts of
+        # one (128-wide diagonal factorisations, small block kernels) overlap the wide kernels of another
+        main = torch.cuda.current_stream(dev) if dev.type == "cuda" else None
+        concurrent = main is not None and getattr(args, "concurrent_linears", True) and len(mine) > 1
+        states = {}
+        order = sorted(mine, key=lambda n: -parallel.linear_cost(*shapes[n]))
+        if concurrent:
+            ready = torch.cuda.Event()
+            ready.record(main)
+            for name in order:
+                s = torch.cuda.Stream(device=dev)
+                s.wait_event(ready)
+                with torch.cuda.stream(s):
+                    states[name] = gptq[name].fasterquant_begin(percdamp=args.percdamp, blocksize=args.blocksize,
+                                                                partition=args.partition,
+                                                                global_scale=args.global_scale)
+        for name in (reversed(order) if concurrent else mine):
+            if args.verbose:
+                print(index, name)
+                print("Quantizing ...")
+            if concurrent:
+                info = gptq[name].fasterquant_end(states[name])
+                main.wait_stream(states[name]["stream"])
+            else:
                 info = gptq[name].fasterquant(percdamp=args.percdamp, blocksize=args.blocksize,
                                               partition=args.partition, global_scale=args.global_scale)
-                errors[name] = info["error"]
-                for k, v in gptq[name].last_timing.items():
-                    timer.ms[k] = timer.ms.get(k, 0.0) + v
-            else:
-                errors[name] = 0.0
+            errors[name] = info["error"]
+            for k, v in gptq[name].last_timing.items():
+                timer.ms[k] = timer.ms.get(k, 0.0) + v
+        for name in gptq:
             gptq[name].free()
     with timer.span("weight_broadcast"):
         if ws > 1:
