@@ -11,7 +11,7 @@
 // Kernel sequence per block (stream ordered, no host synchronisation, no kernel waits on
 // another CTA: grid-wide decisions are taken by whichever CTA finishes last):
 //   k_metric_colscore  M, column scores, top-50 columns
-//   k_salient_search   49 candidates x rows, deterministic reduction, first strict minimum
+//   k_salient_search_sorted  49 candidates x rows from prefix sums of the sorted rows, first strict minimum
 //   k_select_l1/l2/l3  exact radix selection (15+9+7 bits) of the 162 order statistics that
 //                      numpy.quantile(method="linear") interpolates between
 //   k_sort_rows        every metric row sorted (bitonic network), for the split search
@@ -45,7 +45,9 @@ constexpr int kL2Bins = 512;     // key bits 15..7
 constexpr int kL3Bins = 128;     // key bits 6..0
 constexpr int kMaxCtas1 = 148;   // CTAs of the metric kernel (one per SM at most)
 constexpr int kMaxTiles = 256;   // row tiles of the search kernels
-constexpr int kSearchThreads = 256;
+constexpr int kAccSlots = 136;   // 0..48 salient candidates, 49..129 split candidates, 130 salient-group term
+constexpr int kAccSplit = kSalCand, kAccSalTerm = kSalCand + kSplits;
+static_assert(kAccSalTerm < kAccSlots, "accumulator slots");
 
 // Device workspace of the block step, carved by carve_block_ws().
 struct BlockWs {
@@ -58,12 +60,14 @@ struct BlockWs {
     unsigned char* slot1;    // [kL1Bins] 0 = not a target bin, else level-1 slot + 1
     unsigned* hist2;         // [kTargets][kL2Bins]
     unsigned* hist3;         // [kTargets][kL3Bins]
+    unsigned long long* acc; // [kAccSlots] fixed-point candidate error sums (49 salient, 81 split, 1 salient term)
     // ---- scratch ----
     float* M;                // [R][128] metric
     float* sv;               // [R][128] every row of M sorted ascending
     unsigned char* sc;       // [R][128] the column of each sorted value
     double* colpart;         // [kMaxCtas1][128]
-    double* partial;         // [kSplits + 1][tile_stride]
+    double* energy;          // [kMaxCtas1] per-CTA sum of M^2 (bounds every candidate error)
+    double* fx;              // [2] fixed-point scale of the error sums and its inverse
     unsigned char* rank;     // [128] position of each column in the score order (>= 50: never salient)
     int* sel;                // [8]   0: i*   1: k*   2: level-1 slots   3: level-2 slots
     float* pvals;            // [kSplits + 1]  the 81 split candidates, [81] = chosen split
@@ -76,7 +80,6 @@ struct BlockWs {
     unsigned* l2_start;      // [kTargets + 1] per level-1 slot: first level-2 slot
     unsigned* l2_bin;        // [kTargets]     level-2 bin of each level-2 slot
     double* trace_dummy;     // [CRB_TRACE_DOUBLES] sink when the caller passes no trace
-    int tile_stride;
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -96,14 +99,15 @@ static size_t carve_block_ws(void* base, int R, BlockWs* ws) {
     w.slot1 = static_cast<unsigned char*>(take(kL1Bins));
     w.hist2 = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets * kL2Bins));
     w.hist3 = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets * kL3Bins));
+    w.acc = static_cast<unsigned long long*>(take(sizeof(unsigned long long) * kAccSlots));
     w.zero_begin = base ? static_cast<unsigned char*>(base) + z0 : nullptr;
     w.zero_bytes = off - z0;
     w.M = static_cast<float*>(take(sizeof(float) * (size_t)R * kBlock));
     w.sv = static_cast<float*>(take(sizeof(float) * (size_t)R * kBlock));
     w.sc = static_cast<unsigned char*>(take((size_t)R * kBlock));
     w.colpart = static_cast<double*>(take(sizeof(double) * kMaxCtas1 * kBlock));
-    w.tile_stride = kMaxTiles;
-    w.partial = static_cast<double*>(take(sizeof(double) * (kSplits + 1) * kMaxTiles));
+    w.energy = static_cast<double*>(take(sizeof(double) * kMaxCtas1));
+    w.fx = static_cast<double*>(take(sizeof(double) * 2));
     w.rank = static_cast<unsigned char*>(take(kBlock));
     w.sel = static_cast<int*>(take(sizeof(int) * 8));
     w.pvals = static_cast<float*>(take(sizeof(float) * (kSplits + 1)));
@@ -126,10 +130,11 @@ static size_t carve_block_ws(void* base, int R, BlockWs* ws) {
 __global__ void __launch_bounds__(256)
 k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
                   const float* __restrict__ U, int64_t ldu, int rows_per_cta,
-                  float* __restrict__ M, double* __restrict__ colpart, unsigned* counters,
-                  unsigned char* __restrict__ rank_out, double* __restrict__ trace,
-                  unsigned* status) {
+                  float* __restrict__ M, double* __restrict__ colpart, double* __restrict__ energy,
+                  double* __restrict__ fx, unsigned* counters, unsigned char* __restrict__ rank_out,
+                  double* __restrict__ trace, unsigned* status) {
     __shared__ float s_d2[kBlock];
+    __shared__ double s_e[8];
     __shared__ double s_wcol[8][kBlock];
     __shared__ double s_score[kBlock];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -143,22 +148,28 @@ k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
 #pragma unroll
     for (int j = 0; j < 16; ++j) { d2[j] = s_d2[col_of(l, j)]; csum[j] = 0.f; }
     bool bad = false;
+    double e2 = 0.0;
     const int row_base = blockIdx.x * rows_per_cta;
     for (int p = 0; p < rows_per_cta; p += 32) {
         const int row = row_base + p + warp * 4 + g;
         if (row < R && row < row_base + rows_per_cta) {
             float x[16];
             load_row16(W + (int64_t)row * ldw + col0, l, x);
+            float e = 0.f;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const float m = __fdiv_rn(__fmul_rn(x[j], x[j]), d2[j]);
                 bad |= !isfinite(m);
                 x[j] = m;
                 csum[j] += m;          // M >= 0, so |M| = M (autosearch.py:37)
+                e = fmaf(m, m, e);
             }
+            e2 += (double)e;
             store_row16(M + (int64_t)row * kBlock, l, x);
         }
     }
+    e2 = warp_sum_d(e2);
+    if (lane == 0) s_e[warp] = e2;
     if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(status, CRB_FLAG_NONFINITE);
     // sum the 4 rows of the warp, then the 8 warps, in double
 #pragma unroll
@@ -175,12 +186,33 @@ k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
         for (int w = 0; w < 8; ++w) v += s_wcol[w][tid];
         colpart[(size_t)blockIdx.x * kBlock + tid] = v;
     }
+    if (tid == 0) {
+        double v = 0.0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v += s_e[w];
+        energy[blockIdx.x] = v;
+    }
     if (!last_cta_done(&counters[0], gridDim.x)) return;
 
     if (tid < kBlock) {
         double v = 0.0;
+#pragma unroll 8
         for (unsigned c = 0; c < gridDim.x; ++c) v += __ldcg(&colpart[(size_t)c * kBlock + tid]);
         s_score[tid] = v;
+    }
+    if (warp == 4) {
+        // Candidate error sums are accumulated as 64-bit fixed point so that their value does not
+        // depend on the order in which CTAs add to them.  No candidate error exceeds sum(M^2):
+        // scale it to 2^61.
+        double v = 0.0;
+        for (unsigned c = lane; c < gridDim.x; c += 32) v += __ldcg(&energy[c]);
+        v = warp_sum_d(v);
+        if (lane == 0) {
+            int ex = 0;
+            if (v > 0.0 && isfinite(v)) frexp(v, &ex);
+            fx[0] = ldexp(1.0, 61 - ex);
+            fx[1] = ldexp(1.0, ex - 61);
+        }
     }
     __syncthreads();
     if (tid < kBlock) {
@@ -196,156 +228,12 @@ k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
 }
 
 // ---------------------------------------------------------------------------------------
-// Row evaluators of the searches: squared error of the braq residual binarizer
-// (binary.py:18-39) on column sets of one row held by 8 lanes.
+// Helpers shared by the two searches
 // ---------------------------------------------------------------------------------------
-// Order-2 expansion on the set S = {rank < i} and on its complement; returns the squared
-// error over all 128 columns (identical in the 8 lanes of the row).
-__device__ __forceinline__ float hor2_pair_err(const float (&x)[16], const int (&rk)[16], int i) {
-    const float nS = (float)i, nN = (float)(kBlock - i);
-    float sS = 0.f, sN = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const bool in = rk[j] < i;
-        sS += in ? x[j] : 0.f;
-        sN += in ? 0.f : x[j];
-    }
-    const float muS = __fdiv_rn(red8(sS), nS), muN = __fdiv_rn(red8(sN), nN);
-    float dv[16], y1[16];
-    float aS = 0.f, aN = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const bool in = rk[j] < i;
-        dv[j] = x[j] - (in ? muS : muN);
-        const float a = fabsf(dv[j]);
-        aS += in ? a : 0.f;
-        aN += in ? 0.f : a;
-    }
-    const float alS = __fdiv_rn(red8(aS), nS), alN = __fdiv_rn(red8(aN), nN);
-    float rS = 0.f, rN = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const bool in = rk[j] < i;
-        y1[j] = __fadd_rn((in ? alS : alN) * sgnf(dv[j]), in ? muS : muN);
-        const float r = x[j] - y1[j];
-        dv[j] = r;
-        rS += in ? r : 0.f;
-        rN += in ? 0.f : r;
-    }
-    const float mu2S = __fdiv_rn(red8(rS), nS), mu2N = __fdiv_rn(red8(rN), nN);
-    aS = 0.f; aN = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const bool in = rk[j] < i;
-        dv[j] = dv[j] - (in ? mu2S : mu2N);
-        const float a = fabsf(dv[j]);
-        aS += in ? a : 0.f;
-        aN += in ? 0.f : a;
-    }
-    const float al2S = __fdiv_rn(red8(aS), nS), al2N = __fdiv_rn(red8(aN), nN);
-    float err = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const bool in = rk[j] < i;
-        const float piece = __fadd_rn((in ? al2S : al2N) * sgnf(dv[j]), in ? mu2S : mu2N);
-        const float q = __fadd_rn(y1[j], piece);
-        const float d = x[j] - q;
-        err += d * d;
-    }
-    return red8(err);
-}
-
-// Order-2 expansion on S = {rank < i} only; squared error over S.
-__device__ __forceinline__ float hor2_single_err(const float (&x)[16], const int (&rk)[16], int i) {
-    const float n = (float)i;
-    float s = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) s += (rk[j] < i) ? x[j] : 0.f;
-    const float mu = __fdiv_rn(red8(s), n);
-    float dv[16], y1[16];
-    float a = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) { dv[j] = x[j] - mu; a += (rk[j] < i) ? fabsf(dv[j]) : 0.f; }
-    const float al = __fdiv_rn(red8(a), n);
-    s = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        y1[j] = __fadd_rn(al * sgnf(dv[j]), mu);
-        dv[j] = x[j] - y1[j];
-        s += (rk[j] < i) ? dv[j] : 0.f;
-    }
-    const float mu2 = __fdiv_rn(red8(s), n);
-    a = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) { dv[j] -= mu2; a += (rk[j] < i) ? fabsf(dv[j]) : 0.f; }
-    const float al2 = __fdiv_rn(red8(a), n);
-    float err = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const float q = __fadd_rn(y1[j], __fadd_rn(al2 * sgnf(dv[j]), mu2));
-        const float d = x[j] - q;
-        err += (rk[j] < i) ? d * d : 0.f;
-    }
-    return red8(err);
-}
-
-// Order-1 expansion on {non-salient, x < p} and on {non-salient, x >= p}; squared error over
-// the non-salient columns of the row (mask.py:7-18 + binary.py:18-39 with order 1).
-__device__ __forceinline__ float hor1_split_err(const float (&x)[16], const int (&rk)[16], int isal,
-                                                float p) {
-    float s1 = 0.f, s2 = 0.f;
-    int n1 = 0, n2 = 0;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const bool ns = rk[j] >= isal;
-        const bool lo = ns && (x[j] < p), hi = ns && (x[j] >= p);
-        s1 += lo ? x[j] : 0.f;
-        s2 += hi ? x[j] : 0.f;
-        n1 += lo; n2 += hi;
-    }
-    n1 = red8i(n1); n2 = red8i(n2);
-    s1 = red8(s1); s2 = red8(s2);               // reductions stay outside row-dependent branches
-    const float mu1 = n1 ? __fdiv_rn(s1, (float)n1) : 0.f;   // empty side: nanmean -> 0 (binary.py:29)
-    const float mu2 = n2 ? __fdiv_rn(s2, (float)n2) : 0.f;
-    float dv[16];
-    float a1 = 0.f, a2 = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const bool ns = rk[j] >= isal;
-        const bool lo = ns && (x[j] < p), hi = ns && (x[j] >= p);
-        dv[j] = x[j] - (lo ? mu1 : mu2);
-        const float a = fabsf(dv[j]);
-        a1 += lo ? a : 0.f;
-        a2 += hi ? a : 0.f;
-    }
-    a1 = red8(a1); a2 = red8(a2);
-    const float al1 = n1 ? __fdiv_rn(a1, (float)n1) : 0.f;
-    const float al2 = n2 ? __fdiv_rn(a2, (float)n2) : 0.f;
-    float err = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const bool ns = rk[j] >= isal;
-        const bool lo = ns && (x[j] < p), hi = ns && (x[j] >= p);
-        const float q = __fadd_rn((lo ? al1 : al2) * sgnf(dv[j]), lo ? mu1 : mu2);
-        const float d = x[j] - q;
-        // a non-salient NaN belongs to neither side and is reconstructed as 0
-        err += (lo || hi) ? d * d : (ns ? x[j] * x[j] : 0.f);
-    }
-    return red8(err);
-}
-
-// Sums partial[c][0..n_tiles) for c in [0, n_cand) with a fixed order (one warp per
-// candidate: lane-strided sequential sums, then a butterfly), result in s_out[c].
-__device__ void reduce_partials(const double* __restrict__ partial, int tile_stride, int n_tiles,
-                                int n_cand, double* s_out) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    for (int c = warp; c < n_cand; c += nw) {
-        double v = 0.0;
-        for (int t = lane; t < n_tiles; t += 32) v += __ldcg(&partial[(size_t)c * tile_stride + t]);
-        v = warp_sum_d(v);
-        if (lane == 0) s_out[c] = v;
-    }
-    __syncthreads();
+// Adds a non-negative float64 partial sum to a fixed-point accumulator (order independent).
+__device__ __forceinline__ void acc_add(unsigned long long* acc, double v, double scale) {
+    const unsigned long long q = __double2ull_rn(fmax(v, 0.0) * scale);
+    if (q) atomicAdd(acc, q);
 }
 
 // First strict minimum (autosearch.py:53, :78) and the relative gap to the runner-up.
@@ -359,64 +247,6 @@ __device__ void first_strict_min(const double* e, int n, int fallback, int* best
         if (c != best && e[c] < second) second = e[c];
     *best_out = best < 0 ? fallback : best;
     *gap_out = (best < 0 || !(be > 0.0)) ? 0.0 : (second - be) / be;
-}
-
-// ---------------------------------------------------------------------------------------
-// K2: salient-count search                                           (autosearch.py:44-55)
-// grid (row tiles, candidate chunks); each CTA: rows_per_cta rows x `chunk` candidates.
-// ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kSearchThreads)
-k_salient_search(const float* __restrict__ M, int R, int rows_per_cta, int chunk,
-                 const unsigned char* __restrict__ rank, double* __restrict__ partial,
-                 int tile_stride, unsigned* counters, int* __restrict__ sel,
-                 double* __restrict__ trace, unsigned* status) {
-    __shared__ double s_acc[kSalCand][32];
-    __shared__ double s_tot[kSalCand];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = row_in_warp(lane), l = lane_in_row(lane);
-    const int c0 = blockIdx.y * chunk;
-    const int nc = min(chunk, kSalCand - c0);
-    for (int k = tid; k < kSalCand * 32; k += blockDim.x) (&s_acc[0][0])[k] = 0.0;
-    int rk[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) rk[j] = rank[col_of(l, j)];
-    __syncthreads();
-    const int row_base = blockIdx.x * rows_per_cta;
-    for (int p = 0; p < rows_per_cta; p += 32) {
-        const int row = row_base + p + warp * 4 + g;
-        float x[16];
-        if (row < R) {
-            load_row16(M + (int64_t)row * kBlock, l, x);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) x[j] = 0.f;
-        }
-        for (int c = 0; c < nc; ++c) {
-            const float e = hor2_pair_err(x, rk, c0 + c + 1);
-            if (l == 0) s_acc[c][warp * 4 + g] += (double)e;
-        }
-    }
-    __syncthreads();
-    if (tid < nc) {
-        double v = 0.0;
-#pragma unroll
-        for (int k = 0; k < 32; ++k) v += s_acc[tid][k];
-        partial[(size_t)(c0 + tid) * tile_stride + blockIdx.x] = v;
-    }
-    if (!last_cta_done(&counters[1], gridDim.x * gridDim.y)) return;
-
-    reduce_partials(partial, tile_stride, gridDim.x, kSalCand, s_tot);
-    if (tid == 0) {
-        int best; double gap;
-        first_strict_min(s_tot, kSalCand, max(1, kSalLimit / 3) - 1, &best, &gap);
-        sel[0] = best + 1;
-        trace[0] = (double)(best + 1);
-        trace[3] = gap;
-        bool bad = false;
-        const double inv = 1.0 / ((double)R * kBlock);
-        for (int c = 0; c < kSalCand; ++c) { trace[56 + c] = s_tot[c] * inv; bad |= !isfinite(s_tot[c]); }
-        if (bad) atomicOr(status, CRB_FLAG_NONFINITE);
-    }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -454,7 +284,7 @@ __device__ __forceinline__ unsigned block_exclusive_scan_1024(unsigned v, unsign
 __global__ void __launch_bounds__(1024)
 k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
             const int* __restrict__ sel, BlockWs ws) {
-    extern __shared__ unsigned s_hist[];           // kL1Bins
+    extern __shared__ __align__(16) unsigned s_hist[];   // kL1Bins
     __shared__ unsigned s_warp[32];
     __shared__ unsigned s_tbin[kTargets];
     __shared__ bool s_sal[kBlock];
@@ -482,7 +312,17 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
     // ---- scan + locate the 162 target ranks ----
     const unsigned N = (unsigned)R * kBlock;
     const unsigned zeros = (unsigned)R * (unsigned)isal;
-    for (int k = tid; k < kL1Bins; k += blockDim.x) s_hist[k] = __ldcg(&ws.hist1[k]) + (k == 0 ? zeros : 0u);
+    {
+        // 32768 counters as 8 independent 16-byte loads per thread
+        const uint4* src = reinterpret_cast<const uint4*>(ws.hist1);
+        uint4 h[kL1Bins / 4 / 1024];
+#pragma unroll
+        for (int u = 0; u < kL1Bins / 4 / 1024; ++u) h[u] = __ldcg(&src[tid + 1024 * u]);
+#pragma unroll
+        for (int u = 0; u < kL1Bins / 4 / 1024; ++u) reinterpret_cast<uint4*>(s_hist)[tid + 1024 * u] = h[u];
+        __syncthreads();
+        if (tid == 0) s_hist[0] += zeros;
+    }
     __syncthreads();
     {
         unsigned loc = 0;
@@ -516,14 +356,21 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
         ws.tgt_rem[tid] = r - s_hist[lo];
     }
     __syncthreads();
-    if (tid == 0) {
-        unsigned slot = 0;
-        for (int t = 0; t < kTargets; ++t) {
-            if (t > 0 && s_tbin[t] != s_tbin[t - 1]) ++slot;
-            ws.tgt_slot[t] = slot;
-            ws.slot1[s_tbin[t]] = (unsigned char)(slot + 1);
+    // level-1 slots: the number of distinct bins before each target (targets are rank ordered)
+    if (tid < 32) {
+        unsigned base = 0;
+        for (int t0 = 0; t0 < kTargets; t0 += 32) {
+            const int t = t0 + tid;
+            const bool fresh = t < kTargets && t > 0 && s_tbin[t] != s_tbin[t - 1];
+            const unsigned m = __ballot_sync(0xffffffffu, fresh);
+            if (t < kTargets) {
+                const unsigned slot = base + __popc(m & (0xffffffffu >> (31 - tid)));
+                ws.tgt_slot[t] = slot;
+                ws.slot1[s_tbin[t]] = (unsigned char)(slot + 1);
+                if (t == kTargets - 1) ws.sel[2] = (int)slot + 1;
+            }
+            base += __popc(m);
         }
-        ws.sel[2] = (int)slot + 1;
     }
 }
 
@@ -565,7 +412,8 @@ __global__ void __launch_bounds__(512)
 k_select_l2(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
             const int* __restrict__ sel, BlockWs ws) {
     __shared__ bool s_sal[kBlock];
-    __shared__ unsigned s_bin2[kTargets];
+    __shared__ unsigned s_bin2[kTargets], s_slot1[kTargets], s_rem[kTargets], s_slot2[kTargets];
+    __shared__ unsigned s_l2start[kTargets + 1], s_l2bin[kTargets];
     const int tid = threadIdx.x;
     const int isal = sel[0];
     if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
@@ -591,30 +439,35 @@ k_select_l2(const float* __restrict__ M, int R, const unsigned char* __restrict_
     }
     __syncthreads();
     const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+    if (tid < kTargets) { s_slot1[tid] = ws.tgt_slot[tid]; s_rem[tid] = ws.tgt_rem[tid]; }
+    __syncthreads();
     for (int t = warp; t < kTargets; t += nw) {
         unsigned bin, left;
-        warp_locate<kL2Bins / 32>(ws.hist2 + (size_t)ws.tgt_slot[t] * kL2Bins, ws.tgt_rem[t], &bin, &left);
-        if (lane == 0) { s_bin2[t] = bin; ws.tgt_bin2[t] = bin; ws.tgt_rem[t] = left; }
+        warp_locate<kL2Bins / 32>(ws.hist2 + (size_t)s_slot1[t] * kL2Bins, s_rem[t], &bin, &left);
+        if (lane == 0) { s_bin2[t] = bin; s_rem[t] = left; }
     }
     __syncthreads();
     if (tid == 0) {
-        // level-2 slots: distinct (level-1 slot, bin2) pairs in rank order
+        // level-2 slots: distinct (level-1 slot, bin2) pairs in rank order (shared memory only)
         unsigned slot2 = 0, prev1 = 0xffffffffu;
         for (int t = 0; t < kTargets; ++t) {
-            const unsigned s1 = ws.tgt_slot[t];
+            const unsigned s1 = s_slot1[t];
             const bool fresh = (t == 0) || s1 != prev1 || s_bin2[t] != s_bin2[t - 1];
             if (t > 0 && fresh) ++slot2;
-            if (s1 != prev1) {
-                // every level-1 slot between prev1 and s1 starts here (slots are consecutive)
-                ws.l2_start[s1] = slot2;
-                prev1 = s1;
-            }
-            if (fresh) ws.l2_bin[slot2] = s_bin2[t];
-            ws.tgt_slot[t] = slot2;
+            if (s1 != prev1) { s_l2start[s1] = slot2; prev1 = s1; }   // level-1 slots are consecutive
+            if (fresh) s_l2bin[slot2] = s_bin2[t];
+            s_slot2[t] = slot2;
         }
-        ws.l2_start[prev1 + 1] = slot2 + 1;
+        s_l2start[prev1 + 1] = slot2 + 1;
         ws.sel[3] = (int)slot2 + 1;
+        ws.sel[2] = (int)prev1 + 1;
     }
+    __syncthreads();
+    if (tid < kTargets) {
+        ws.tgt_bin2[tid] = s_bin2[tid]; ws.tgt_rem[tid] = s_rem[tid]; ws.tgt_slot[tid] = s_slot2[tid];
+        ws.l2_bin[tid] = s_l2bin[tid];
+    }
+    if (tid <= kTargets) ws.l2_start[tid] = s_l2start[tid];
 }
 
 // Level 3: key bits 6..0, then the 81 interpolated split candidates.
@@ -655,11 +508,16 @@ k_select_l3(const float* __restrict__ M, int R, const unsigned char* __restrict_
     }
     __syncthreads();
     const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+    __shared__ unsigned s_slot[kTargets], s_rem[kTargets], s_hi[kTargets];
+    if (tid < kTargets) {
+        s_slot[tid] = ws.tgt_slot[tid]; s_rem[tid] = ws.tgt_rem[tid];
+        s_hi[tid] = (ws.tgt_bin1[tid] << 16) | (ws.tgt_bin2[tid] << 7);
+    }
+    __syncthreads();
     for (int t = warp; t < kTargets; t += nw) {
         unsigned bin, left;
-        warp_locate<kL3Bins / 32>(ws.hist3 + (size_t)ws.tgt_slot[t] * kL3Bins, ws.tgt_rem[t], &bin, &left);
-        if (lane == 0)
-            s_val[t] = __uint_as_float((ws.tgt_bin1[t] << 16) | (ws.tgt_bin2[t] << 7) | bin);
+        warp_locate<kL3Bins / 32>(ws.hist3 + (size_t)s_slot[t] * kL3Bins, s_rem[t], &bin, &left);
+        if (lane == 0) s_val[t] = __uint_as_float(s_hi[t] | bin);
     }
     __syncthreads();
     if (tid < kSplits) {
@@ -779,9 +637,9 @@ __device__ __forceinline__ double range_order1_err(const float* v, const double*
 __global__ void __launch_bounds__(256)
 k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restrict__ sc, int R,
                       int rows_per_cta, const unsigned char* __restrict__ rank,
-                      const float* __restrict__ pvals_in, double* __restrict__ partial, int tile_stride,
-                      unsigned* counters, int* __restrict__ sel, float* __restrict__ pvals_out,
-                      double* __restrict__ trace, unsigned* status) {
+                      const float* __restrict__ pvals_in, unsigned long long* __restrict__ acc,
+                      const double* __restrict__ fx, unsigned* counters, int* __restrict__ sel,
+                      float* __restrict__ pvals_out, double* __restrict__ trace, unsigned* status) {
     extern __shared__ __align__(16) unsigned char s_raw[];
     double* s_P1 = reinterpret_cast<double*>(s_raw);                         // [rows][pitch]
     double* s_P2 = s_P1 + kSplitRows * kRowPitch;
@@ -903,11 +761,12 @@ k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restr
         double t = 0.0;
 #pragma unroll 8
         for (int r = 0; r < kSplitRows; ++r) t += s_acc[tid * kSplitRows + r];
-        partial[(size_t)tid * tile_stride + blockIdx.x] = t;
+        acc_add(&acc[kAccSplit + tid], t, fx[0]);        // slot kAccSplit + 81 is the salient-group term
     }
     if (!last_cta_done(&counters[5], gridDim.x)) return;
 
-    reduce_partials(partial, tile_stride, gridDim.x, kSplits + 1, s_tot);
+    if (tid <= kSplits) s_tot[tid] = (double)__ldcg(&acc[kAccSplit + tid]) * fx[1];
+    __syncthreads();
     if (tid == 0) {
         int best; double gap;
         const double e3 = s_tot[kSplits];
@@ -923,6 +782,183 @@ k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restr
         trace[5] = e3 * inv;
         bool bad = false;
         for (int c = 0; c < kSplits; ++c) { trace[105 + c] = s_tot[c] * inv; bad |= !isfinite(s_tot[c]); }
+        if (bad) atomicOr(status, CRB_FLAG_NONFINITE);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// K2: salient-count search on sorted rows                              (autosearch.py:44-55)
+//
+// Candidate i moves the i highest-score columns into the salient set S_i.  Per row:
+//  * S_i (at most 49 values, kept in score order) is evaluated directly;
+//  * the complement is the whole sorted row minus those i values ("holes"): any count / sum /
+//    sum of squares below a threshold is a prefix-sum lookup on the whole row minus a pass over
+//    the holes.  The order-2 expansion (binary.py:18-39) needs three thresholds: mu1, and the
+//    second-pass split points y1 + mu2 of the elements below / above mu1.
+// One thread per (row, candidate); the 32 lanes of a warp share the candidate, so the hole
+// loops have the same length across the warp.
+// ---------------------------------------------------------------------------------------
+constexpr int kSalRows = 32;
+constexpr int kTopPitch = kSalLimit + 1;
+constexpr int kSalSmem = kSalRows * kRowPitch * (int)(sizeof(float) + 2 * sizeof(double)) +
+                         kSalRows * kTopPitch * (int)sizeof(float) + kSalCand * kSalRows * (int)sizeof(double);
+
+__device__ __forceinline__ int lower_bound_d(const float* v, int n, double t) {
+    int lo = 0, len = n;                         // first index with v[idx] >= t
+    while (len > 0) {
+        const int half = len >> 1;
+        if ((double)v[lo + half] < t) { lo += half + 1; len -= half + 1; } else { len = half; }
+    }
+    return lo;
+}
+
+__device__ __forceinline__ double salient_candidate_err(const float* v, const double* P1, const double* P2,
+                                                        const float* tv, int i) {
+    const int n = kBlock - i;
+    // ---- the complement of the i top columns ----
+    double H1 = 0.0, H2 = 0.0;
+    for (int h = 0; h < i; ++h) { const double t = (double)tv[h]; H1 += t; H2 += t * t; }
+    const double S1 = P1[kBlock] - H1, S2 = P2[kBlock] - H2;
+    const float mu1 = __fdiv_rn((float)S1, (float)n);
+    int cf = lower_bound_f(v, 0, kBlock, mu1);
+    double c1 = (double)cf, a1 = P1[cf], b1 = P2[cf];
+    for (int h = 0; h < i; ++h) {
+        const float t = tv[h];
+        if (t < mu1) { c1 -= 1.0; a1 -= (double)t; b1 -= (double)t * (double)t; }
+    }
+    const double dmu1 = (double)mu1, dn = (double)n;
+    const double A1 = dmu1 * c1 - a1 + (S1 - a1) - dmu1 * (dn - c1);
+    const float al1 = __fdiv_rn((float)A1, (float)n);
+    const float ylo = __fadd_rn(-al1, mu1), yhi = __fadd_rn(al1, mu1);
+    const double sr = (a1 - c1 * (double)ylo) + ((S1 - a1) - (dn - c1) * (double)yhi);
+    const float mu2 = __fdiv_rn((float)sr, (float)n);
+    const double tlo = (double)ylo + (double)mu2, thi = (double)yhi + (double)mu2;
+    const double t1 = fmin(tlo, dmu1), t2 = fmax(thi, dmu1);
+    cf = lower_bound_d(v, kBlock, t1);
+    double c2 = (double)cf, a2 = P1[cf];
+    cf = lower_bound_d(v, kBlock, t2);
+    double c3 = (double)cf, a3 = P1[cf];
+    for (int h = 0; h < i; ++h) {
+        const double t = (double)tv[h];
+        if (t < t1) { c2 -= 1.0; a2 -= t; }
+        if (t < t2) { c3 -= 1.0; a3 -= t; }
+    }
+    c3 -= c1; a3 -= a1;                                     // elements in [mu1, t2)
+    const double cu = dn - c1, au = S1 - a1, bu = S2 - b1;  // the group at or above mu1
+    const double A2 = (tlo * c2 - a2 + (a1 - a2) - tlo * (c1 - c2)) + (thi * c3 - a3 + (au - a3) - thi * (cu - c3));
+    const double al2 = (double)__fdiv_rn((float)A2, (float)n);
+    const double SS = (b1 - 2.0 * tlo * a1 + c1 * tlo * tlo) + (bu - 2.0 * thi * au + cu * thi * thi);
+    double err = SS - 2.0 * al2 * A2 + dn * al2 * al2;
+    // ---- the i top columns themselves, evaluated like the reference in float32 ----
+    const float fi = (float)i;
+    float s = 0.f;
+    for (int h = 0; h < i; ++h) s += tv[h];
+    const float mu = __fdiv_rn(s, fi);
+    float a = 0.f;
+    for (int h = 0; h < i; ++h) a += fabsf(tv[h] - mu);
+    const float al = __fdiv_rn(a, fi);
+    s = 0.f;
+    for (int h = 0; h < i; ++h) s += tv[h] - __fadd_rn(al * sgnf(tv[h] - mu), mu);
+    const float m2 = __fdiv_rn(s, fi);
+    a = 0.f;
+    for (int h = 0; h < i; ++h) a += fabsf((tv[h] - __fadd_rn(al * sgnf(tv[h] - mu), mu)) - m2);
+    const float al2s = __fdiv_rn(a, fi);
+    float e = 0.f;
+    for (int h = 0; h < i; ++h) {
+        const float y1 = __fadd_rn(al * sgnf(tv[h] - mu), mu);
+        const float r = (tv[h] - y1) - m2;
+        const float d = tv[h] - __fadd_rn(y1, __fadd_rn(al2s * sgnf(r), m2));
+        e = fmaf(d, d, e);
+    }
+    return err + (double)e;
+}
+
+__global__ void __launch_bounds__(256)
+k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __restrict__ sc, int R,
+                        int rows_per_cta, const unsigned char* __restrict__ rank,
+                        unsigned long long* __restrict__ acc, const double* __restrict__ fx,
+                        unsigned* counters, int* __restrict__ sel, double* __restrict__ trace,
+                        unsigned* status) {
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    double* s_P1 = reinterpret_cast<double*>(s_raw);                         // [rows][pitch]
+    double* s_P2 = s_P1 + kSalRows * kRowPitch;
+    double* s_acc = s_P2 + kSalRows * kRowPitch;                             // [kSalCand][rows]
+    float* s_v = reinterpret_cast<float*>(s_acc + kSalCand * kSalRows);      // [rows][pitch]
+    float* s_tv = s_v + kSalRows * kRowPitch;                                // [rows][kTopPitch]
+    __shared__ unsigned char s_rank[kBlock];
+    __shared__ double s_tot[kSalCand];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < kBlock) s_rank[tid] = rank[tid];
+    for (int k = tid; k < kSalCand * kSalRows; k += blockDim.x) s_acc[k] = 0.0;
+    __syncthreads();
+    const int row_base = blockIdx.x * rows_per_cta;
+    for (int p0 = 0; p0 < rows_per_cta; p0 += kSalRows) {
+        // ---- phase A: one warp per row: sorted values, float64 prefix sums, top-column values ----
+        for (int r = warp; r < kSalRows; r += 8) {
+            const int row = row_base + p0 + r;
+            float x[4] = {0.f, 0.f, 0.f, 0.f};
+            uchar4 c = make_uchar4(0, 0, 0, 0);
+            if (row < R) {
+                const float4 v = *reinterpret_cast<const float4*>(sv + (int64_t)row * kBlock + 4 * lane);
+                c = *reinterpret_cast<const uchar4*>(sc + (int64_t)row * kBlock + 4 * lane);
+                x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+            }
+            const unsigned char cc[4] = {c.x, c.y, c.z, c.w};
+            float* vrow = s_v + r * kRowPitch;
+            double l1 = 0.0, l2 = 0.0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                vrow[4 * lane + q] = x[q];
+                l1 += (double)x[q]; l2 += (double)x[q] * (double)x[q];
+                const int rk = s_rank[cc[q]];
+                if (row < R && rk < kSalLimit) s_tv[r * kTopPitch + rk] = x[q];
+            }
+            double i1 = l1, i2 = l2;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const double t1 = __shfl_up_sync(0xffffffffu, i1, o);
+                const double t2 = __shfl_up_sync(0xffffffffu, i2, o);
+                if (lane >= o) { i1 += t1; i2 += t2; }
+            }
+            double r1 = i1 - l1, r2 = i2 - l2;
+            double* P1 = s_P1 + r * kRowPitch;
+            double* P2 = s_P2 + r * kRowPitch;
+            if (lane == 0) { P1[0] = 0.0; P2[0] = 0.0; }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                r1 += (double)x[q]; r2 += (double)x[q] * (double)x[q];
+                P1[4 * lane + q + 1] = r1; P2[4 * lane + q + 1] = r2;
+            }
+        }
+        __syncthreads();
+        // ---- phase B: one thread per (row, candidate) ----
+        for (int task = tid; task < kSalRows * kSalCand; task += blockDim.x) {
+            const int r = task % kSalRows, cand = task / kSalRows;
+            if (row_base + p0 + r >= R) continue;
+            s_acc[cand * kSalRows + r] += salient_candidate_err(s_v + r * kRowPitch, s_P1 + r * kRowPitch,
+                                                                s_P2 + r * kRowPitch, s_tv + r * kTopPitch, cand + 1);
+        }
+        __syncthreads();
+    }
+    if (tid < kSalCand) {
+        double t = 0.0;
+#pragma unroll 8
+        for (int r = 0; r < kSalRows; ++r) t += s_acc[tid * kSalRows + r];
+        acc_add(&acc[tid], t, fx[0]);
+    }
+    if (!last_cta_done(&counters[1], gridDim.x)) return;
+
+    if (tid < kSalCand) s_tot[tid] = (double)__ldcg(&acc[tid]) * fx[1];
+    __syncthreads();
+    if (tid == 0) {
+        int best; double gap;
+        first_strict_min(s_tot, kSalCand, max(1, kSalLimit / 3) - 1, &best, &gap);
+        sel[0] = best + 1;
+        trace[0] = (double)(best + 1);
+        trace[3] = gap;
+        bool bad = false;
+        const double inv = 1.0 / ((double)R * kBlock);
+        for (int c = 0; c < kSalCand; ++c) { trace[56 + c] = s_tot[c] * inv; bad |= !isfinite(s_tot[c]); }
         if (bad) atomicOr(status, CRB_FLAG_NONFINITE);
     }
 }
@@ -1249,7 +1285,9 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
         if (cudaFuncSetAttribute(k_select_l1, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kL1Bins * (int)sizeof(unsigned)) != cudaSuccess ||
             cudaFuncSetAttribute(k_split_search_sorted, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kSplitSmem) != cudaSuccess)
+                                 kSplitSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(k_salient_search_sorted, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kSalSmem) != cudaSuccess)
             return CRB_ERR_LAUNCH;
         attr_set = true;
     }
@@ -1258,18 +1296,14 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
     // K1
     const int rows1 = 32 * ceil_div(R, 32 * kMaxCtas1);
     k_metric_colscore<<<ceil_div(R, rows1), 256, 0, st>>>(W, R, ldw, col0, U, ldu, rows1, ws.M, ws.colpart,
-                                                          ws.counters, ws.rank, tr, ws.status);
+                                                          ws.energy, ws.fx, ws.counters, ws.rank, tr, ws.status);
     CRB_LAUNCHED();
     k_sort_rows<<<ceil_div(R, 8), 256, 0, st>>>(ws.M, R, ws.sv, ws.sc);
     CRB_LAUNCHED();
-    // K2 tiling: <= kMaxTiles row tiles, candidate chunks so that the grid fills the GPU
-    const int rows_s = 32 * ceil_div(R, 32 * kMaxTiles);
-    const int tiles = ceil_div(R, rows_s);
-    const int want_chunks = max(1, ceil_div(4 * 148, tiles));
-    const int chunks_sal = min(want_chunks, ceil_div(kSalCand, 4));
-    const int chunk_sal = ceil_div(kSalCand, chunks_sal);
-    k_salient_search<<<dim3(tiles, ceil_div(kSalCand, chunk_sal)), kSearchThreads, 0, st>>>(
-        ws.M, R, rows_s, chunk_sal, ws.rank, ws.partial, ws.tile_stride, ws.counters, ws.sel, tr, ws.status);
+    // K2: salient-count search on the sorted rows (<= kMaxTiles CTAs)
+    const int rows_sal = kSalRows * ceil_div(R, kSalRows * kMaxTiles);
+    k_salient_search_sorted<<<ceil_div(R, rows_sal), 256, kSalSmem, st>>>(
+        ws.sv, ws.sc, R, rows_sal, ws.rank, ws.acc, ws.fx, ws.counters, ws.sel, tr, ws.status);
     CRB_LAUNCHED();
     // K3-K5
     const int n4 = R * (kBlock / 4);
@@ -1284,8 +1318,7 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
     // K6: split search on the sorted rows
     const int rows_sp = kSplitRows * ceil_div(R, kSplitRows * kMaxTiles);
     k_split_search_sorted<<<ceil_div(R, rows_sp), 256, kSplitSmem, st>>>(
-        ws.sv, ws.sc, R, rows_sp, ws.rank, ws.pvals, ws.partial, ws.tile_stride, ws.counters, ws.sel, ws.pvals,
-        tr, ws.status);
+        ws.sv, ws.sc, R, rows_sp, ws.rank, ws.pvals, ws.acc, ws.fx, ws.counters, ws.sel, ws.pvals, tr, ws.status);
     CRB_LAUNCHED();
     // K7
     k_finalize<<<ceil_div(R, 32), 256, 0, st>>>(W, R, ldw, col0, U, ldu, ws.rank, ws.sel, ws.pvals, technique,
