@@ -247,6 +247,255 @@ k_hessian_umma(const __grid_constant__ CUtensorMap map0, const __grid_constant__
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Two-CTA variant: a cluster of two CTAs (two SMs) computes one 256 x 256 output tile with
+// tcgen05.mma.cta_group::2.  CTA r of the pair loads the operand rows r*128..r*128+127 of the M
+// side and of the N side, so every CTA stages 256 channel rows per 256 x 256 x K of work instead
+// of 384 per 128 x 256 x K: a third less L2 -> shared-memory traffic per flop, which is what
+// limits the single-CTA kernel.  The leader (cluster rank 0) issues all MMAs; both CTAs' TMA
+// copies report to the leader's "full" barrier; MMA completion is committed to the barriers of
+// both CTAs (two plain commits, no multicast); each CTA drains its own 128 accumulator rows.
+// ---------------------------------------------------------------------------------------------
+constexpr int H2_STAGES = 6;
+constexpr int H2_HALF_BYTES = 2 * HT_BOX_BYTES;                 // 128 channels x 64 tokens = 16 KiB
+constexpr int H2_STAGE_BYTES = 2 * H2_HALF_BYTES;               // A half + B half = 32 KiB per CTA
+constexpr int H2_SMEM = H2_STAGES * H2_STAGE_BYTES + 1024 + 256;
+constexpr int H2_TILE = 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// TMA load of one CTA of a pair; the completion bytes go to `cluster_bar`, which may live in the peer.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)acc) : "memory");
+}
+// Arrives on `cluster_bar` (any CTA of the cluster) once all MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+// Linear index over the upper-triangle 256 x 256 tiles, row by row.
+__device__ __forceinline__ void pair_tile_coords(int t, int nt, int* mi, int* nj) {
+    int m = 0;
+    while (t >= nt - m) { t -= nt - m; ++m; }
+    *mi = m; *nj = m + t;
+}
+
+__global__ void __launch_bounds__(HT_THREADS, 1)
+k_hessian_umma_pair(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
+                    const HessArgs args) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + H2_STAGES * H2_STAGE_BYTES);
+    // bars[0..S) full (used in the leader), [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty (leader)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * H2_STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * H2_STAGES;
+    const uint32_t tfull0 = empty0 + 8 * H2_STAGES, tempty0 = tfull0 + 16;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < H2_STAGES; ++s) { mbar_init(full0 + 8 * s, 2); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 16); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc_pair(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                       // the peer's barriers exist before anything remote touches them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int n_chunks = (int)((args.T + args.chunk_tokens - 1) / args.chunk_tokens);
+    const int pairs = gridDim.x >> 1;
+    const int pair = (int)cluster_id_x();
+    const int nt = args.n_col_tiles;          // 256-wide tiles per dimension
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs): own 128 rows of the M side and of the N side ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int t = pair; t < args.n_tiles && ok; t += pairs) {
+                int mi, nj;
+                pair_tile_coords(t, nt, &mi, &nj);
+                const int ca = mi * H2_TILE + (int)rank * 128, cb = nj * H2_TILE + (int)rank * 128;
+                for (int ch = 0; ch < n_chunks && ok; ++ch) {
+                    const int64_t t0 = (int64_t)ch * args.chunk_tokens;
+                    const int64_t t1 = min(args.T, t0 + args.chunk_tokens);
+                    for (int p = 0; p < args.n_pass && ok; ++p) {
+                        const CUtensorMap* ma = (p == 2) ? &map1 : &map0;
+                        const CUtensorMap* mb = (p == 1) ? &map1 : &map0;
+                        for (int64_t tk = t0; tk < t1; tk += HT_K) {
+                            ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag);
+                            if (!ok) break;
+                            const uint32_t sa = smem_u32(smem + stage * H2_STAGE_BYTES);
+                            const uint32_t sb = sa + H2_HALF_BYTES;
+                            const uint32_t fb = map_to_cta(full0 + 8 * stage, 0);      // the leader's barrier
+                            mbar_expect_tx_cluster(fb, H2_STAGE_BYTES);
+#pragma unroll
+                            for (int b = 0; b < 2; ++b) {
+                                tma_load_2d_pair(sa + b * HT_BOX_BYTES, ma, ca + b * HT_BOX, (int)tk, fb);
+                                tma_load_2d_pair(sb + b * HT_BOX_BYTES, mb, cb + b * HT_BOX, (int)tk, fb);
+                            }
+                            if (++stage == H2_STAGES) { stage = 0; phase ^= 1; }
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: the leader CTA only ----------------
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = f16_idesc(args.ab_format, 2 * HT_M, HT_N);
+            uint32_t stage = 0, phase = 0, unit = 0;
+            bool ok = true;
+            for (int t = pair; t < args.n_tiles && ok; t += pairs) {
+                for (int ch = 0; ch < n_chunks && ok; ++ch, ++unit) {
+                    const uint32_t buf = unit & 1, use = unit >> 1;
+                    ok = mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + buf * HT_N;
+                    const int64_t t0 = (int64_t)ch * args.chunk_tokens;
+                    const int64_t t1 = min(args.T, t0 + args.chunk_tokens);
+                    bool first = true;
+                    for (int p = 0; p < args.n_pass && ok; ++p) {
+                        for (int64_t tk = t0; tk < t1; tk += HT_K) {
+                            ok = mbar_wait(full0 + 8 * stage, phase, abort_flag);
+                            if (!ok) break;
+                            tc_fence_after();
+                            const uint32_t sa = smem_u32(smem + stage * H2_STAGE_BYTES);
+                            const uint32_t sb = sa + H2_HALF_BYTES;
+#pragma unroll
+                            for (int k = 0; k < HT_K / 16; ++k) {
+                                const uint64_t da = mn_sw128_desc(sa + k * 2048, HT_BOX_BYTES, 1024);
+                                const uint64_t db = mn_sw128_desc(sb + k * 2048, HT_BOX_BYTES, 1024);
+                                umma_f16_pair(d_tmem, da, db, idesc, !first);
+                                first = false;
+                            }
+                            umma_commit_pair(empty0 + 8 * stage);                       // frees the stage here ...
+                            umma_commit_pair(map_to_cta(empty0 + 8 * stage, 1));        // ... and in the peer
+                            if (++stage == H2_STAGES) { stage = 0; phase ^= 1; }
+                        }
+                    }
+                    if (ok) {
+                        umma_commit_pair(tfull0 + 8 * buf);
+                        umma_commit_pair(map_to_cta(tfull0 + 8 * buf, 1));
+                    }
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue (both CTAs): own 128 accumulator rows, all 256 columns.
+        // Each token chunk's TMEM accumulator is folded into float32 registers (round to nearest);
+        // S is read and written once per tile, after the last chunk. ----------------
+        const int q = warp & 3;
+        const int c_begin = ((warp - 2) >> 2) * (HT_N / 2);
+        const float scale = args.inv_scale2 ? *args.inv_scale2 : 1.0f;
+        const uint32_t tempty_leader = map_to_cta(tempty0, 0);
+        uint32_t unit = 0;
+        bool ok = true;
+        for (int t = pair; t < args.n_tiles && ok; t += pairs) {
+            int mi, nj;
+            pair_tile_coords(t, nt, &mi, &nj);
+            const int row = mi * H2_TILE + (int)rank * 128 + q * 32 + lane;
+            float acc[4][32];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[u][j] = 0.f;
+            for (int ch = 0; ch < n_chunks && ok; ++ch, ++unit) {
+                const uint32_t buf = unit & 1, use = unit >> 1;
+                ok = mbar_wait(tfull0 + 8 * buf, use & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * HT_N + c_begin;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    float v[32];
+                    tmem_ld32(taddr + 32 * u, v);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[u][j] += v[j];
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * buf);
+            }
+            if (!ok) break;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int col = nj * H2_TILE + c_begin + 32 * u;
+                // only columns at or right of this row's diagonal are ever read back
+                if (row < args.C && col < args.C && col + 31 >= row) {
+                    float4* dst = reinterpret_cast<float4*>(args.S + (int64_t)row * args.C + col);
+                    float4 o[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o[j] = dst[j];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        o[j].x = fmaf(acc[u][4 * j + 0], scale, o[j].x); o[j].y = fmaf(acc[u][4 * j + 1], scale, o[j].y);
+                        o[j].z = fmaf(acc[u][4 * j + 2], scale, o[j].z); o[j].w = fmaf(acc[u][4 * j + 3], scale, o[j].w);
+                        dst[j] = o[j];
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        // a wait ran out: report it and give copies that may still be in flight 2 ms to land
+        if (threadIdx.x == 0) atomicOr(args.status, CRB_FLAG_WAIT_LIMIT);
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) { }
+    }
+    cluster_sync_all();                       // neither CTA leaves while the peer may still signal it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
 // ---- float32 input: amax, then split into two fp16 planes ------------------------------------
 __global__ void k_amax(const float* __restrict__ X, int64_t T, int C, int64_t ldx, unsigned* amax_bits) {
     float m = 0.f;
@@ -323,6 +572,16 @@ static int hessian_chunk_tokens() {
     return v;
 }
 
+// CRB_HESSIAN_PAIRS=0 selects the single-CTA kernel (for comparison runs); default is the pair kernel.
+static bool hessian_use_pairs() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("CRB_HESSIAN_PAIRS");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 size_t hessian_workspace_bytes(int C, int64_t T, int dtype) {
     size_t b = 256;                                           // amax + inv_scale2 + status
     if (dtype == CRB_F32) b += 2 * align256((size_t)T * C * sizeof(__half));
@@ -376,13 +635,34 @@ int hessian_accumulate_launch(const void* X, int dtype, int64_t T, int C, int64_
     }
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(k_hessian_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, HT_SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(k_hessian_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, HT_SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(k_hessian_umma_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, H2_SMEM) != cudaSuccess)
             return CRB_ERR_LAUNCH;
         attr_set = true;
     }
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (hessian_use_pairs()) {
+        // clusters of two CTAs over 256 x 256 upper-triangle tiles
+        const int nt = (C + H2_TILE - 1) / H2_TILE;
+        a.n_col_tiles = nt;
+        a.n_tiles = nt * (nt + 1) / 2;
+        const int pairs = a.n_tiles < sms / 2 ? a.n_tiles : sms / 2;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * pairs);
+        cfg.blockDim = dim3(HT_THREADS);
+        cfg.dynamicSmemBytes = H2_SMEM;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, k_hessian_umma_pair, map0, map1, a) != cudaSuccess) return CRB_ERR_LAUNCH;
+        CRB_LAUNCHED();
+        return CRB_OK;
+    }
     const int grid = a.n_tiles < sms ? a.n_tiles : sms;
     k_hessian_umma<<<grid, HT_THREADS, HT_SMEM, st>>>(map0, map1, a);
     CRB_LAUNCHED();

@@ -167,6 +167,17 @@ def _replay_kwargs(kwargs: dict, batch: int) -> dict:
     return out
 
 
+_STREAMS: Dict[int, list] = {}
+
+
+def _stream_pool(dev, n):
+    """Side streams per device, created once: scratch buffers are cached per stream."""
+    pool = _STREAMS.setdefault(torch.device(dev).index or 0, [])
+    while len(pool) < n:
+        pool.append(torch.cuda.Stream(device=dev))
+    return pool
+
+
 def _layer_out(res):
     return res[0] if isinstance(res, (tuple, list)) else res
 
@@ -290,8 +301,9 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
         if concurrent:
             ready = torch.cuda.Event()
             ready.record(main)
-            for name in order:
-                s = torch.cuda.Stream(device=dev)
+            pool = _stream_pool(dev, len(order))
+            for slot, name in enumerate(order):
+                s = pool[slot]
                 s.wait_event(ready)
                 with torch.cuda.stream(s):
                     states[name] = gptq[name].fasterquant_begin(percdamp=args.percdamp, blocksize=args.blocksize,
