@@ -327,14 +327,14 @@ def hessian_roofline(dev, d, f, args, peaks):
     b.record()
     torch.cuda.synchronize()
     ms = a.elapsed_time(b) / reps
-    ncol = (f + 255) // 256
-    tiles = sum(2 * (ncol - h) for h in range(ncol))
-    issued = tiles * 128 * 256 * 2.0 * T
+    nt = (f + 255) // 256
+    tiles = nt * (nt + 1) // 2                      # upper-triangle 256 x 256 tiles, one per CTA pair
+    issued = tiles * 256 * 256 * 2.0 * T
     algorithmic = 2.0 * T * f * f
     achieved = issued / (ms * 1e-3) / 1e12
     peak = peaks["bf16_tflops"]
     del X, S
-    return {"kernel": "k_hessian_umma", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+    return {"kernel": "k_hessian_umma_pair", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": achieved / peak, "traffic": None, "launch_ms": ms,
             "work": f"T={T} tokens x C={f}: {issued:.3e} flop issued on upper-triangle tiles "
                     f"({algorithmic:.3e} for the full product the reference computes)",

@@ -78,74 +78,200 @@ __global__ void k_reverse_copy(const float* __restrict__ H, int C, const float* 
     A[(int64_t)i * C + j] = v;
 }
 
-// Factor one 128x128 diagonal block (lower Cholesky, left-looking) and overwrite it with the
-// inverse of its factor (zeros above the diagonal).  512 threads: four lanes share a row (or a
-// column of the inverse) and split every dot product four ways, so that the serial chain per
-// column is a quarter of the row length plus two shuffles.
-constexpr int kDiagThreads = 4 * FB;
-constexpr int kDiagPitch = FB + 4;
+// Factor one 128x128 diagonal block (lower Cholesky) and overwrite it with the inverse of its
+// factor (zeros above the diagonal).  One CTA of 512 threads, blocked by 16 columns:
+//   phase 1, per 16-column panel: one warp factors the 16x16 diagonal block and inverts it with
+//            shuffles; the rows below are multiplied by that inverse; the trailing block gets a
+//            rank-16 update with 4x4 register tiles (16-byte shared-memory loads);
+//   phase 2: the inverse is assembled from the 16x16 diagonal inverses by merging neighbouring
+//            blocks three times:  [[A,0],[B,D]]^-1 = [[A^-1,0],[-D^-1 B A^-1, D^-1]].
+constexpr int kDiagThreads = 512;
+constexpr int kDiagPitch = FB + 4;                 // 132 floats: rows 16-byte aligned, 8 rows hit 8 bank groups
+constexpr int kDiagTmpPitch = 68;
+constexpr int kDiagSmemFloats = 2 * FB * kDiagPitch + 64 * kDiagTmpPitch;
 
-__device__ __forceinline__ float quad_sum(float v) {
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    return v;
+// C[i][j] (+)= sign * sum_k A[i][k] * B[k][j] for an n x n block, 4x4 outputs per thread, rows and
+// columns of a thread's tile strided by n/4 so that consecutive lanes read consecutive rows.
+template <bool SUBTRACT_FROM_ZERO>
+__device__ __forceinline__ void smem_gemm_nn(const float* A, int lda, const float* B, int ldb, float* C, int ldc,
+                                             int n, int tid_in_group, int group_threads) {
+    const int q = n >> 2;                           // tile grid q x q, strided rows / contiguous 4-column groups
+    for (int idx = tid_in_group; idx < q * q; idx += group_threads) {
+        const int ti = idx % q, tj = idx / q;
+        float acc[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+        for (int k = 0; k < n; k += 4) {
+            float4 av[4], bv[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) av[a] = *reinterpret_cast<const float4*>(A + (ti + a * q) * lda + k);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) bv[kk] = *reinterpret_cast<const float4*>(B + (k + kk) * ldb + 4 * tj);
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const float ak[4] = {av[a].x, av[a].y, av[a].z, av[a].w};
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    acc[a][0] = fmaf(ak[kk], bv[kk].x, acc[a][0]);
+                    acc[a][1] = fmaf(ak[kk], bv[kk].y, acc[a][1]);
+                    acc[a][2] = fmaf(ak[kk], bv[kk].z, acc[a][2]);
+                    acc[a][3] = fmaf(ak[kk], bv[kk].w, acc[a][3]);
+                }
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            float4 o = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+            if (SUBTRACT_FROM_ZERO) { o.x = -o.x; o.y = -o.y; o.z = -o.z; o.w = -o.w; }
+            *reinterpret_cast<float4*>(C + (ti + a * q) * ldc + 4 * tj) = o;
+        }
+    }
 }
 
 __global__ void __launch_bounds__(kDiagThreads)
 k_chol_diag(float* __restrict__ Akk, int64_t ld, unsigned* status) {
-    // row pitch 132 floats: the four lanes of a row and the eight rows of a warp hit 32 distinct banks
-    extern __shared__ float s_diag[];
-    float (*a)[kDiagPitch] = reinterpret_cast<float (*)[kDiagPitch]>(s_diag);
-    float (*x)[kDiagPitch] = reinterpret_cast<float (*)[kDiagPitch]>(s_diag + FB * kDiagPitch);
-    const int tid = threadIdx.x;
-    const int i = tid >> 2, s = tid & 3;               // row (phase 1) / column (phase 2), quarter
-    for (int e = tid; e < FB * FB; e += kDiagThreads) a[e >> 7][e & 127] = Akk[(int64_t)(e >> 7) * ld + (e & 127)];
-    __syncthreads();
-    bool bad = false;
-    for (int k = 0; k < FB; ++k) {
-        // column k: acc = a[i][k] - sum_{j<k} a[i][j] * a[k][j]   for rows i >= k
-        float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
-        if (i >= k) {
-            int j = s;
-            for (; j + 12 < k; j += 16) {          // four independent chains keep the loads in flight
-                p0 = fmaf(a[i][j], a[k][j], p0);
-                p1 = fmaf(a[i][j + 4], a[k][j + 4], p1);
-                p2 = fmaf(a[i][j + 8], a[k][j + 8], p2);
-                p3 = fmaf(a[i][j + 12], a[k][j + 12], p3);
-            }
-            for (; j < k; j += 4) p0 = fmaf(a[i][j], a[k][j], p0);
-        }
-        const float acc = a[i][k] - quad_sum((p0 + p1) + (p2 + p3));
-        if (i == k && s == 0) {
-            float piv = acc;
-            if (!(piv > 0.f) || !isfinite(piv)) { bad = true; piv = 1.f; }
-            a[k][k] = sqrtf(piv);
-        }
-        __syncthreads();
-        if (i > k && s == 0) a[i][k] = __fdiv_rn(acc, a[k][k]);
-        __syncthreads();
-    }
-    if (bad) atomicOr(status, CRB_FLAG_BAD_PIVOT);
-    // inverse of the lower factor by forward substitution, column j = tid / 4:
-    //   x[r][j] = (delta_rj - sum_{m=j}^{r-1} a[r][m] x[m][j]) / a[r][r]
-    // rows are produced in order; the four lanes of a column split the sum over m.
-    const int j = i;
-    for (int r = 0; r < FB; ++r) {
-        float p = 0.f, pb = 0.f;
-        if (r > j) {
-            int m = j + s;
-            for (; m + 4 < r; m += 8) {
-                p = fmaf(a[r][m], x[m][j], p);
-                pb = fmaf(a[r][m + 4], x[m + 4][j], pb);
-            }
-            if (m < r) p = fmaf(a[r][m], x[m][j], p);
-        }
-        p = quad_sum(p + pb);
-        if (s == 0) x[r][j] = (r < j) ? 0.f : ((r == j) ? __fdiv_rn(1.f, a[r][r]) : __fdiv_rn(-p, a[r][r]));
-        __syncwarp();
+    extern __shared__ __align__(16) float s_diag[];
+    float* a = s_diag;                               // [128][132] the block, then its factor L
+    float* x = s_diag + FB * kDiagPitch;             // [128][132] the inverse of L
+    float* tmp = x + FB * kDiagPitch;                // [64][68]   products of phase 2
+    __shared__ float s_li[16][17];                   // inverse of the current 16x16 diagonal factor
+    __shared__ int s_bad;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) s_bad = 0;
+    for (int e = tid; e < FB * FB; e += kDiagThreads) {
+        a[(e >> 7) * kDiagPitch + (e & 127)] = Akk[(int64_t)(e >> 7) * ld + (e & 127)];
+        x[(e >> 7) * kDiagPitch + (e & 127)] = 0.f;
     }
     __syncthreads();
-    for (int e = tid; e < FB * FB; e += kDiagThreads) Akk[(int64_t)(e >> 7) * ld + (e & 127)] = x[e >> 7][e & 127];
+
+    // ---------------- phase 1: blocked Cholesky ----------------
+    for (int c0 = 0; c0 < FB; c0 += 16) {
+        if (warp == 0) {
+            // 16x16 diagonal block: lane i (< 16) holds row i
+            const int i = lane & 15;
+            float d[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) d[j] = a[(c0 + i) * kDiagPitch + c0 + j];
+            bool bad = false;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                float piv = __shfl_sync(0xffffffffu, d[k], k);
+                if (!(piv > 0.f) || !isfinite(piv)) { bad = true; piv = 1.f; }
+                const float s = sqrtf(piv);
+                d[k] = (i == k) ? s : __fdiv_rn(d[k], s);            // column k of L (rows i >= k meaningful)
+#pragma unroll
+                for (int j = k + 1; j < 16; ++j) {
+                    const float ljk = __shfl_sync(0xffffffffu, d[k], j);
+                    d[j] = fmaf(-d[k], ljk, d[j]);                    // used only for i >= j
+                }
+            }
+            if (bad && lane == 0) s_bad = 1;
+            // inverse of the 16x16 factor: lane j holds column j of the inverse
+            const int j = lane & 15;
+            float xi[16];
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                float acc = 0.f;
+#pragma unroll
+                for (int m = 0; m < r; ++m) {
+                    const float lrm = __shfl_sync(0xffffffffu, d[m], r);      // L[r][m]
+                    acc = fmaf(lrm, (m >= j) ? xi[m] : 0.f, acc);
+                }
+                const float lrr = __shfl_sync(0xffffffffu, d[r], r);
+                xi[r] = (r < j) ? 0.f : ((r == j) ? __fdiv_rn(1.f, lrr) : __fdiv_rn(-acc, lrr));
+            }
+            if (lane < 16) {
+#pragma unroll
+                for (int jj = 0; jj < 16; ++jj) a[(c0 + i) * kDiagPitch + c0 + jj] = (jj <= i) ? d[jj] : 0.f;
+#pragma unroll
+                for (int r = 0; r < 16; ++r) {
+                    s_li[r][j] = xi[r];
+                    x[(c0 + r) * kDiagPitch + c0 + j] = xi[r];
+                }
+            }
+        }
+        __syncthreads();
+        const int below = FB - c0 - 16;                                // rows under the diagonal block
+        if (below > 0) {
+            // panel: P[i][j] = sum_{m <= j} A[i][c0 + m] * Linv[j][m]; four lanes share a row
+            const int r = tid >> 2, jg = tid & 3;
+            float in[16];
+            const bool act = r < below;
+            float* prow = a + (c0 + 16 + (act ? r : 0)) * kDiagPitch + c0;
+#pragma unroll
+            for (int m = 0; m < 16; ++m) in[m] = prow[m];
+            __syncwarp();
+            if (act) {
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int j = 4 * jg + jj;
+                    float acc = 0.f;
+#pragma unroll
+                    for (int m = 0; m < 16; ++m) acc = fmaf(in[m], (m <= j) ? s_li[j][m] : 0.f, acc);
+                    prow[j] = acc;
+                }
+            }
+            __syncthreads();
+            // trailing update: A[i][j] -= sum_m P[i][m] P[j][m] for the rows / columns below the panel
+            const int q = below >> 2;
+            const float* P = a + (c0 + 16) * kDiagPitch + c0;           // P[i][m]
+            float* T = a + (c0 + 16) * kDiagPitch + c0 + 16;            // trailing block, T[i][j]
+            for (int idx = tid; idx < q * q; idx += kDiagThreads) {
+                const int ti = idx % q, tj = idx / q;
+                if (ti + 3 * q < 4 * tj) continue;                      // tile entirely above the diagonal
+                float acc[4][4];
+#pragma unroll
+                for (int aa = 0; aa < 4; ++aa)
+#pragma unroll
+                    for (int bb = 0; bb < 4; ++bb) acc[aa][bb] = 0.f;
+#pragma unroll
+                for (int m = 0; m < 16; m += 4) {
+                    float4 pi[4], pj[4];
+#pragma unroll
+                    for (int aa = 0; aa < 4; ++aa) pi[aa] = *reinterpret_cast<const float4*>(P + (ti + aa * q) * kDiagPitch + m);
+#pragma unroll
+                    for (int bb = 0; bb < 4; ++bb) pj[bb] = *reinterpret_cast<const float4*>(P + (4 * tj + bb) * kDiagPitch + m);
+#pragma unroll
+                    for (int aa = 0; aa < 4; ++aa)
+#pragma unroll
+                        for (int bb = 0; bb < 4; ++bb) {
+                            acc[aa][bb] = fmaf(pi[aa].x, pj[bb].x, acc[aa][bb]);
+                            acc[aa][bb] = fmaf(pi[aa].y, pj[bb].y, acc[aa][bb]);
+                            acc[aa][bb] = fmaf(pi[aa].z, pj[bb].z, acc[aa][bb]);
+                            acc[aa][bb] = fmaf(pi[aa].w, pj[bb].w, acc[aa][bb]);
+                        }
+                }
+#pragma unroll
+                for (int aa = 0; aa < 4; ++aa) {
+                    float4* dst = reinterpret_cast<float4*>(T + (ti + aa * q) * kDiagPitch + 4 * tj);
+                    float4 o = *dst;
+                    o.x -= acc[aa][0]; o.y -= acc[aa][1]; o.z -= acc[aa][2]; o.w -= acc[aa][3];
+                    *dst = o;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (tid == 0 && s_bad) atomicOr(status, CRB_FLAG_BAD_PIVOT);
+
+    // ---------------- phase 2: inverse by merging diagonal blocks of size s = 16, 32, 64 ----------------
+    for (int s = 16; s < FB; s <<= 1) {
+        const int pairs = FB / (2 * s);
+        const int gthreads = kDiagThreads / pairs;                      // threads per pair
+        const int pr = tid / gthreads, tg = tid % gthreads;
+        const int b0 = pr * 2 * s;
+        // T = L21 * Ainv   (L21 = a[b0+s.., b0..], Ainv = x[b0.., b0..])
+        smem_gemm_nn<false>(a + (b0 + s) * kDiagPitch + b0, kDiagPitch, x + b0 * kDiagPitch + b0, kDiagPitch,
+                            tmp + (pr * s) * kDiagTmpPitch, kDiagTmpPitch, s, tg, gthreads);
+        __syncthreads();
+        // X21 = -Dinv * T  (Dinv = x[b0+s.., b0+s..])
+        smem_gemm_nn<true>(x + (b0 + s) * kDiagPitch + b0 + s, kDiagPitch, tmp + (pr * s) * kDiagTmpPitch, kDiagTmpPitch,
+                           x + (b0 + s) * kDiagPitch + b0, kDiagPitch, s, tg, gthreads);
+        __syncthreads();
+    }
+    for (int e = tid; e < FB * FB; e += kDiagThreads) Akk[(int64_t)(e >> 7) * ld + (e & 127)] = x[(e >> 7) * kDiagPitch + (e & 127)];
 }
 
 // U = index-reversed copy of the lower-triangular X (upper triangle and diagonal; zeros below).
@@ -200,7 +326,7 @@ int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
     k_reverse_copy<<<dim3((C + 255) / 256, C), 256, 0, st>>>(H, C, damp, dead, A);
     CRB_LAUNCHED();
     const int nb = C / FB;
-    constexpr int kDiagSmem = 2 * FB * kDiagPitch * (int)sizeof(float);
+    constexpr int kDiagSmem = kDiagSmemFloats * (int)sizeof(float);
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(k_chol_diag, cudaFuncAttributeMaxDynamicSharedMemorySize, kDiagSmem) != cudaSuccess)

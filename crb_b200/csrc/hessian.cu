@@ -6,13 +6,14 @@
 // swizzle atoms, which is the canonical MN-major SWIZZLE_128B operand layout of tcgen05.mma
 // (leading-dimension offset = one 64-channel box, stride offset = 1024 bytes per 8 tokens).
 //
-// One persistent CTA per SM walks the upper-triangle output tiles (128 rows x 256 columns).
-// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (owns the TMEM allocation),
-// warps 2..9 = epilogue (TMEM -> registers -> S += acc; two warps per TMEM lane quarter, one per
-// column half).  Two 256-column accumulators
-// alternate so that the epilogue of one tile / token chunk overlaps the MMAs of the next.
-// The token dimension is cut into chunks; each chunk is accumulated in TMEM and then added
-// to S in float32 by the CUDA cores, which bounds the length of any tensor-core running sum.
+// Clusters of two CTAs (one per SM) walk the upper-triangle 256 x 256 output tiles persistently;
+// a pair computes its tile with tcgen05.mma.cta_group::2 (M = 256 across the two SMs, N = 256).
+// Warp roles per CTA: warp 0 = TMA producer, warp 1 = MMA issuer (leader CTA only; owns the TMEM
+// allocation), warps 2..9 = epilogue (two warps per TMEM lane quarter, one per column half).
+// Two 256-column TMEM accumulators alternate.  The token dimension is cut into chunks; each
+// chunk is accumulated in TMEM and then folded into float32 REGISTER accumulators by the CUDA
+// cores (round to nearest), which bounds the length of any tensor-core running sum (its adder
+// truncates) without touching memory; S is read-modified-written once per tile and call.
 //
 // float32 X (the single-linear configuration) is split by a pre-pass into two fp16 planes
 // x*s = hi + lo (s a power of two); the tile then accumulates hi^T hi + hi^T lo + lo^T hi,
@@ -30,16 +31,11 @@
 
 namespace crb {
 
-constexpr int HT_M = 128;              // output rows per tile (UMMA M)
+constexpr int HT_M = 128;              // output rows per CTA (UMMA M = 256 over the pair)
 constexpr int HT_N = 256;              // output columns per tile (UMMA N)
 constexpr int HT_K = 64;               // tokens per pipeline stage
 constexpr int HT_BOX = 64;             // channels per TMA box (128 bytes of 16-bit elements)
-constexpr int HT_STAGES = 4;
 constexpr int HT_BOX_BYTES = HT_BOX * HT_K * 2;                          // 8 KiB
-constexpr int HT_A_BYTES = (HT_M / HT_BOX) * HT_BOX_BYTES;               // 16 KiB
-constexpr int HT_B_BYTES = (HT_N / HT_BOX) * HT_BOX_BYTES;               // 32 KiB
-constexpr int HT_STAGE_BYTES = HT_A_BYTES + HT_B_BYTES;                  // 48 KiB
-constexpr int HT_SMEM = HT_STAGES * HT_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int HT_THREADS = 320;          // TMA warp, MMA warp, eight epilogue warps
 
 // Shared-memory matrix descriptor of an MN-major, 128-byte-swizzled operand:
@@ -73,188 +69,14 @@ struct HessArgs {
     int n_tiles, n_col_tiles;
 };
 
-// Linear upper-triangle tile index -> (row tile of 128, column tile of 256).  Row tiles 2h and
-// 2h+1 both need column tiles h .. n_col_tiles-1.
-__device__ __forceinline__ void tile_coords(int t, int n_col_tiles, int* mi, int* nj) {
-    int h = 0;
-    for (;;) {
-        const int per_row = n_col_tiles - h;
-        if (t < 2 * per_row) { *mi = 2 * h + (t >= per_row); *nj = h + (t >= per_row ? t - per_row : t); return; }
-        t -= 2 * per_row;
-        ++h;
-    }
-}
-
-__global__ void __launch_bounds__(HT_THREADS, 1)
-k_hessian_umma(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
-               const HessArgs args) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + HT_STAGES * HT_STAGE_BYTES);
-    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * HT_STAGES + 4);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * HT_STAGES;
-    const uint32_t tfull0 = empty0 + 8 * HT_STAGES, tempty0 = tfull0 + 16;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < HT_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 8); }
-        *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-
-    const int n_chunks = (int)((args.T + args.chunk_tokens - 1) / args.chunk_tokens);
-
-    if (warp == 0) {
-        // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            uint32_t armed = 0, armed_phase = 0;      // per stage: was it armed, and with which parity
-            bool ok = true;
-            for (int t = blockIdx.x; t < args.n_tiles && ok; t += gridDim.x) {
-                int mi, nj;
-                tile_coords(t, args.n_col_tiles, &mi, &nj);
-                for (int ch = 0; ch < n_chunks && ok; ++ch) {
-                    const int64_t t0 = (int64_t)ch * args.chunk_tokens;
-                    const int64_t t1 = min(args.T, t0 + args.chunk_tokens);
-                    for (int p = 0; p < args.n_pass && ok; ++p) {
-                        const CUtensorMap* ma = (p == 2) ? &map1 : &map0;     // hi, hi, lo
-                        const CUtensorMap* mb = (p == 1) ? &map1 : &map0;     // hi, lo, hi
-                        for (int64_t tk = t0; tk < t1; tk += HT_K) {
-                            ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag);
-                            if (!ok) break;
-                            const uint32_t sa = smem_u32(smem + stage * HT_STAGE_BYTES);
-                            const uint32_t sb = sa + HT_A_BYTES;
-                            const uint32_t fb = full0 + 8 * stage;
-                            mbar_expect_tx(fb, HT_STAGE_BYTES);
-                            armed |= 1u << stage;
-                            armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
-#pragma unroll
-                            for (int b = 0; b < HT_M / HT_BOX; ++b)
-                                tma_load_2d(sa + b * HT_BOX_BYTES, ma, mi * HT_M + b * HT_BOX, (int)tk, fb);
-#pragma unroll
-                            for (int b = 0; b < HT_N / HT_BOX; ++b)
-                                tma_load_2d(sb + b * HT_BOX_BYTES, mb, nj * HT_N + b * HT_BOX, (int)tk, fb);
-                            if (++stage == HT_STAGES) { stage = 0; phase ^= 1; }
-                        }
-                    }
-                }
-            }
-            // drain: the copies of every armed stage must have landed before shared memory goes away
-            // (immediate on the normal path, where the MMA warp has consumed them all)
-            for (int s = 0; s < HT_STAGES; ++s) {
-                if (!(armed >> s & 1u)) continue;
-                const unsigned long long t0 = global_ns();
-                while (!mbar_try_wait(full0 + 8 * s, (armed_phase >> s) & 1u))
-                    if (global_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; break; }
-            }
-        }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            const uint32_t idesc = f16_idesc(args.ab_format, HT_M, HT_N);
-            uint32_t stage = 0, phase = 0, unit = 0;
-            bool ok = true;
-            for (int t = blockIdx.x; t < args.n_tiles && ok; t += gridDim.x) {
-                for (int ch = 0; ch < n_chunks && ok; ++ch, ++unit) {
-                    const uint32_t buf = unit & 1, use = unit >> 1;
-                    ok = mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, abort_flag);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t d_tmem = tmem_base + buf * HT_N;
-                    const int64_t t0 = (int64_t)ch * args.chunk_tokens;
-                    const int64_t t1 = min(args.T, t0 + args.chunk_tokens);
-                    bool first = true;
-                    for (int p = 0; p < args.n_pass && ok; ++p) {
-                        for (int64_t tk = t0; tk < t1; tk += HT_K) {
-                            ok = mbar_wait(full0 + 8 * stage, phase, abort_flag);
-                            if (!ok) break;
-                            tc_fence_after();
-                            const uint32_t sa = smem_u32(smem + stage * HT_STAGE_BYTES);
-                            const uint32_t sb = sa + HT_A_BYTES;
-#pragma unroll
-                            for (int k = 0; k < HT_K / 16; ++k) {
-                                // 16 tokens = two 8-token swizzle atoms = 2048 bytes further along K
-                                const uint64_t da = mn_sw128_desc(sa + k * 2048, HT_BOX_BYTES, 1024);
-                                const uint64_t db = mn_sw128_desc(sb + k * 2048, HT_BOX_BYTES, 1024);
-                                umma_f16(d_tmem, da, db, idesc, !first);
-                                first = false;
-                            }
-                            umma_commit(empty0 + 8 * stage);          // frees the stage when the MMAs retire
-                            if (++stage == HT_STAGES) { stage = 0; phase ^= 1; }
-                        }
-                    }
-                    if (ok) umma_commit(tfull0 + 8 * buf);             // accumulator ready for the epilogue
-                }
-            }
-        }
-    } else {
-        // ---------------- epilogue: warps 2..9; warp w reads TMEM lanes 32*(w % 4) .. +31 and the
-        // column half (w - 2) / 4 of the 256-column accumulator ----------------
-        const int q = warp & 3;
-        const int c_begin = ((warp - 2) >> 2) * (HT_N / 2);
-        const float scale = args.inv_scale2 ? *args.inv_scale2 : 1.0f;
-        uint32_t unit = 0;
-        bool ok = true;
-        for (int t = blockIdx.x; t < args.n_tiles && ok; t += gridDim.x) {
-            int mi, nj;
-            tile_coords(t, args.n_col_tiles, &mi, &nj);
-            const int row = mi * HT_M + q * 32 + lane;
-            for (int ch = 0; ch < n_chunks && ok; ++ch, ++unit) {
-                const uint32_t buf = unit & 1, use = unit >> 1;
-                ok = mbar_wait(tfull0 + 8 * buf, use & 1, abort_flag);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * HT_N;
-#pragma unroll 1
-                for (int c0 = c_begin; c0 < c_begin + HT_N / 2; c0 += 32) {
-                    float v[32];
-                    tmem_ld32(taddr + c0, v);
-                    const int col = nj * HT_N + c0;
-                    // only columns at or right of this row's diagonal are ever read back
-                    if (row < args.C && col < args.C && col + 31 >= row) {
-                        float4* dst = reinterpret_cast<float4*>(args.S + (int64_t)row * args.C + col);
-                        float4 o[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) o[j] = dst[j];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            o[j].x = fmaf(v[4 * j + 0], scale, o[j].x); o[j].y = fmaf(v[4 * j + 1], scale, o[j].y);
-                            o[j].z = fmaf(v[4 * j + 2], scale, o[j].z); o[j].w = fmaf(v[4 * j + 3], scale, o[j].w);
-                            dst[j] = o[j];
-                        }
-                    }
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
-            }
-        }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0 && *abort_flag) atomicOr(args.status, CRB_FLAG_WAIT_LIMIT);
-    if (warp == 1) {
-        tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
-    }
-}
-
 // ---------------------------------------------------------------------------------------------
-// Two-CTA variant: a cluster of two CTAs (two SMs) computes one 256 x 256 output tile with
+// A cluster of two CTAs (two SMs) computes one 256 x 256 output tile with
 // tcgen05.mma.cta_group::2.  CTA r of the pair loads the operand rows r*128..r*128+127 of the M
-// side and of the N side, so every CTA stages 256 channel rows per 256 x 256 x K of work instead
-// of 384 per 128 x 256 x K: a third less L2 -> shared-memory traffic per flop, which is what
-// limits the single-CTA kernel.  The leader (cluster rank 0) issues all MMAs; both CTAs' TMA
-// copies report to the leader's "full" barrier; MMA completion is committed to the barriers of
-// both CTAs (two plain commits, no multicast); each CTA drains its own 128 accumulator rows.
+// side and of the N side, so every CTA stages 256 channel rows per 256 x 256 x K of work (a
+// single CTA on a 128 x 256 tile would stage 384 per half the work): the L2 -> shared-memory
+// traffic per flop is what limits this kernel.  The leader (cluster rank 0) issues all MMAs; both
+// CTAs' TMA copies report to the leader's "full" barrier; MMA completion is committed to the
+// barriers of both CTAs (two plain commits); each CTA drains its own 128 accumulator rows.
 // ---------------------------------------------------------------------------------------------
 constexpr int H2_STAGES = 6;
 constexpr int H2_HALF_BYTES = 2 * HT_BOX_BYTES;                 // 128 channels x 64 tokens = 16 KiB
@@ -572,16 +394,6 @@ static int hessian_chunk_tokens() {
     return v;
 }
 
-// CRB_HESSIAN_PAIRS=0 selects the single-CTA kernel (for comparison runs); default is the pair kernel.
-static bool hessian_use_pairs() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("CRB_HESSIAN_PAIRS");
-        v = (e && e[0] == '0') ? 0 : 1;
-    }
-    return v == 1;
-}
-
 size_t hessian_workspace_bytes(int C, int64_t T, int dtype) {
     size_t b = 256;                                           // amax + inv_scale2 + status
     if (dtype == CRB_F32) b += 2 * align256((size_t)T * C * sizeof(__half));
@@ -606,13 +418,8 @@ int hessian_accumulate_launch(const void* X, int dtype, int64_t T, int C, int64_
     HessArgs a;
     a.S = S; a.status = status; a.C = C; a.T = T;
     a.chunk_tokens = hessian_chunk_tokens();
-    a.n_col_tiles = (C + HT_N - 1) / HT_N;
-    {
-        int n = 0;
-        for (int h = 0; h < a.n_col_tiles; ++h) n += 2 * (a.n_col_tiles - h);
-        if ((C / HT_M) & 1) n -= (a.n_col_tiles - (C / HT_M) / 2);   // odd number of row tiles: last pair is half
-        a.n_tiles = n;
-    }
+    a.n_col_tiles = (C + H2_TILE - 1) / H2_TILE;
+    a.n_tiles = a.n_col_tiles * (a.n_col_tiles + 1) / 2;
     if (dtype == CRB_F32) {
         if (ldx & 3) return CRB_ERR_BAD_ARG;
         __half* hi = reinterpret_cast<__half*>(static_cast<char*>(workspace) + 256);
@@ -635,36 +442,26 @@ int hessian_accumulate_launch(const void* X, int dtype, int64_t T, int C, int64_
     }
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(k_hessian_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, HT_SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(k_hessian_umma_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, H2_SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(k_hessian_umma_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, H2_SMEM) != cudaSuccess)
             return CRB_ERR_LAUNCH;
         attr_set = true;
     }
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (hessian_use_pairs()) {
-        // clusters of two CTAs over 256 x 256 upper-triangle tiles
-        const int nt = (C + H2_TILE - 1) / H2_TILE;
-        a.n_col_tiles = nt;
-        a.n_tiles = nt * (nt + 1) / 2;
-        const int pairs = a.n_tiles < sms / 2 ? a.n_tiles : sms / 2;
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2 * pairs);
-        cfg.blockDim = dim3(HT_THREADS);
-        cfg.dynamicSmemBytes = H2_SMEM;
-        cfg.stream = st;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        if (cudaLaunchKernelEx(&cfg, k_hessian_umma_pair, map0, map1, a) != cudaSuccess) return CRB_ERR_LAUNCH;
-        CRB_LAUNCHED();
-        return CRB_OK;
-    }
-    const int grid = a.n_tiles < sms ? a.n_tiles : sms;
-    k_hessian_umma<<<grid, HT_THREADS, HT_SMEM, st>>>(map0, map1, a);
+    // clusters of two CTAs over the 256 x 256 upper-triangle tiles
+    const int pairs = a.n_tiles < sms / 2 ? a.n_tiles : sms / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(HT_THREADS);
+    cfg.dynamicSmemBytes = H2_SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, k_hessian_umma_pair, map0, map1, a) != cudaSuccess) return CRB_ERR_LAUNCH;
     CRB_LAUNCHED();
     return CRB_OK;
 }

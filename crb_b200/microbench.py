@@ -69,14 +69,13 @@ def main(argv=None):
         X = torch.randn(a.T, a.C, generator=g, device=dev).to(getattr(torch, a.dtype))
         S = torch.zeros(a.C, a.C, device=dev)
         ms = _time(lambda: ops.hessian_accumulate(S, X), a.warmup, a.iters)
-        ncol = (a.C + 255) // 256
-        rows = a.C // 128
-        tiles = sum(2 * (ncol - h) for h in range(ncol)) - ((ncol - rows // 2) if rows % 2 else 0)
+        nt = (a.C + 255) // 256
+        tiles = nt * (nt + 1) // 2
         passes = 3 if a.dtype == "float32" else 1
-        issued = tiles * 128 * 256 * 2.0 * a.T * passes
+        issued = tiles * 256 * 256 * 2.0 * a.T * passes
         out.update(ms=ms, dtype=a.dtype, tflops_issued=issued / ms / 1e9,
                    tflops_full_product=2.0 * a.T * a.C * a.C / ms / 1e9,
-                   note="flop issued on upper-triangle 128x256 tiles; full product = 2*T*C^2")
+                   note="flop issued on upper-triangle 256x256 tiles; full product = 2*T*C^2")
     elif a.what == "factor":
         X = torch.randn(2 * a.C, a.C, generator=g, device=dev)
         H0 = (X.t() @ X) / a.C
