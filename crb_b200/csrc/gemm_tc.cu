@@ -11,7 +11,7 @@
 //
 // One persistent CTA per SM over 128 x 256 output tiles.  Warp roles: warp 0 TMA producer
 // (float32 tiles, 128-byte swizzle), warp 1 MMA issuer (owns TMEM), warps 2-5 split the
-// landed tiles into hi / lo in place, warps 6-9 epilogue (TMEM -> registers -> C).  Two
+// landed tiles into hi / lo in place, warps 6-13 epilogue (TMEM -> registers -> C).  Two
 // shared-memory stages of K = 32, two 256-column TMEM accumulators.  A is [M, K] row-major
 // (K-major operand); B is [N, K] row-major (K-major) or [K, N] row-major (MN-major operand).
 // All mbarrier waits are bounded (2 s); on expiry CRB_FLAG_WAIT_LIMIT is raised and the kernel
@@ -27,8 +27,9 @@ constexpr int GT_A_BYTES = GT_M * GT_K * 4;                 // 16 KiB
 constexpr int GT_B_BYTES = GT_N * GT_K * 4;                 // 32 KiB
 constexpr int GT_RAW_BYTES = GT_A_BYTES + GT_B_BYTES;       // 48 KiB: hi planes (TMA destination)
 constexpr int GT_STAGE_BYTES = 2 * GT_RAW_BYTES;            // + lo planes
-constexpr int GT_SMEM = GT_STAGES * GT_STAGE_BYTES + 1024 + 256;
-constexpr int GT_THREADS = 320;
+constexpr int GT_EPI_BYTES = 8 * 32 * 33 * 4;                 // per-warp transpose patches of the epilogue
+constexpr int GT_SMEM = GT_STAGES * GT_STAGE_BYTES + 256 + GT_EPI_BYTES + 1024;
+constexpr int GT_THREADS = 448;              // TMA, MMA, 4 splitter warps, 8 epilogue warps
 
 struct GemmArgs {
     float* C;
@@ -99,7 +100,7 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         for (int s = 0; s < GT_STAGES; ++s) {
             mbar_init(full0 + 8 * s, 1); mbar_init(ready0 + 8 * s, 4); mbar_init(empty0 + 8 * s, 1);
         }
-        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 8); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -220,8 +221,10 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             }
         }
     } else {
-        // ---------------- epilogue: warps 6..9 own TMEM lanes 32 * (warp % 4) .. +31 ----------------
+        // ---------------- epilogue: warps 6..13; warp w reads TMEM lanes 32 * (w % 4) .. +31 and the
+        // column half (w - 6) / 4 of the accumulator ----------------
         const int q = warp & 3;
+        const int c_begin = ((warp - 6) >> 2) * (GT_N / 2);
         uint32_t unit = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
@@ -229,38 +232,61 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             if (tile_skipped(g, mi, nj)) continue;
             const uint32_t buf = unit & 1, use = unit >> 1;
             ++unit;
+            // A TMEM load hands every lane one accumulator row (32 columns): written to memory like
+            // that, each instruction would touch 32 different cache lines.  The 32 x 32 chunk is
+            // transposed through a per-warp shared-memory patch instead, so that a warp instruction
+            // covers 4 rows x 128 contiguous bytes.  Lane l then owns rows (l / 8) + 4k, k = 0..7,
+            // and columns 4 (l % 8) .. +3 of the chunk.
+            const int r_sub = lane >> 3, cg = lane & 7;
+            const int row0 = mi * GT_M + q * 32 + r_sub;                 // + 4k
+            const int colbase = nj * GT_N + c_begin + 4 * cg;            // + 32c
+            // The old values of C do not depend on the MMAs: their loads are issued two chunks
+            // ahead (the first two before the accumulator is even ready) to keep memory busy.
+            float4 o[2][8];
+            auto live = [&](int c, int k) {
+                const int row = row0 + 4 * k, col = colbase + 32 * c;
+                // lower_only: nothing is written above the 128 x 128 block that holds the diagonal,
+                // so that a triangular matrix updated this way keeps exact zeros there
+                return row < g.M && col < g.N && !(g.lower_only && col > (row | 127));
+            };
+            auto fetch = [&](int c, float4 (&dst)[8]) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    dst[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (g.beta != 0.f && live(c, k))
+                        dst[k] = *reinterpret_cast<const float4*>(g.C + (int64_t)(row0 + 4 * k) * g.ldc + colbase + 32 * c);
+                }
+            };
+            fetch(0, o[0]);
+            fetch(1, o[1]);
             ok = mbar_wait(tfull0 + 8 * buf, use & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const int row = mi * GT_M + q * 32 + lane;
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * GT_N;
-#pragma unroll 1
-            for (int c0 = 0; c0 < GT_N; c0 += 32) {
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * GT_N + c_begin;
+            float* patch = reinterpret_cast<float*>(smem + GT_STAGES * GT_STAGE_BYTES + 256) + (warp - 6) * (32 * 33);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
                 float v[32];
-                tmem_ld32(taddr + c0, v);
-                const int col = nj * GT_N + c0;
-                // lower_only: nothing is written above the 128 x 128 block that holds the diagonal,
-                // so that a triangular matrix updated this way keeps exact zeros there
-                if (row < g.M && col < g.N && !(g.lower_only && col > (row | 127))) {
-                    float4* dst = reinterpret_cast<float4*>(g.C + (int64_t)row * g.ldc + col);
-                    float4 o[8];
-                    if (g.beta != 0.f) {
+                tmem_ld32(taddr + 32 * c, v);
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) o[j] = dst[j];
-                    } else {
+                for (int j = 0; j < 32; ++j) patch[lane * 33 + j] = v[j];
+                __syncwarp();
+                float4 (&oc)[8] = o[c & 1];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) o[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        o[j].x = fmaf(g.alpha, v[4 * j + 0], g.beta * o[j].x);
-                        o[j].y = fmaf(g.alpha, v[4 * j + 1], g.beta * o[j].y);
-                        o[j].z = fmaf(g.alpha, v[4 * j + 2], g.beta * o[j].z);
-                        o[j].w = fmaf(g.alpha, v[4 * j + 3], g.beta * o[j].w);
-                        dst[j] = o[j];
+                for (int k = 0; k < 8; ++k) {
+                    const float* src = patch + (r_sub + 4 * k) * 33 + 4 * cg;
+                    if (live(c, k)) {
+                        float4 w;
+                        w.x = fmaf(g.alpha, src[0], g.beta * oc[k].x);
+                        w.y = fmaf(g.alpha, src[1], g.beta * oc[k].y);
+                        w.z = fmaf(g.alpha, src[2], g.beta * oc[k].z);
+                        w.w = fmaf(g.alpha, src[3], g.beta * oc[k].w);
+                        *reinterpret_cast<float4*>(g.C + (int64_t)(row0 + 4 * k) * g.ldc + colbase + 32 * c) = w;
                     }
                 }
+                __syncwarp();
+                if (c + 2 < 4) fetch(c + 2, oc);
             }
             tc_fence_before();
             __syncwarp();
