@@ -38,6 +38,7 @@ struct GemmArgs {
     float alpha, beta;
     int b_is_nk;          // 1: B is [N, K] row-major (K-major operand); 0: B is [K, N] row-major (MN-major)
     int lower_only;       // write only 128 x 128 blocks on or below the diagonal (tiles above it are skipped)
+    int b_slabs;          // MN-major B: 1 = one 3-D copy per stage (map_b is a slab map), 0 = eight 2-D copies
     int m_tiles, n_tiles;
     unsigned* status;
 };
@@ -78,6 +79,20 @@ __device__ __forceinline__ uint32_t tf32_idesc(int b_mn_major) {
            ((uint32_t)(GT_N >> 3) << 17) | ((uint32_t)(GT_M >> 4) << 24);
 }
 
+#ifdef CRB_GEMM_PROFILE
+// Wait-time accounting per warp role (development builds only): nanoseconds spent in each kind of
+// barrier wait, summed over CTAs.  0 producer/empty, 1 splitter/full, 2 mma/ready, 3 mma/tmem-empty,
+// 4 epilogue/tmem-full, 5 epilogue/total, 6 splitter/total, 7 mma/total, 8 producer/total.
+__device__ unsigned long long g_gemm_prof[16];
+#define PROF_DECL unsigned long long prof_t = 0, prof_t0 = global_ns();
+#define PROF_WAIT(expr) ([&]() { const unsigned long long a_ = global_ns(); const bool r_ = (expr); prof_t += global_ns() - a_; return r_; })()
+#define PROF_END(slot_wait, slot_total) do { atomicAdd(&g_gemm_prof[slot_wait], prof_t); atomicAdd(&g_gemm_prof[slot_total], global_ns() - prof_t0); } while (0)
+#else
+#define PROF_DECL
+#define PROF_WAIT(expr) (expr)
+#define PROF_END(a, b)
+#endif
+
 __device__ __forceinline__ bool tile_skipped(const GemmArgs& g, int mi, int nj) {
     return g.lower_only && (nj * GT_N > mi * GT_M + GT_M - 1);
 }
@@ -117,11 +132,12 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         if (lane == 0) {
             uint32_t stage = 0, phase = 0, armed = 0, armed_phase = 0;
             bool ok = true;
+            PROF_DECL
             for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
                 const int mi = t / g.n_tiles, nj = t % g.n_tiles;
                 if (tile_skipped(g, mi, nj)) continue;
                 for (int ks = 0; ks < k_steps; ++ks) {
-                    ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag);
+                    ok = PROF_WAIT(mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag));
                     if (!ok) break;
                     const uint32_t sa = smem_u32(smem + stage * GT_STAGE_BYTES);
                     const uint32_t sb = sa + GT_A_BYTES;
@@ -132,6 +148,8 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     tma_load_2d(sa, &map_a, ks * GT_K, mi * GT_M, fb);                    // 32 k x 128 rows
                     if (g.b_is_nk) {
                         tma_load_2d(sb, &map_b, ks * GT_K, nj * GT_N, fb);                // 32 k x 256 rows
+                    } else if (g.b_slabs) {
+                        tma_load_3d(sb, &map_b, 0, ks * GT_K, nj * (GT_N / 32), fb);      // 8 slabs of 32 cols x 32 k-rows
                     } else {
 #pragma unroll
                         for (int b = 0; b < GT_N / 32; ++b)                               // 32 cols x 32 k-rows each
@@ -140,6 +158,7 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     if (++stage == GT_STAGES) { stage = 0; phase ^= 1; }
                 }
             }
+            PROF_END(0, 8);
             for (int s = 0; s < GT_STAGES; ++s) {          // drain copies in flight before smem goes away
                 if (!(armed >> s & 1u)) continue;
                 const unsigned long long t0 = global_ns();
@@ -153,18 +172,28 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             const uint32_t idesc = tf32_idesc(g.b_is_nk ? 0 : 1);
             uint32_t stage = 0, phase = 0, unit = 0;
             bool ok = true;
+            PROF_DECL
+#ifdef CRB_GEMM_PROFILE
+            unsigned long long prof_te = 0;
+#endif
             for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
                 const int mi = t / g.n_tiles, nj = t % g.n_tiles;
                 if (tile_skipped(g, mi, nj)) continue;
                 const uint32_t buf = unit & 1, use = unit >> 1;
                 ++unit;
+#ifdef CRB_GEMM_PROFILE
+                const unsigned long long pa_ = global_ns();
+#endif
                 ok = mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, abort_flag);
+#ifdef CRB_GEMM_PROFILE
+                prof_te += global_ns() - pa_;
+#endif
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * GT_N;
                 bool first = true;
                 for (int ks = 0; ks < k_steps; ++ks) {
-                    ok = mbar_wait(ready0 + 8 * stage, phase, abort_flag);
+                    ok = PROF_WAIT(mbar_wait(ready0 + 8 * stage, phase, abort_flag));
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t a_hi = smem_u32(smem + stage * GT_STAGE_BYTES), b_hi = a_hi + GT_A_BYTES;
@@ -187,17 +216,22 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 }
                 if (ok) umma_commit(tfull0 + 8 * buf);
             }
+            PROF_END(2, 7);
+#ifdef CRB_GEMM_PROFILE
+            atomicAdd(&g_gemm_prof[3], prof_te);
+#endif
         }
     } else if (warp < 6) {
         // ---------------- splitter: hi = x with 13 low mantissa bits cleared, lo = x - hi ----------------
         const int ctid = threadIdx.x - 64;                  // 0..127
         uint32_t stage = 0, phase = 0;
         bool ok = true;
+        PROF_DECL
         for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
             const int mi = t / g.n_tiles, nj = t % g.n_tiles;
             if (tile_skipped(g, mi, nj)) continue;
             for (int ks = 0; ks < k_steps; ++ks) {
-                ok = mbar_wait(full0 + 8 * stage, phase, abort_flag);
+                ok = PROF_WAIT(mbar_wait(full0 + 8 * stage, phase, abort_flag));
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 float4* hi = reinterpret_cast<float4*>(smem + stage * GT_STAGE_BYTES);
@@ -220,6 +254,7 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 if (++stage == GT_STAGES) { stage = 0; phase ^= 1; }
             }
         }
+        if (threadIdx.x == 64) { PROF_END(1, 6); }
     } else {
         // ---------------- epilogue: warps 6..13; warp w reads TMEM lanes 32 * (w % 4) .. +31 and the
         // column half (w - 6) / 4 of the accumulator ----------------
@@ -227,6 +262,7 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const int c_begin = ((warp - 6) >> 2) * (GT_N / 2);
         uint32_t unit = 0;
         bool ok = true;
+        PROF_DECL
         for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
             const int mi = t / g.n_tiles, nj = t % g.n_tiles;
             if (tile_skipped(g, mi, nj)) continue;
@@ -249,17 +285,20 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 // so that a triangular matrix updated this way keeps exact zeros there
                 return row < g.M && col < g.N && !(g.lower_only && col > (row | 127));
             };
+            // beta == 1 (the rank-128 updates): C += alpha * acc goes out as vector reductions that
+            // the L2 performs, so the SM never waits for the old values of C
+            const bool use_red = (g.beta == 1.0f);
             auto fetch = [&](int c, float4 (&dst)[8]) {
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     dst[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (g.beta != 0.f && live(c, k))
+                    if (g.beta != 0.f && !use_red && live(c, k))
                         dst[k] = *reinterpret_cast<const float4*>(g.C + (int64_t)(row0 + 4 * k) * g.ldc + colbase + 32 * c);
                 }
             };
             fetch(0, o[0]);
             fetch(1, o[1]);
-            ok = mbar_wait(tfull0 + 8 * buf, use & 1, abort_flag);
+            ok = PROF_WAIT(mbar_wait(tfull0 + 8 * buf, use & 1, abort_flag));
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -277,12 +316,19 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 for (int k = 0; k < 8; ++k) {
                     const float* src = patch + (r_sub + 4 * k) * 33 + 4 * cg;
                     if (live(c, k)) {
-                        float4 w;
-                        w.x = fmaf(g.alpha, src[0], g.beta * oc[k].x);
-                        w.y = fmaf(g.alpha, src[1], g.beta * oc[k].y);
-                        w.z = fmaf(g.alpha, src[2], g.beta * oc[k].z);
-                        w.w = fmaf(g.alpha, src[3], g.beta * oc[k].w);
-                        *reinterpret_cast<float4*>(g.C + (int64_t)(row0 + 4 * k) * g.ldc + colbase + 32 * c) = w;
+                        float* dst = g.C + (int64_t)(row0 + 4 * k) * g.ldc + colbase + 32 * c;
+                        if (use_red) {
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                                         ::"l"(dst), "f"(g.alpha * src[0]), "f"(g.alpha * src[1]),
+                                           "f"(g.alpha * src[2]), "f"(g.alpha * src[3]) : "memory");
+                        } else {
+                            float4 w;
+                            w.x = fmaf(g.alpha, src[0], g.beta * oc[k].x);
+                            w.y = fmaf(g.alpha, src[1], g.beta * oc[k].y);
+                            w.z = fmaf(g.alpha, src[2], g.beta * oc[k].z);
+                            w.w = fmaf(g.alpha, src[3], g.beta * oc[k].w);
+                            *reinterpret_cast<float4*>(dst) = w;
+                        }
                     }
                 }
                 __syncwarp();
@@ -292,6 +338,7 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
         }
+        if (warp == 6 && lane == 0) { PROF_END(4, 5); }
     }
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag && g.status) atomicOr(g.status, CRB_FLAG_WAIT_LIMIT);
@@ -318,11 +365,21 @@ int gemm_tf32x3(bool b_is_nk, bool lower_only, int M, int N, int K, float alpha,
     if (b_is_nk)
         rc = make_tensor_map_2d(&map_b, B, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)K, (uint64_t)N, (uint64_t)ldb,
                                 GT_K, GT_N);
-    else
-        rc = make_tensor_map_2d(&map_b, B, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)N, (uint64_t)K, (uint64_t)ldb,
-                                32, GT_K, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    int b_slabs = 0;
+    if (!b_is_nk) {
+        // one 3-D copy for the eight 32-column slabs of a stage when the driver accepts that shape
+        rc = make_tensor_map_slabs(&map_b, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, GT_K, GT_N / 32,
+                                   CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+        if (rc == CRB_OK) {
+            b_slabs = 1;
+        } else {
+            rc = make_tensor_map_2d(&map_b, B, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)N, (uint64_t)K, (uint64_t)ldb,
+                                    32, GT_K, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+        }
+    }
     if (rc != CRB_OK) return rc;
     GemmArgs g;
+    g.b_slabs = b_slabs;
     g.C = C; g.ldc = ldc; g.M = M; g.N = N; g.K = K; g.alpha = alpha; g.beta = beta;
     g.b_is_nk = b_is_nk ? 1 : 0; g.lower_only = lower_only ? 1 : 0;
     g.m_tiles = (M + GT_M - 1) / GT_M; g.n_tiles = (N + GT_N - 1) / GT_N;
@@ -345,5 +402,16 @@ int gemm_tf32x3(bool b_is_nk, bool lower_only, int M, int N, int K, float alpha,
     CRB_LAUNCHED();
     return CRB_OK;
 }
+
+#ifdef CRB_GEMM_PROFILE
+extern "C" void crb_gemm_profile_read(unsigned long long* out16, int reset) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out16, g_gemm_prof, sizeof(unsigned long long) * 16);
+    if (reset) {
+        unsigned long long z[16] = {0};
+        cudaMemcpyToSymbol(g_gemm_prof, z, sizeof(z));
+    }
+}
+#endif
 
 }  // namespace crb

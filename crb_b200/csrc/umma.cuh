@@ -127,4 +127,28 @@ inline int make_tensor_map_2d(CUtensorMap* map, const void* base, CUtensorMapDat
     return r == CUDA_SUCCESS ? CRB_OK : CRB_ERR_BAD_ARG;
 }
 
+// 3-D tiled map that fetches `chunks` side-by-side 32-column slabs of a row-major float32
+// matrix in ONE copy: dim0 = 32 columns of a slab, dim1 = rows (stride ld), dim2 = slab index
+// (stride 128 bytes).  A box {32, box_rows, chunks} lands as [slab][row][128 bytes], i.e. as
+// `chunks` consecutive 2-D boxes.  Returns CRB_ERR_UNSUPPORTED if the driver rejects the shape.
+inline int make_tensor_map_slabs(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows, uint64_t ld,
+                                 uint32_t box_rows, uint32_t chunks, CUtensorMapSwizzle swizzle) {
+    EncodeTiledFn enc = tensor_map_encoder();
+    if (!enc) return CRB_ERR_LAUNCH;
+    const cuuint64_t dims[3] = {32, rows, (cols + 31) / 32};
+    const cuuint64_t strides[2] = {ld * 4ull, 128ull};
+    const cuuint32_t box[3] = {32, box_rows, chunks};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? CRB_OK : CRB_ERR_UNSUPPORTED;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
 }  // namespace crb
