@@ -106,11 +106,16 @@ class BRAGPTQ:
         state = self.fasterquant_begin(blocksize, percdamp, partition, orders, global_scale)
         return self.fasterquant_end(state)
 
-    # The two halves below let a caller overlap several linears: `begin` only enqueues work on the
-    # current stream (factorisation attempt 0); `end` handles the rare damping retry, enqueues the
-    # block loop, synchronises and writes the weight back.
+    # The three steps below let a caller overlap several linears, each on its own stream:
+    #   begin  - enqueues the factorisation (attempt 0); no host synchronisation
+    #   blocks - reads the factorisation status (waits for that stream only), handles the rare
+    #            damping retry and enqueues the whole block loop; returns without waiting for it
+    #   end    - waits for the block loop, reads the error and writes the weight back
+    # A caller with several linears runs every `begin`, then every `blocks`, then every `end`.
+    # `factor_from` names the state of another linear with the very same Hessian (q/k/v of one
+    # attention block): its factor U is read instead of computing an identical one.
     def fasterquant_begin(self, blocksize=128, percdamp=0.01, partition=3, orders=(1, 1, 2),
-                          global_scale=False):
+                          global_scale=False, factor_from=None):
         technique = getattr(self.braq_quantizer, "method", None)
         if technique not in ("braq", "crbog", "crb"):
             raise NotImplementedError(f"technique {technique!r}: only braq, crbog and crb are implemented")
@@ -127,7 +132,7 @@ class BRAGPTQ:
             raise NotImplementedError(f"in_features must be a multiple of {BLOCK}")
 
         st = {"tick": time.time(), "percdamp": percdamp, "technique": technique,
-              "stream": torch.cuda.current_stream(self.dev),
+              "stream": torch.cuda.current_stream(self.dev), "leader": factor_from,
               "ev": [torch.cuda.Event(enable_timing=True) for _ in range(3)]}
         W = self.layer.weight.data.clone()
         if isinstance(self.layer, nn.Conv2d):
@@ -135,6 +140,14 @@ class BRAGPTQ:
         if _Conv1D and isinstance(self.layer, _Conv1D):
             W = W.t()
         st["W"] = W.float().contiguous()
+        st["ev"][0].record()
+        if factor_from is not None:
+            if factor_from["percdamp"] != percdamp or factor_from["H"].shape[0] != self.columns:
+                raise CrbError("factor_from: the other linear does not have the same Hessian and damping")
+            # dead input channels zero the weight column (bigptq.py:103-105); the factor is the leader's
+            st["W"].masked_fill_((factor_from["diag0"] == 0).unsqueeze(0), 0.0)
+            self._H_set, self._S, self._H_keep = None, None, None
+            return st
         # the reference consumes H here (bigptq.py:101-102)
         if self._H_set is not None:
             H, self._H_keep = self._H_set.clone(), self._H_set
@@ -144,30 +157,47 @@ class BRAGPTQ:
         st["H"] = H
         st["diag0"] = torch.diagonal(H).clone()
         st["status"] = torch.zeros(4, dtype=torch.int32, device=self.dev)
-        st["ev"][0].record()
         ops.factor_enqueue(H, st["W"], percdamp, 0, st["status"])
         return st
 
-    def fasterquant_end(self, st):
+    def fasterquant_blocks(self, st):
+        if "out" in st:
+            return st
         with torch.cuda.stream(st["stream"]):
-            H, W = st["H"], st["W"]
-            attempt = 0
-            while int(st["status"][0].item()) & FLAG_BAD_PIVOT:          # bigptq.py:115-123
-                attempt += 1
-                if attempt > 10:
-                    ops.diagonal_fallback(H, st["diag0"], st["percdamp"])   # bigptq.py:124-126
-                    break
-                self._restore_hessian(H)
-                st["status"].zero_()
-                ops.factor_enqueue(H, W, st["percdamp"], attempt, st["status"])
-            U = H
+            W = st["W"]
+            if st["leader"] is not None:
+                lead = st["leader"]
+                if "factor_done" not in lead:
+                    raise CrbError("factor_from: run fasterquant_blocks of the other linear first")
+                st["stream"].wait_event(lead["factor_done"])
+                U = lead["H"]
+            else:
+                H = st["H"]
+                attempt = 0
+                while int(st["status"][0].item()) & FLAG_BAD_PIVOT:          # bigptq.py:115-123
+                    attempt += 1
+                    if attempt > 10:
+                        ops.diagonal_fallback(H, st["diag0"], st["percdamp"])   # bigptq.py:124-126
+                        break
+                    self._restore_hessian(H)
+                    st["status"].zero_()
+                    ops.factor_enqueue(H, W, st["percdamp"], attempt, st["status"])
+                U = H
+                st["factor_done"] = torch.cuda.Event()
+                st["factor_done"].record()
+                self._H_set, self._S, self._H_keep = None, None, None
             st["ev"][1].record()
-            self._H_set, self._S, self._H_keep = None, None, None
             lam = float(getattr(self.braq_quantizer, "lam", 1e-5))
             corr_damp = float(getattr(self.braq_quantizer, "corr_damp", 0.1))
-            out = ops.quantize_linear(W, U, st["technique"], lam, corr_damp, self.salient_metric,
-                                      want_codes=False, want_trace=True)
+            st["out"] = ops.quantize_linear(W, U, st["technique"], lam, corr_damp, self.salient_metric,
+                                            want_codes=False, want_trace=True)
             st["ev"][2].record()
+        return st
+
+    def fasterquant_end(self, st):
+        self.fasterquant_blocks(st)
+        with torch.cuda.stream(st["stream"]):
+            out, W = st["out"], st["W"]
             error = torch.sum(out["losses"]).item()                     # synchronises this stream
             flags = ops.read_status(out["workspace"])
             if flags & ~FLAG_NONFINITE:

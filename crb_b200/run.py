@@ -178,6 +178,10 @@ def _stream_pool(dev, n):
     return pool
 
 
+class _TailReached(Exception):
+    """Raised by the hook of a layer's last linear to end a calibration forward early."""
+
+
 def _layer_out(res):
     return res[0] if isinstance(res, (tuple, list)) else res
 
@@ -246,24 +250,35 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
     seen: Dict[tuple, tuple] = {}
     cur = {"batch": 1}
 
+    # The hooks run BEFORE each linear: add_batch only needs the input (bigptq.py:37-54 never reads
+    # `out`).  The first forward of the layer records the order in which the linears are called;
+    # in the following ones the hook of the last linear stops the forward right after its Hessian
+    # update, because nothing computed from there on is used: the outputs of this pass are
+    # overwritten by the re-propagation with the quantized weights (run.py:376-377).
+    call_order: List[str] = []
+
     def make_hook(name):
-        def hook(_, inp, out):
+        def hook(_, inp):
             x = inp[0].data
             if x.dim() == 2 and cur["batch"] > 1:
                 # some layers flatten [batch, tokens, C] before their linears (OPT fc1 / fc2); the
                 # sample count of add_batch is the number of sequences (bigptq.py:41-49)
                 x = x.reshape(cur["batch"], -1, x.shape[-1])
+            if cur["last"] is None:
+                call_order.append(name)
             key = (x.data_ptr(), tuple(x.shape), x.dtype)
-            if name in alias:
-                return
-            if key in seen and seen[key][0] != name:
-                alias[name] = seen[key][0]
-                return
-            seen[key] = (name, x)              # keeps x alive so that its address stays unique
-            gptq[name].add_batch(x, out.data)
+            if name not in alias:
+                if key in seen and seen[key][0] != name:
+                    alias[name] = seen[key][0]
+                else:
+                    seen[key] = (name, x)      # keeps x alive so that its address stays unique
+                    gptq[name].add_batch(x, None)
+            if name == cur["last"]:
+                raise _TailReached()
         return hook
 
-    handles = [subset[name].register_forward_hook(make_hook(name)) for name in gptq]
+    cur["last"] = None
+    handles = [subset[name].register_forward_pre_hook(make_hook(name)) for name in gptq]
     n_local = inps.shape[0]
     fb = max(1, int(args.forward_batch))
     with timer.span("forward_hessian"):
@@ -271,7 +286,13 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
             x = inps[j:j + fb].to(dev, non_blocking=True)
             seen.clear()
             cur["batch"] = x.shape[0]
-            layer(x, **_replay_kwargs(layer_kwargs, x.shape[0]))
+            try:
+                layer(x, **_replay_kwargs(layer_kwargs, x.shape[0]))
+            except _TailReached:
+                pass
+            if j == 0 and getattr(args, "skip_dead_tail", True) and call_order \
+                    and call_order.count(call_order[-1]) == 1:
+                cur["last"] = call_order[-1]
         seen.clear()
     for h in handles:
         h.remove()
@@ -302,13 +323,23 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
             ready = torch.cuda.Event()
             ready.record(main)
             pool = _stream_pool(dev, len(order))
-            for slot, name in enumerate(order):
-                s = pool[slot]
+            slot_of = {name: slot for slot, name in enumerate(order)}
+            # linears that share a Hessian on this rank share its factor: leaders first
+            lead_of = {n: alias[n] for n in order if n in alias and alias[n] in slot_of}
+            begin_order = [n for n in order if n not in lead_of] + [n for n in order if n in lead_of]
+            for name in begin_order:
+                s = pool[slot_of[name]]
                 s.wait_event(ready)
                 with torch.cuda.stream(s):
-                    states[name] = gptq[name].fasterquant_begin(percdamp=args.percdamp, blocksize=args.blocksize,
-                                                                partition=args.partition,
-                                                                global_scale=args.global_scale)
+                    states[name] = gptq[name].fasterquant_begin(
+                        percdamp=args.percdamp, blocksize=args.blocksize, partition=args.partition,
+                        global_scale=args.global_scale,
+                        factor_from=states[lead_of[name]] if name in lead_of else None)
+            # cheapest factorisations finish first: enqueue their block loops as soon as they are checked
+            for name in reversed(begin_order[:len(order) - len(lead_of)]):
+                gptq[name].fasterquant_blocks(states[name])
+                for other in (n for n in lead_of if lead_of[n] == name):
+                    gptq[other].fasterquant_blocks(states[other])
         for name in (reversed(order) if concurrent else mine):
             if args.verbose:
                 print(index, name)
@@ -322,6 +353,7 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
             errors[name] = info["error"]
             for k, v in gptq[name].last_timing.items():
                 timer.ms[k] = timer.ms.get(k, 0.0) + v
+        states.clear()
         for name in gptq:
             gptq[name].free()
     with timer.span("weight_broadcast"):
