@@ -10,16 +10,12 @@ unsigned long long g_launches = 0;
 // block_step.cu
 size_t block_workspace_bytes(int R);
 int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu, int block,
-                      int technique, float lam, float corr_damp, int metric, float* Err,
+                      int technique, float lam, float corr_damp, int metric, float* Err, int64_t ld_err,
                       float* Losses, unsigned char* codes, int64_t ld_codes, float* scales,
                       double* trace, void* workspace, size_t workspace_bytes, cudaStream_t st);
 int binarize_group_launch(const float* W, int R, int64_t ldw, const unsigned char* mask, int64_t ldm,
                           int order, int technique, float lam, float corr_damp, float* Q, int64_t ldq,
                           cudaStream_t st);
-// gemm_tc.cu
-int gemm_tf32x3(bool b_is_nk, bool lower_only, int M, int N, int K, float alpha, const float* A, int64_t lda,
-                const float* B, int64_t ldb, float beta, float* C, int64_t ldc, unsigned* status,
-                cudaStream_t st);
 // hessian.cu
 size_t hessian_workspace_bytes(int C, int64_t T, int dtype);
 int hessian_accumulate_launch(const void* X, int dtype, int64_t T, int C, int64_t ldx, float* S,
@@ -86,7 +82,7 @@ int crb_block_step(float* W, int R, int64_t ldw, const float* U, int64_t ldu, in
     // `codes` is [R, 128] for a single block: offset the base so that column (block*128 + j)
     // of a virtual [R, ldw]-wide buffer lands on codes[r, j].
     uint8_t* codes_base = codes ? codes - (int64_t)block * kBlock : nullptr;
-    return block_step_launch(W, R, ldw, U, ldu, block, technique, lam, corr_damp, metric, Err, Losses,
+    return block_step_launch(W, R, ldw, U, ldu, block, technique, lam, corr_damp, metric, Err, kBlock, Losses,
                              codes_base, kBlock, scales, trace, workspace, workspace_bytes,
                              static_cast<cudaStream_t>(stream));
 }
@@ -103,7 +99,7 @@ static int trailing_update_impl(float* W, int R, int C, int64_t ldw, const float
     const int ed = (block + 1) * kBlock;
     if (ed > C) return CRB_ERR_BAD_ARG;
     if (ed == C) return CRB_OK;
-    return gemm_tf32x3(false, false, R, C - ed, kBlock, -1.0f, Err, kBlock, U + (int64_t)block * kBlock * ldu + ed,
+    return gemm_tf32x3(false, 0, R, C - ed, kBlock, -1.0f, Err, kBlock, U + (int64_t)block * kBlock * ldu + ed,
                        ldu, 1.0f, W + ed, ldw, status, st);
 }
 
@@ -112,15 +108,24 @@ int crb_trailing_update(float* W, int R, int C, int64_t ldw, const float* Err, c
     return trailing_update_impl(W, R, C, ldw, Err, U, ldu, block, nullptr, static_cast<cudaStream_t>(stream));
 }
 
-int crb_gemm_f32(int b_is_nk, int lower_only, int M, int N, int K, float alpha, const float* A, int64_t lda,
+int crb_gemm_f32(int b_is_nk, int shape, int M, int N, int K, float alpha, const float* A, int64_t lda,
                  const float* B, int64_t ldb, float beta, float* C, int64_t ldc, unsigned* status, void* stream) {
-    return gemm_tf32x3(b_is_nk != 0, lower_only != 0, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, status,
+    return gemm_tf32x3(b_is_nk != 0, shape, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, status,
                        static_cast<cudaStream_t>(stream));
 }
 
+// Blocks per group of the block loop.  Inside a group a block's error is propagated to the group's
+// remaining columns right away (K = 128); the columns right of the group receive the group's
+// errors in one product with K = kGroup * 128 once its last block is done.  The sums are the ones
+// of bigptq.py:264, associated differently; the trailing part of W is read and written once per
+// group instead of once per block.
+constexpr int kGroup = 8;
+static_assert(CRB_GEMM_LOWER_ONLY == GEMM_LOWER_ONLY && CRB_GEMM_B_LOWER == GEMM_B_LOWER &&
+              CRB_GEMM_A_LOWER == GEMM_A_LOWER, "shape flags of the header and of the kernel");
+
 size_t crb_linear_workspace_bytes(int R) {
     if (R <= 0) return 0;
-    return align256(block_workspace_bytes(R)) + align256(sizeof(float) * (size_t)R * kBlock);
+    return align256(block_workspace_bytes(R)) + align256(sizeof(float) * (size_t)R * kBlock * kGroup);
 }
 
 int crb_quantize_linear(float* W, int R, int C, int64_t ldw, const float* U, int64_t ldu,
@@ -132,16 +137,28 @@ int crb_quantize_linear(float* W, int R, int C, int64_t ldw, const float* U, int
     if (workspace_bytes < crb_linear_workspace_bytes(R)) return CRB_ERR_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t bws = align256(block_workspace_bytes(R));
-    float* Err = reinterpret_cast<float*>(static_cast<char*>(workspace) + bws);
+    float* ErrG = reinterpret_cast<float*>(static_cast<char*>(workspace) + bws);      // [R, kGroup * 128]
+    const int64_t ld_err = (int64_t)kGroup * kBlock;
+    unsigned* status = static_cast<unsigned*>(workspace);
     if (cudaMemsetAsync(workspace, 0, 64, st) != cudaSuccess) return CRB_ERR_LAUNCH;   // status word
     const int nblk = C / kBlock;
     for (int b = 0; b < nblk; ++b) {
-        int rc = block_step_launch(W, R, ldw, U, ldu, b, technique, lam, corr_damp, metric, Err, Losses, codes,
+        const int g0 = b / kGroup * kGroup, g1 = g0 + kGroup < nblk ? g0 + kGroup : nblk;
+        float* Err = ErrG + (size_t)(b - g0) * kBlock;
+        int rc = block_step_launch(W, R, ldw, U, ldu, b, technique, lam, corr_damp, metric, Err, ld_err, Losses, codes,
                                    C, scales ? scales + (size_t)b * R * 8 : nullptr,
                                    trace ? trace + (size_t)b * CRB_TRACE_DOUBLES : nullptr, workspace, bws, st);
         if (rc != CRB_OK) return rc;
-        rc = trailing_update_impl(W, R, C, ldw, Err, U, ldu, b, static_cast<unsigned*>(workspace), st);
+        const int ed = (b + 1) * kBlock;
+        rc = gemm_tf32x3(false, 0, R, g1 * kBlock - ed, kBlock, -1.0f, Err, ld_err,
+                         U + (int64_t)b * kBlock * ldu + ed, ldu, 1.0f, W + ed, ldw, status, st);
         if (rc != CRB_OK) return rc;
+        if (b == g1 - 1 && g1 < nblk) {
+            const int gd = g1 * kBlock;
+            rc = gemm_tf32x3(false, 0, R, C - gd, (g1 - g0) * kBlock, -1.0f, ErrG, ld_err,
+                             U + (int64_t)g0 * kBlock * ldu + gd, ldu, 1.0f, W + gd, ldw, status, st);
+            if (rc != CRB_OK) return rc;
+        }
     }
     return CRB_OK;
 }

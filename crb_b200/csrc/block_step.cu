@@ -1137,8 +1137,8 @@ __global__ void __launch_bounds__(256)
 k_finalize(float* __restrict__ W, int R, int64_t ldw, int col0, const float* __restrict__ U,
            int64_t ldu, const unsigned char* __restrict__ rank, const int* __restrict__ sel,
            const float* __restrict__ pvals, int technique, float lam, float corr_damp,
-           float* __restrict__ Err, float* __restrict__ Losses, unsigned char* __restrict__ codes,
-           int64_t ld_codes, float* __restrict__ scales) {
+           float* __restrict__ Err, int64_t ld_err, float* __restrict__ Losses,
+           unsigned char* __restrict__ codes, int64_t ld_codes, float* __restrict__ scales) {
     __shared__ float s_d[kBlock];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = row_in_warp(lane), l = lane_in_row(lane);
@@ -1199,7 +1199,7 @@ k_finalize(float* __restrict__ W, int R, int64_t ldw, int col0, const float* __r
     loss = red8(loss);
     if (!live) return;
     store_row16(W + (int64_t)row * ldw + col0, l, q);
-    store_row16(Err + (int64_t)row * kBlock, l, e);
+    store_row16(Err + (int64_t)row * ld_err, l, e);
     if (l == 0) Losses[row] += loss * 0.5f;
     if (codes) {
 #pragma unroll
@@ -1265,10 +1265,11 @@ static int ceil_div(int a, int b) { return (a + b - 1) / b; }
 size_t block_workspace_bytes(int R) { return carve_block_ws(nullptr, R, nullptr); }
 
 int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu, int block,
-                      int technique, float lam, float corr_damp, int metric, float* Err,
+                      int technique, float lam, float corr_damp, int metric, float* Err, int64_t ld_err,
                       float* Losses, unsigned char* codes, int64_t ld_codes, float* scales,
                       double* trace, void* workspace, size_t workspace_bytes, cudaStream_t st) {
     if (!W || !U || !Err || !Losses || !workspace || R <= 0 || block < 0) return CRB_ERR_BAD_ARG;
+    if (ld_err < kBlock || (ld_err & 3)) return CRB_ERR_BAD_ARG;
     if (technique < CRB_TECH_BRAQ || technique > CRB_TECH_CRB) return CRB_ERR_BAD_ARG;
     if (metric != CRB_METRIC_HESSIAN) return CRB_ERR_UNSUPPORTED;
     if ((ldw & 3) || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(Err) & 15))
@@ -1322,7 +1323,7 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
     CRB_LAUNCHED();
     // K7
     k_finalize<<<ceil_div(R, 32), 256, 0, st>>>(W, R, ldw, col0, U, ldu, ws.rank, ws.sel, ws.pvals, technique,
-                                               lam, corr_damp, Err, Losses, codes, ld_codes, scales);
+                                               lam, corr_damp, Err, ld_err, Losses, codes, ld_codes, scales);
     CRB_LAUNCHED();
     return CRB_OK;
 }

@@ -80,4 +80,12 @@ __device__ __forceinline__ bool last_cta_done(unsigned* counter, unsigned total)
     return s_last;
 }
 
+// Shape flags of gemm_tf32x3 (gemm_tc.cu).
+constexpr int GEMM_LOWER_ONLY = 1;   // write only the 128 x 128 blocks of C on or below the diagonal
+constexpr int GEMM_B_LOWER = 2;      // the [K, N] operand B is lower triangular (zero for k < n)
+constexpr int GEMM_A_LOWER = 4;      // the [M, K] operand A is lower triangular (zero for k > m)
+int gemm_tf32x3(bool b_is_nk, int shape, int M, int N, int K, float alpha, const float* A, int64_t lda,
+                const float* B, int64_t ldb, float beta, float* C, int64_t ldc, unsigned* status,
+                cudaStream_t st);
+
 }  // namespace crb

@@ -8,21 +8,20 @@
 // V = reverse(L)), so U = reverse(L^-1): one factorisation and one triangular inverse
 // (2 C^3 / 3 flop) instead of the reference's three library calls (4 C^3 / 3 flop).
 //
-// Blocked with 128-wide panels.  Per panel: one CTA factors the 128x128 diagonal block in
-// shared memory and inverts it; the panel below is multiplied by that inverse and the trailing
-// matrix gets a rank-128 update, both through the split-TF32 tensor-core GEMM (gemm_tc.cu).  The triangular inverse
-// merges neighbouring diagonal blocks recursively: [[A,0],[B,D]]^-1 = [[A^-1,0],[-D^-1 B A^-1, D^-1]].
+// Blocked at two levels.  Per 128-wide diagonal block: one CTA factors the 128x128 block in
+// shared memory and inverts it; the rows below are multiplied by that inverse and the rest of
+// the current 1024-wide outer panel gets a rank-128 update.  After the panel's last block the
+// whole trailing matrix is updated once with K = 1024.  All products run through the split-TF32
+// tensor-core GEMM (gemm_tc.cu).  The triangular inverse merges neighbouring diagonal blocks
+// recursively: [[A,0],[B,D]]^-1 = [[A^-1,0],[-D^-1 B A^-1, D^-1]], skipping the zero halves.
 // A non-positive pivot sets CRB_FLAG_BAD_PIVOT (the host re-damps and calls again, like the
 // retry loop at bigptq.py:115-123) and is replaced by 1 so that nothing non-finite spreads.
 #include "common.cuh"
 
 namespace crb {
 
-int gemm_tf32x3(bool b_is_nk, bool lower_only, int M, int N, int K, float alpha, const float* A, int64_t lda,
-                const float* B, int64_t ldb, float beta, float* C, int64_t ldc, unsigned* status,
-                cudaStream_t st);
-
 constexpr int FB = 128;    // panel width
+constexpr int kOuter = 8;  // diagonal blocks per outer panel of the factorisation
 
 // diag statistics: dead columns, mean of the diagonal after the dead fix, total damping.
 __global__ void __launch_bounds__(1024)
@@ -300,9 +299,10 @@ static int invert_range(float* A, int C, int lo, int hi, float* tmp, unsigned* s
     float* B = A + (int64_t)mid * FB * C + (int64_t)lo * FB;
     const float* Ainv = A + (int64_t)lo * FB * (C + 1);
     const float* Dinv = A + (int64_t)mid * FB * (C + 1);
-    rc = gemm_tf32x3(false, false, s2, s1, s1, 1.0f, B, C, Ainv, C, 0.0f, tmp, s1, status, st);      // T = B A^-1
+    // both inverses are lower triangular: their zero halves are not multiplied
+    rc = gemm_tf32x3(false, GEMM_B_LOWER, s2, s1, s1, 1.0f, B, C, Ainv, C, 0.0f, tmp, s1, status, st);      // T = B A^-1
     if (rc != CRB_OK) return rc;
-    return gemm_tf32x3(false, false, s2, s1, s2, -1.0f, Dinv, C, tmp, s1, 0.0f, B, C, status, st);   // B = -D^-1 T
+    return gemm_tf32x3(false, GEMM_A_LOWER, s2, s1, s2, -1.0f, Dinv, C, tmp, s1, 0.0f, B, C, status, st);   // B = -D^-1 T
 }
 
 int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp, int extra_steps,
@@ -333,16 +333,31 @@ int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
             return CRB_ERR_LAUNCH;
         attr_set = true;
     }
-    for (int k = 0; k < nb; ++k) {
-        float* Akk = A + (int64_t)k * FB * (C + 1);
-        k_chol_diag<<<1, kDiagThreads, kDiagSmem, st>>>(Akk, C, status);
-        CRB_LAUNCHED();
-        const int rem = C - (k + 1) * FB;
+    // Two levels of blocking: inside an outer panel of kOuter diagonal blocks the rank-128 updates
+    // touch the panel's own columns only; everything right of the panel gets one update with
+    // K = kOuter * 128 afterwards, which is compute bound instead of re-reading the whole trailing
+    // matrix once per diagonal block.
+    for (int k0 = 0; k0 < nb; k0 += kOuter) {
+        const int k1 = k0 + kOuter < nb ? k0 + kOuter : nb;
+        for (int k = k0; k < k1; ++k) {
+            float* Akk = A + (int64_t)k * FB * (C + 1);
+            k_chol_diag<<<1, kDiagThreads, kDiagSmem, st>>>(Akk, C, status);
+            CRB_LAUNCHED();
+            const int rem = C - (k + 1) * FB;
+            if (rem <= 0) break;
+            float* panel = Akk + (int64_t)FB * C;
+            int rc = gemm_tf32x3(true, 0, rem, FB, FB, 1.0f, panel, C, Akk, C, 0.0f, panel, C, status, st);   // P = A21 L^-T
+            if (rc != CRB_OK) return rc;
+            const int inside = (k1 - (k + 1)) * FB;         // columns of the outer panel still to factor
+            rc = gemm_tf32x3(true, GEMM_LOWER_ONLY, rem, inside, FB, -1.0f, panel, C, panel, C, 1.0f, panel + FB, C,
+                             status, st);                                                                   // A22[:, :inside] -= P P^T
+            if (rc != CRB_OK) return rc;
+        }
+        const int rem = C - k1 * FB;
         if (rem <= 0) break;
-        float* panel = Akk + (int64_t)FB * C;
-        int rc = gemm_tf32x3(true, false, rem, FB, FB, 1.0f, panel, C, Akk, C, 0.0f, panel, C, status, st);   // P = A21 L^-T
-        if (rc != CRB_OK) return rc;
-        rc = gemm_tf32x3(true, true, rem, rem, FB, -1.0f, panel, C, panel, C, 1.0f, panel + FB, C, status, st);  // A22 -= P P^T
+        const float* P = A + (int64_t)k1 * FB * C + (int64_t)k0 * FB;     // rows below the panel, the panel's columns
+        int rc = gemm_tf32x3(true, GEMM_LOWER_ONLY, rem, rem, (k1 - k0) * FB, -1.0f, P, C, P, C, 1.0f,
+                             A + (int64_t)k1 * FB * (C + 1), C, status, st);
         if (rc != CRB_OK) return rc;
     }
     int rc = invert_range(A, C, 0, nb, H, status, st);          // H is free to serve as scratch now

@@ -39,6 +39,8 @@ struct GemmArgs {
     int b_is_nk;          // 1: B is [N, K] row-major (K-major operand); 0: B is [K, N] row-major (MN-major)
     int lower_only;       // write only 128 x 128 blocks on or below the diagonal (tiles above it are skipped)
     int b_slabs;          // MN-major B: 1 = one 3-D copy per stage (map_b is a slab map), 0 = eight 2-D copies
+    int tri;              // bit 0: op(B)[k][n] = 0 for k < n (lower-triangular [K, N] operand): K starts at the tile's column
+                          // bit 1: A[m][k] = 0 for k > m (lower-triangular A): K ends with the tile's last row
     int m_tiles, n_tiles;
     unsigned* status;
 };
@@ -97,6 +99,15 @@ __device__ __forceinline__ bool tile_skipped(const GemmArgs& g, int mi, int nj) 
     return g.lower_only && (nj * GT_N > mi * GT_M + GT_M - 1);
 }
 
+// K steps [k0, k1) a tile has to run: all of them, less the part a triangular operand makes zero.
+__device__ __forceinline__ void tile_k_range(const GemmArgs& g, int mi, int nj, int* k0, int* k1) {
+    int lo = 0, hi = g.K / GT_K;
+    if (g.tri & 1) lo = (nj * GT_N) / GT_K;
+    if (g.tri & 2) hi = min(hi, (mi * GT_M + GT_M + GT_K - 1) / GT_K);
+    *k0 = min(lo, hi - 1);
+    *k1 = hi;
+}
+
 __global__ void __launch_bounds__(GT_THREADS, 1)
 k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
               const GemmArgs g) {
@@ -125,7 +136,6 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int total = g.m_tiles * g.n_tiles;
-    const int k_steps = g.K / GT_K;
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -136,7 +146,9 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
                 const int mi = t / g.n_tiles, nj = t % g.n_tiles;
                 if (tile_skipped(g, mi, nj)) continue;
-                for (int ks = 0; ks < k_steps; ++ks) {
+                int ks0, ks1;
+                tile_k_range(g, mi, nj, &ks0, &ks1);
+                for (int ks = ks0; ks < ks1; ++ks) {
                     ok = PROF_WAIT(mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag));
                     if (!ok) break;
                     const uint32_t sa = smem_u32(smem + stage * GT_STAGE_BYTES);
@@ -192,7 +204,9 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * GT_N;
                 bool first = true;
-                for (int ks = 0; ks < k_steps; ++ks) {
+                int ks0, ks1;
+                tile_k_range(g, mi, nj, &ks0, &ks1);
+                for (int ks = ks0; ks < ks1; ++ks) {
                     ok = PROF_WAIT(mbar_wait(ready0 + 8 * stage, phase, abort_flag));
                     if (!ok) break;
                     tc_fence_after();
@@ -230,7 +244,9 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
             const int mi = t / g.n_tiles, nj = t % g.n_tiles;
             if (tile_skipped(g, mi, nj)) continue;
-            for (int ks = 0; ks < k_steps; ++ks) {
+            int ks0, ks1;
+            tile_k_range(g, mi, nj, &ks0, &ks1);
+            for (int ks = ks0; ks < ks1; ++ks) {
                 ok = PROF_WAIT(mbar_wait(full0 + 8 * stage, phase, abort_flag));
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
@@ -351,10 +367,16 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
 // C[M,N] = alpha * A[M,K] * op(B) + beta * C on the tensor cores.
 // Requirements: K % 32 == 0, N % 32 == 0, leading dimensions % 4 == 0, 16-byte aligned bases.
 // `status` (device, may be NULL) receives CRB_FLAG_WAIT_LIMIT if a bounded wait ran out.
-int gemm_tf32x3(bool b_is_nk, bool lower_only, int M, int N, int K, float alpha, const float* A, int64_t lda,
+// `shape` is a set of GEMM_* flags: GEMM_LOWER_ONLY writes only the 128 x 128 blocks on or below
+// the diagonal of C; GEMM_B_LOWER / GEMM_A_LOWER promise a lower-triangular [K, N] operand B /
+// [M, K] operand A, whose zero part is then not multiplied.
+int gemm_tf32x3(bool b_is_nk, int shape, int M, int N, int K, float alpha, const float* A, int64_t lda,
                 const float* B, int64_t ldb, float beta, float* C, int64_t ldc, unsigned* status,
                 cudaStream_t st) {
     if (M <= 0 || N <= 0) return CRB_OK;
+    const bool lower_only = (shape & GEMM_LOWER_ONLY) != 0;
+    if ((shape & GEMM_B_LOWER) && (b_is_nk || N > K)) return CRB_ERR_BAD_ARG;
+    if ((shape & GEMM_A_LOWER) && M > K) return CRB_ERR_BAD_ARG;
     if (K <= 0 || (K % GT_K) || (N % 32) || (lda & 3) || (ldb & 3) || (ldc & 3)) return CRB_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
         return CRB_ERR_BAD_ARG;
@@ -382,6 +404,7 @@ int gemm_tf32x3(bool b_is_nk, bool lower_only, int M, int N, int K, float alpha,
     g.b_slabs = b_slabs;
     g.C = C; g.ldc = ldc; g.M = M; g.N = N; g.K = K; g.alpha = alpha; g.beta = beta;
     g.b_is_nk = b_is_nk ? 1 : 0; g.lower_only = lower_only ? 1 : 0;
+    g.tri = ((shape & GEMM_B_LOWER) ? 1 : 0) | ((shape & GEMM_A_LOWER) ? 2 : 0);
     g.m_tiles = (M + GT_M - 1) / GT_M; g.n_tiles = (N + GT_N - 1) / GT_N;
     g.status = status;
     static bool attr_set = false;

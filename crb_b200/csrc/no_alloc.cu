@@ -30,7 +30,7 @@ namespace crb {
 
 size_t block_workspace_bytes(int R);
 int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu, int block,
-                      int technique, float lam, float corr_damp, int metric, float* Err,
+                      int technique, float lam, float corr_damp, int metric, float* Err, int64_t ld_err,
                       float* Losses, unsigned char* codes, int64_t ld_codes, float* scales,
                       double* trace, void* workspace, size_t workspace_bytes, cudaStream_t st);
 
@@ -82,7 +82,7 @@ int crb_block_step_static(float* W, int R, int64_t ldw, const float* U, int64_t 
     // the status word is the first thing in the scratch; it must describe this call only
     if (cudaMemsetAsync(scratch, 0, 64, st) != cudaSuccess) return CRB_ERR_LAUNCH;
     uint8_t* codes_base = codes ? codes - (int64_t)block * kBlock : nullptr;   // codes is [R, 128]
-    rc = block_step_launch(W, R, ldw, U, ldu, block, technique, lam, corr_damp, metric, Err, Losses,
+    rc = block_step_launch(W, R, ldw, U, ldu, block, technique, lam, corr_damp, metric, Err, kBlock, Losses,
                            codes_base, kBlock, scales, trace, scratch, kStaticScratchBytes, st);
     if (rc != CRB_OK) return rc;
     if (flags_out &&

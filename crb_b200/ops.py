@@ -200,13 +200,17 @@ def trailing_update(W: torch.Tensor, Err: torch.Tensor, U: torch.Tensor, block: 
 
 
 def gemm_f32(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, alpha: float = 1.0, beta: float = 0.0,
-             b_is_nk: bool = False, lower_only: bool = False) -> torch.Tensor:
-    """C = alpha * A @ (B.T if b_is_nk else B) + beta * C on the tensor cores (hi/lo TF32 split)."""
+             b_is_nk: bool = False, lower_only: bool = False, b_lower: bool = False,
+             a_lower: bool = False) -> torch.Tensor:
+    """C = alpha * A @ (B.T if b_is_nk else B) + beta * C on the tensor cores (hi/lo TF32 split).
+
+    `b_lower` / `a_lower` promise a lower-triangular B [K, N] / A [M, K] whose zero part is skipped."""
     _need_cuda(A, B, C)
     M, K = A.shape
     N = B.shape[0] if b_is_nk else B.shape[1]
     status = torch.zeros(1, dtype=torch.int32, device=A.device)
-    check(lib().crb_gemm_f32(int(b_is_nk), int(lower_only), M, N, K, alpha, ptr(A), A.stride(0), ptr(B),
+    shape = int(lower_only) | 2 * int(b_lower) | 4 * int(a_lower)
+    check(lib().crb_gemm_f32(int(b_is_nk), shape, M, N, K, alpha, ptr(A), A.stride(0), ptr(B),
                              B.stride(0), beta, ptr(C), C.stride(0), ptr(status), stream_ptr()), "crb_gemm_f32")
     return C
 

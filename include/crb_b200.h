@@ -143,15 +143,23 @@ int crb_trailing_update(float *W_dev, int R, int C, int64_t ldw, const float *Er
  * cores with a hi/lo TF32 split of both operands (three products per term, float32
  * accumulation), which keeps float32-level accuracy; this is what stands in for the
  * reference's TF32-disabled torch matmuls (bigptq.py:11-12, :264 and the factorisation).
- * b_is_nk != 0: B is [N, K]; else B is [K, N].  lower_only != 0 skips tiles above the diagonal.
+ * b_is_nk != 0: B is [N, K]; else B is [K, N].  `shape` is a set of CRB_GEMM_* flags:
+ * LOWER_ONLY writes only the 128 x 128 blocks of C on or below its diagonal; B_LOWER promises
+ * a lower-triangular [K, N] operand B (needs b_is_nk == 0, N <= K) and A_LOWER a
+ * lower-triangular A (M <= K): the zero part of such an operand is not multiplied.
  * K % 32 == 0, N % 32 == 0, leading dimensions % 4 == 0; status (device, may be NULL).   */
-int crb_gemm_f32(int b_is_nk, int lower_only, int M, int N, int K, float alpha, const float *A_dev,
+#define CRB_GEMM_LOWER_ONLY 1
+#define CRB_GEMM_B_LOWER 2
+#define CRB_GEMM_A_LOWER 4
+int crb_gemm_f32(int b_is_nk, int shape, int M, int N, int K, float alpha, const float *A_dev,
                  int64_t lda, const float *B_dev, int64_t ldb, float beta, float *C_dev, int64_t ldc,
                  unsigned *status_dev, void *stream);
 
 /* ---- whole linear ----------------------------------------------------------------
  * The block loop of BRAGPTQ.fasterquant (bigptq.py:131-264) for all C/128 blocks:
- * block step + trailing update, no host synchronisation.  Buffers as above;
+ * block step + trailing update, no host synchronisation.  The updates are grouped: a block's
+ * error reaches the rest of its group of 8 blocks at once and the columns right of the group
+ * in one product per group (same sums as bigptq.py:264, associated differently).  Buffers as above;
  * codes [R, C], scales [C/128, R, 8], trace [C/128, 192] are optional.
  * Workspace: crb_linear_workspace_bytes(R).                                       */
 size_t crb_linear_workspace_bytes(int R);

@@ -136,6 +136,64 @@ def test_gemm_f32_keeps_float32_accuracy(ops):
         assert float(err.max()) < 3e-6, (M, N, K, b_is_nk, lower, float(err.max()))
 
 
+def test_gemm_f32_triangular_operands_and_long_k(ops):
+    """Operands promised lower triangular (their zero half is skipped), a rectangular lower-only
+    update as the factorisation's outer panels issue it, and K = 1024 with beta = 1."""
+    g = torch.Generator().manual_seed(12)
+    for M, N, K, kind in [(384, 512, 512, "b"), (640, 256, 640, "a"), (512, 768, 768, "b"), (128, 128, 128, "a"),
+                          (768, 384, 128, "rect"), (384, 640, 1024, "longk")]:
+        A = torch.randn(M, K, generator=g)
+        B = torch.randn(K, N, generator=g)
+        C0 = torch.randn(M, N, generator=g)
+        kw = {}
+        if kind == "b":
+            B = torch.tril(B)
+            kw["b_lower"] = True
+        if kind == "a":
+            A = torch.tril(A)
+            kw["a_lower"] = True
+        beta = 1.0 if kind in ("rect", "longk") else 0.0
+        if kind == "rect":
+            kw["lower_only"] = True
+        ref = 0.75 * (A.double() @ B.double()) + beta * C0.double()
+        mag = A.double().abs() @ B.double().abs() + C0.double().abs()
+        Cd = C0.to(DEV).clone()
+        ops.gemm_f32(A.to(DEV), B.to(DEV), Cd, alpha=0.75, beta=beta, **kw)
+        got = Cd.cpu().double()
+        err = (got - ref).abs() / mag
+        if kind == "rect":
+            keep = torch.zeros(M, N, dtype=torch.bool)
+            for mi in range(0, M, 128):
+                keep[mi:mi + 128, mi + 128:] = True
+            assert torch.equal(Cd.cpu()[keep], C0[keep])
+            err = err[~keep]
+        assert float(err.max()) < 3e-6, (M, N, K, kind, float(err.max()))
+
+
+def test_grouped_linear_loop_matches_per_block_calls(ops):
+    """crb_quantize_linear (updates grouped by 8 blocks) against block step + trailing update per block."""
+    g = torch.Generator().manual_seed(21)
+    R, C = 192, 128 * 11                    # one full group and a partial one
+    W = torch.randn(R, C, generator=g) * 0.02
+    U = torch.triu(torch.randn(C, C, generator=g) * (0.05 / C ** 0.5), 1) + torch.diag(0.5 + torch.rand(C, generator=g))
+    Wa, Wb, Ud = W.to(DEV).clone(), W.to(DEV).clone(), U.to(DEV).contiguous()
+    out = ops.quantize_linear(Wa, Ud, "braq", want_trace=True)
+    loss_b = torch.zeros(R, device=DEV)
+    same_decisions = True
+    for b in range(C // 128):
+        o = ops.block_step(Wb, Ud, b, "braq")
+        loss_b += o["losses"]
+        ops.trailing_update(Wb, o["Err"], Ud, b)
+        ta, tb = Hh.trace_fields(out["trace"][b]), Hh.trace_fields(o["trace"])
+        if (ta["n_salient"], ta["split_index"]) != (tb["n_salient"], tb["split_index"]):
+            assert min(ta["salient_gap"], tb["salient_gap"], ta["split_gap"], tb["split_gap"]) < Hh.TIE_GAP
+            same_decisions = False
+            break
+    if same_decisions:
+        assert torch.allclose(Wa, Wb, rtol=1e-4, atol=1e-6)
+        assert torch.allclose(out["losses"], loss_b, rtol=1e-4)
+
+
 def test_trailing_update_matches_fp32_matmul(ops):
     g = torch.Generator().manual_seed(3)
     for R, C, blk in ((96, 384, 0), (257, 512, 2), (128, 256, 1)):
