@@ -190,7 +190,8 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    n_layers = args.warmup + args.steps
+    per_arm = args.warmup + args.steps
+    n_layers = 2 * per_arm                      # layers [0, per_arm): resident arm; the rest: host arm
     model = crun.get_model(args.model, fill_device=str(dev), n_layers=n_layers)
     model.seqlen = args.seqlen
     qargs = crun.default_args(model=args.model, low_quant_method=args.technique, nsamples=args.nsamples,
@@ -223,6 +224,7 @@ def run_ours(args):
     host_out = torch.empty_like(host_in, pin_memory=True)
     dev_in = torch.empty((n_local, args.seqlen, hidden), dtype=dtype, device=dev)
     dev_out = torch.empty_like(dev_in)
+    dev_in.copy_(host_in)
     layer_kwargs = sink["kwargs"]
     sink["inps"].clear()
     layer_bytes = sum(p.numel() * p.element_size() for p in layers[0].parameters())
@@ -238,42 +240,71 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def one_step(i, timed):
-        nonlocal host_in, host_out
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-        ev[0].record()
-        resident = crun._Resident(layers[i], dev)
-        layer = resident.__enter__()                       # H2D of the layer's weights (pinned)
-        dev_in.copy_(host_in, non_blocking=True)           # H2D of the calibration activations
-        ev[1].record()
-        with torch.no_grad():
-            errs = crun.quantize_layer(layer, i, dev_in, dev_out, layer_kwargs, qargs, dev,
-                                       timer if timed else None)
-        ev[2].record()
-        host_out.copy_(dev_out, non_blocking=True)         # D2H of the layer outputs
-        resident.__exit__()                                # D2H of the quantized weights (+ sync)
-        ev[3].record()
-        host_in, host_out = host_out, host_in              # next layer calibrates on these outputs
+    # ---- arm 1 (`value`): weights and activations resident in HBM when a step starts ----
+    def resident_step(i, timed):
+        nonlocal dev_in, dev_out
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        with crun._Resident(layers[i], dev) as layer:
+            ev[0].record()
+            with torch.no_grad():
+                errs = crun.quantize_layer(layer, i, dev_in, dev_out, layer_kwargs, qargs, dev,
+                                           timer if timed else None)
+            ev[1].record()
+        dev_in, dev_out = dev_out, dev_in                  # next layer calibrates on these outputs
         if timed:
             step_events.append(ev)
             errors.append(sum(errs.values()))
 
     for i in range(args.warmup):
-        one_step(i, False)
+        resident_step(i, False)
     barrier()
     launches0 = ops.launch_count()
     sampler.start()
     t0 = time.time()
-    for i in range(args.warmup, n_layers):
-        one_step(i, True)
+    for i in range(args.warmup, per_arm):
+        resident_step(i, True)
     barrier()
     wall = time.time() - t0
     clocks = sampler.stop()
     launches = ops.launch_count() - launches0
     phases = timer.collect()
+    dev_ms = sum(e[0].elapsed_time(e[1]) for e in step_events)
 
-    dev_ms = sum(e[1].elapsed_time(e[2]) for e in step_events)
-    e2e_ms = sum(e[0].elapsed_time(e[3]) for e in step_events)
+    # ---- arm 2 (`e2e`): the same call on HOST buffers.  Weights and activations start every step in
+    # pinned host memory and end there; quantize_layer streams the activations through the device
+    # batch by batch (twice in, once out) and the weights of the next / previous layer move while a
+    # layer is being quantized.  Timed as a whole: first copy in to last copy out. ----
+    host_in.copy_(dev_in)
+    torch.cuda.synchronize()
+
+    def host_steps(first, count):
+        nonlocal host_in, host_out
+        nxt = crun._Resident(layers[first], dev).prefetch()
+        leaving = None
+        for i in range(first, first + count):
+            res, nxt = nxt, None
+            layer = res.__enter__()
+            if i + 1 < first + count:
+                nxt = crun._Resident(layers[i + 1], dev).prefetch()
+            with torch.no_grad():
+                crun.quantize_layer(layer, i, host_in, host_out, layer_kwargs, qargs, dev, None)
+            if leaving is not None:
+                leaving.finish()
+            res.__exit__(defer=True)
+            leaving = res
+            host_in, host_out = host_out, host_in
+        leaving.finish()
+        torch.cuda.current_stream().wait_stream(crun._copy_streams(dev)[1])
+
+    host_steps(per_arm, args.warmup)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    host_steps(per_arm + args.warmup, args.steps)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
     dev_ms = parallel.max_over_ranks(dev_ms, dev)
     e2e_ms = parallel.max_over_ranks(e2e_ms, dev)
     launches = int(parallel.sum_over_ranks(float(launches), dev))
@@ -298,8 +329,10 @@ def run_ours(args):
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32 (fp16 operands on the Hessian tensor cores)",
                 "data": "synthetic", "config": workload_config(args),
-                "e2e": {"value": e2e_value, "unit": "s", "h2d_bytes_per_step": layer_bytes + act_bytes,
-                        "d2h_bytes_per_step": layer_bytes + act_bytes + 8},
+                "e2e": {"value": e2e_value, "unit": "s", "h2d_bytes_per_step": layer_bytes + 2 * act_bytes,
+                        "d2h_bytes_per_step": layer_bytes + act_bytes + 8 * 6,
+                        "note": "same call on pinned host buffers; activations stream in twice (calibration and "
+                                "re-propagation pass) and out once per step, copies overlap compute"},
                 "gpu_launches": launches, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
                 "phases_ms_per_step": {k: v / args.steps for k, v in phases.items()},
                 "block_error_sum_per_layer": err_sum / args.steps, "wall_clock_s_timed_region": wall,
@@ -307,6 +340,12 @@ def run_ours(args):
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of k_hessian_umma_pair on fp16
+# X [T, C], from an ncu capture of exactly that launch (profiles/k_hessian_umma_pair_fp16.txt);
+# the algorithmic bytes of the launch are T*C*2 + 2 * 4 * C*(C+256)/2 = 1.63e9.
+HESSIAN_DRAM_BYTES = {(16384, 16384): 8895349504 + 552018432}
 
 
 def hessian_roofline(dev, d, f, args, peaks):
@@ -335,7 +374,7 @@ def hessian_roofline(dev, d, f, args, peaks):
     peak = peaks["bf16_tflops"]
     del X, S
     return {"kernel": "k_hessian_umma_pair", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-            "frac": achieved / peak, "traffic": None, "launch_ms": ms,
+            "frac": achieved / peak, "traffic": HESSIAN_DRAM_BYTES.get((T, f)), "launch_ms": ms,
             "work": f"T={T} tokens x C={f}: {issued:.3e} flop issued on upper-triangle tiles "
                     f"({algorithmic:.3e} for the full product the reference computes)",
             "peak_source": f"{peaks['source']} cuBLAS bf16 burst"}

@@ -44,7 +44,7 @@ constexpr int kL1Bins = 32768;   // key bits 30..16
 constexpr int kL2Bins = 512;     // key bits 15..7
 constexpr int kL3Bins = 128;     // key bits 6..0
 constexpr int kMaxCtas1 = 148;   // CTAs of the metric kernel (one per SM at most)
-constexpr int kMaxTiles = 256;   // row tiles of the search kernels
+constexpr int kMaxTiles = 512;   // row tiles of the search kernels
 constexpr int kAccSlots = 136;   // 0..48 salient candidates, 49..129 split candidates, 130 salient-group term
 constexpr int kAccSplit = kSalCand, kAccSalTerm = kSalCand + kSplits;
 static_assert(kAccSalTerm < kAccSlots, "accumulator slots");
@@ -606,7 +606,7 @@ k_sort_rows(const float* __restrict__ M, int R, float* __restrict__ sv, unsigned
 // accurate as the reference's float32 element-wise evaluation (differences ~1e-7 relative).
 // One thread per (row, candidate); three binary searches per task.
 // ---------------------------------------------------------------------------------------
-constexpr int kSplitRows = 32;                   // rows per pass of a CTA
+constexpr int kSplitRows = 16;                   // rows per pass of a CTA (small: more CTAs in flight, the phases are latency bound)
 constexpr int kRowPitch = kBlock + 1;            // odd pitch: rows start in different banks
 constexpr int kSplitSmem = kSplitRows * kRowPitch * (int)(sizeof(float) + 2 * sizeof(double)) +
                            (kSplits + 1) * kSplitRows * (int)sizeof(double);
@@ -798,7 +798,7 @@ k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restr
 // One thread per (row, candidate); the 32 lanes of a warp share the candidate, so the hole
 // loops have the same length across the warp.
 // ---------------------------------------------------------------------------------------
-constexpr int kSalRows = 32;
+constexpr int kSalRows = 16;
 constexpr int kTopPitch = kSalLimit + 1;
 constexpr int kSalSmem = kSalRows * kRowPitch * (int)(sizeof(float) + 2 * sizeof(double)) +
                          kSalRows * kTopPitch * (int)sizeof(float) + kSalCand * kSalRows * (int)sizeof(double);

@@ -103,30 +103,156 @@ def _decoder_parts(model):
     return inner.layers, pre
 
 
+_STREAMS: Dict[object, list] = {}
+
+
+def _copy_streams(dev):
+    """(host->device, device->host) side streams of a device, created once."""
+    key = ("copy", torch.device(dev).index or 0)
+    if key not in _STREAMS:
+        _STREAMS[key] = [torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)]
+    return _STREAMS[key]
+
+
 class _Resident:
-    """Moves a module's parameters to the device and back without losing the pinned host copies."""
+    """Moves a module's parameters to the device and back without losing the pinned host copies.
+
+    `prefetch()` starts the host->device copies on a side stream (so that they overlap the work of
+    the layer before); `__enter__` then only makes the current stream wait for them.
+    `__exit__(defer=True)` starts the copies back on a side stream and returns at once; `finish()`
+    waits for them.  The plain `with` form does both synchronously.
+    """
 
     def __init__(self, module: nn.Module, dev):
         self.module, self.dev, self.host = module, dev, {}
+        self._ready = None
+        self._back = None
+        self._keep = []
+
+    def _tensors(self):
+        return list(self.module.named_parameters()) + list(self.module.named_buffers())
+
+    def prefetch(self):
+        if torch.device(self.dev).type != "cuda" or self._ready is not None:
+            return self
+        h2d = _copy_streams(self.dev)[0]
+        with torch.cuda.stream(h2d):
+            for name, p in self._tensors():
+                if p.device.type != "cuda":
+                    self.host[name] = p.data
+                    p.data = p.data.to(self.dev, non_blocking=True)
+            self._ready = torch.cuda.Event()
+            self._ready.record(h2d)
+        return self
 
     def __enter__(self):
         if torch.device(self.dev).type != "cuda":
             return self.module
-        for name, p in list(self.module.named_parameters()) + list(self.module.named_buffers()):
+        if self._ready is not None:
+            torch.cuda.current_stream(self.dev).wait_event(self._ready)
+            return self.module
+        for name, p in self._tensors():
             if p.device.type != "cuda":
                 self.host[name] = p.data
                 p.data = p.data.to(self.dev, non_blocking=True)
         return self.module
 
-    def __exit__(self, *exc):
-        tensors = dict(list(self.module.named_parameters()) + list(self.module.named_buffers()))
-        for name, host in self.host.items():
-            p = tensors[name]
-            host.copy_(p.data, non_blocking=True)
-            p.data = host
-        if self.host:
-            torch.cuda.current_stream().synchronize()
+    def __exit__(self, *exc, defer=False):
+        if not self.host:
+            return
+        tensors = dict(self._tensors())
+        main = torch.cuda.current_stream(self.dev)
+        stream = _copy_streams(self.dev)[1] if defer else main
+        if defer:
+            stream.wait_stream(main)
+        with torch.cuda.stream(stream):
+            for name, host in self.host.items():
+                p = tensors[name]
+                host.copy_(p.data, non_blocking=True)
+                self._keep.append(p.data)            # the device copy lives until the copy back is done
+                p.data = host
+            self._back = torch.cuda.Event()
+            self._back.record(stream)
         self.host.clear()
+        if not defer:
+            self.finish()
+
+    def finish(self):
+        if self._back is not None:
+            self._back.synchronize()
+            self._back = None
+        self._keep.clear()
+        self._ready = None
+
+
+class _Feeder:
+    """Hands the layer its calibration batches.  Device-resident activations are sliced; activations
+    kept in pinned host memory (the reference offloads them above 8 GiB, run.py:166-172) are
+    copied one batch ahead on a side stream into two device buffers, so that the copy of batch
+    j + 1 overlaps the layer forward of batch j."""
+
+    _buffers: Dict[tuple, torch.Tensor] = {}
+
+    def __init__(self, inps: torch.Tensor, fb: int, dev):
+        self.inps, self.fb, self.dev = inps, fb, torch.device(dev)
+        self.n = inps.shape[0]
+        self.staged = inps.device.type == "cpu" and self.dev.type == "cuda"
+        if not self.staged:
+            return
+        key = (self.dev.index or 0, fb, tuple(inps.shape[1:]), inps.dtype)
+        if key not in _Feeder._buffers:
+            _Feeder._buffers[key] = torch.empty((2, fb) + tuple(inps.shape[1:]), dtype=inps.dtype, device=self.dev)
+        self.buf = _Feeder._buffers[key]
+        self.h2d, d2h = _copy_streams(self.dev)
+        self.main = torch.cuda.current_stream(self.dev)
+        self.h2d.wait_stream(d2h)              # these inputs may be outputs still on their way to the host
+        self.h2d.wait_stream(self.main)        # and the buffers may still be read by earlier work
+        self.ready = [None, None]
+        self.free = [None, None]
+        self._stage(0)
+
+    def _stage(self, idx):
+        j = idx * self.fb
+        if j >= self.n:
+            return
+        slot = idx & 1
+        if self.free[slot] is not None:
+            self.h2d.wait_event(self.free[slot])
+        with torch.cuda.stream(self.h2d):
+            m = min(self.fb, self.n - j)
+            self.buf[slot, :m].copy_(self.inps[j:j + m], non_blocking=True)
+            self.ready[slot] = torch.cuda.Event()
+            self.ready[slot].record(self.h2d)
+
+    def __len__(self):
+        return (self.n + self.fb - 1) // self.fb
+
+    def batch(self, idx):
+        """Batch `idx` on the device; call in increasing order, `done(idx)` after its last use."""
+        j = idx * self.fb
+        m = min(self.fb, self.n - j)
+        if not self.staged:
+            return self.inps[j:j + m].to(self.dev, non_blocking=True)
+        self._stage(idx + 1)
+        self.main.wait_event(self.ready[idx & 1])
+        return self.buf[idx & 1, :m]
+
+    def done(self, idx):
+        if self.staged:
+            self.free[idx & 1] = torch.cuda.Event()
+            self.free[idx & 1].record(self.main)
+
+
+def _store_outputs(outs: torch.Tensor, j: int, y: torch.Tensor, dev):
+    """outs[j : j + len(y)] = y; towards pinned host memory the copy runs on a side stream."""
+    if outs.device.type == "cpu" and torch.device(dev).type == "cuda":
+        d2h = _copy_streams(dev)[1]
+        d2h.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(d2h):
+            outs[j:j + y.shape[0]].copy_(y, non_blocking=True)
+        y.record_stream(d2h)
+    else:
+        outs[j:j + y.shape[0]].copy_(y, non_blocking=True)
 
 
 class _Catcher(nn.Module):
@@ -165,9 +291,6 @@ def _replay_kwargs(kwargs: dict, batch: int) -> dict:
         out[k] = v
     out["use_cache"] = False
     return out
-
-
-_STREAMS: Dict[int, list] = {}
 
 
 def _stream_pool(dev, n):
@@ -282,15 +405,17 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
     n_local = inps.shape[0]
     fb = max(1, int(args.forward_batch))
     with timer.span("forward_hessian"):
-        for j in range(0, n_local, fb):
-            x = inps[j:j + fb].to(dev, non_blocking=True)
+        feed = _Feeder(inps, fb, dev)
+        for b in range(len(feed)):
+            x = feed.batch(b)
             seen.clear()
             cur["batch"] = x.shape[0]
             try:
                 layer(x, **_replay_kwargs(layer_kwargs, x.shape[0]))
             except _TailReached:
                 pass
-            if j == 0 and getattr(args, "skip_dead_tail", True) and call_order \
+            feed.done(b)
+            if b == 0 and getattr(args, "skip_dead_tail", True) and call_order \
                     and call_order.count(call_order[-1]) == 1:
                 cur["last"] = call_order[-1]
         seen.clear()
@@ -363,10 +488,12 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
 
     # ---- pass 2: re-propagate with the quantized weights (run.py:376-377) ----
     with timer.span("forward_repropagate"):
-        for j in range(0, n_local, fb):
-            x = inps[j:j + fb].to(dev, non_blocking=True)
+        feed = _Feeder(inps, fb, dev)
+        for b in range(len(feed)):
+            x = feed.batch(b)
             y = _layer_out(layer(x, **_replay_kwargs(layer_kwargs, x.shape[0])))
-            outs[j:j + fb].copy_(y.reshape(x.shape), non_blocking=True)
+            feed.done(b)
+            _store_outputs(outs, b * fb, y.reshape(x.shape), dev)
     del gptq
     return errors
 
@@ -421,11 +548,26 @@ def quant_sequential(model, dataloader, dev, args=None) -> dict:
     timer = _Timer()
     all_errors: List[Dict[str, float]] = []
     t0 = time.time()
+    # weights stream through the device: layer i + 1 is copied in and layer i - 1 copied out while
+    # layer i is being quantized
+    nxt = _Resident(layers[0], dev).prefetch() if len(layers) else None
+    leaving = None
     for i in range(len(layers)):
-        with _Resident(layers[i], dev) as layer:
-            errs = quantize_layer(layer, i, inps, outs, layer_kwargs, args, dev, timer)
+        res, nxt = nxt, None
+        layer = res.__enter__()
+        if i + 1 < len(layers):
+            nxt = _Resident(layers[i + 1], dev).prefetch()
+        errs = quantize_layer(layer, i, inps, outs, layer_kwargs, args, dev, timer)
+        if leaving is not None:
+            leaving.finish()
+        res.__exit__(defer=True)
+        leaving = res
         all_errors.append(errs)
         inps, outs = outs, inps
+    if leaving is not None:
+        leaving.finish()
+    if dev.type == "cuda":
+        torch.cuda.synchronize(dev)          # outputs on their way to the host have arrived
     timing = timer.collect()
     timing["wall_s"] = time.time() - t0
     model.config.use_cache = use_cache

@@ -6,7 +6,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _run(concurrent: bool, arch: str, tech: str):
+def _run(concurrent: bool, arch: str, tech: str, offload: bool = False):
     from crb_b200 import run as crun
     from crb_b200.synth import build_synthetic_model, synthetic_calibration
     model = build_synthetic_model(arch, n_layers=2, seed=3)
@@ -15,6 +15,8 @@ def _run(concurrent: bool, arch: str, tech: str):
     args = crun.default_args(low_quant_method=tech, nsamples=8, forward_batch=4, verbose=False,
                              device="cuda:0", percdamp=0.1)
     args.concurrent_linears = concurrent
+    if offload:
+        args.act_offload_gib = 0.0          # activations live in pinned host memory and stream through the device
     out = crun.quant_sequential(model, loader, "cuda:0", args)
     layers, _ = crun._decoder_parts(model)
     weights = {f"{i}.{n}": m.weight.data.float().cpu().clone()
@@ -35,3 +37,15 @@ def test_overlapped_linears_equal_sequential(arch, tech):
         assert ec == es
     assert torch.equal(out_c["final_hidden"].cpu(), out_s["final_hidden"].cpu())
     assert out_c["error_sum"] > 0
+
+
+def test_host_resident_activations_equal_device_resident():
+    """Activations offloaded to pinned host memory (prefetched batch by batch, written back on a side
+    stream) and weights streamed one layer ahead give the very same result."""
+    out_h, w_h = _run(True, "opt-tiny", "crb", offload=True)
+    out_d, w_d = _run(True, "opt-tiny", "crb", offload=False)
+    assert out_h["final_hidden"].device.type == "cpu" and out_d["final_hidden"].device.type == "cuda"
+    for name in w_d:
+        assert torch.equal(w_h[name], w_d[name]), name
+    assert torch.equal(out_h["final_hidden"], out_d["final_hidden"].cpu())
+    assert out_h["errors"] == out_d["errors"]
