@@ -60,11 +60,12 @@ def lib():
     """The loaded library (loads it on first use)."""
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
+        path = os.environ.get("CRB_B200_LIBRARY", LIB_PATH)      # another build of the same library
+        if not os.path.exists(path):
             raise CrbError(
-                f"{LIB_PATH} is missing: build it with `python -m crb_b200.build` "
+                f"{path} is missing: build it with `python -m crb_b200.build` "
                 "(there is no CPU or PyTorch fallback for the CUDA path)")
-        handle = C.CDLL(LIB_PATH)
+        handle = C.CDLL(path)
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(handle, name)       # AttributeError if the export is missing
             fn.restype, fn.argtypes = res, args

@@ -120,6 +120,19 @@ int crb_gemm_f32(int b_is_nk, int shape, int M, int N, int K, float alpha, const
 // of bigptq.py:264, associated differently; the trailing part of W is read and written once per
 // group instead of once per block.
 constexpr int kGroup = 8;
+
+// CRB_LINEAR_GROUP (1..8) overrides the group size for experiments; 1 is the per-block update.
+static int group_blocks() {
+    static int v = 0;
+    if (!v) {
+        v = kGroup;
+        if (const char* e = getenv("CRB_LINEAR_GROUP")) {
+            const int x = atoi(e);
+            if (x >= 1 && x <= kGroup) v = x;
+        }
+    }
+    return v;
+}
 static_assert(CRB_GEMM_LOWER_ONLY == GEMM_LOWER_ONLY && CRB_GEMM_B_LOWER == GEMM_B_LOWER &&
               CRB_GEMM_A_LOWER == GEMM_A_LOWER, "shape flags of the header and of the kernel");
 
@@ -141,9 +154,9 @@ int crb_quantize_linear(float* W, int R, int C, int64_t ldw, const float* U, int
     const int64_t ld_err = (int64_t)kGroup * kBlock;
     unsigned* status = static_cast<unsigned*>(workspace);
     if (cudaMemsetAsync(workspace, 0, 64, st) != cudaSuccess) return CRB_ERR_LAUNCH;   // status word
-    const int nblk = C / kBlock;
+    const int nblk = C / kBlock, grp = group_blocks();
     for (int b = 0; b < nblk; ++b) {
-        const int g0 = b / kGroup * kGroup, g1 = g0 + kGroup < nblk ? g0 + kGroup : nblk;
+        const int g0 = b / grp * grp, g1 = g0 + grp < nblk ? g0 + grp : nblk;
         float* Err = ErrG + (size_t)(b - g0) * kBlock;
         int rc = block_step_launch(W, R, ldw, U, ldu, b, technique, lam, corr_damp, metric, Err, ld_err, Losses, codes,
                                    C, scales ? scales + (size_t)b * R * 8 : nullptr,

@@ -21,7 +21,20 @@
 namespace crb {
 
 constexpr int FB = 128;    // panel width
-constexpr int kOuter = 8;  // diagonal blocks per outer panel of the factorisation
+constexpr int kOuterDefault = 8;  // diagonal blocks per outer panel of the factorisation
+
+// CRB_FACTOR_OUTER overrides the outer panel width (in 128-column blocks) for experiments.
+static int outer_blocks() {
+    static int v = 0;
+    if (!v) {
+        v = kOuterDefault;
+        if (const char* e = getenv("CRB_FACTOR_OUTER")) {
+            const int x = atoi(e);
+            if (x >= 1 && x <= 64) v = x;
+        }
+    }
+    return v;
+}
 
 // diag statistics: dead columns, mean of the diagonal after the dead fix, total damping.
 __global__ void __launch_bounds__(1024)
@@ -335,8 +348,9 @@ int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
     }
     // Two levels of blocking: inside an outer panel of kOuter diagonal blocks the rank-128 updates
     // touch the panel's own columns only; everything right of the panel gets one update with
-    // K = kOuter * 128 afterwards, which is compute bound instead of re-reading the whole trailing
+    // K = 8 * 128 afterwards, which is compute bound instead of re-reading the whole trailing
     // matrix once per diagonal block.
+    const int kOuter = outer_blocks();
     for (int k0 = 0; k0 < nb; k0 += kOuter) {
         const int k1 = k0 + kOuter < nb ? k0 + kOuter : nb;
         for (int k = k0; k < k1; ++k) {

@@ -9,10 +9,20 @@
 // Used by the trailing update W[:, i2:] -= Err @ U[i1:i2, i2:] (bigptq.py:264) and by the
 // panel / rank-128 / inverse-merge products of the blocked factorisation.
 //
-// One persistent CTA per SM over 128 x 256 output tiles.  Warp roles: warp 0 TMA producer
-// (float32 tiles, 128-byte swizzle), warp 1 MMA issuer (owns TMEM), warps 2-5 split the
-// landed tiles into hi / lo in place, warps 6-13 epilogue (TMEM -> registers -> C).  Two
-// shared-memory stages of K = 32, two 256-column TMEM accumulators.  A is [M, K] row-major
+// One persistent CTA per SM over 128 x 256 output tiles, four warpgroups: warp 0 TMA producer
+// (float32 tiles, 128-byte swizzle), warp 1 MMA issuer (owns TMEM), warps 4-7 split the
+// landed tiles into hi / lo in place, warps 8-15 epilogue.  Two shared-memory stages of K = 32,
+// two 256-column TMEM accumulators.
+//
+// The tensor core truncates (rounds toward zero) every time it adds to its float32 accumulator,
+// a bias that grows with the length of the chain (measured on a 4096 x 4096 factorisation with
+// condition number 6e4: chains of K = 1024 gave a factor 7 x less accurate than the float32
+// library chain, K = 128 chains 5 x its error on the diagonal, K = 32 chains parity).  The MMAs
+// therefore accumulate one shared-memory stage (K = 32, 12 instructions) in TMEM; the epilogue
+// warps fold every such chunk into float32 REGISTER accumulators with round-to-nearest adds while
+// the next chunk runs in the other TMEM buffer, and write C once per tile.  The epilogue warpgroups hold 128 accumulator registers per
+// thread; setmaxnreg moves registers to them from the producer / splitter warpgroups.
+// A is [M, K] row-major
 // (K-major operand); B is [N, K] row-major (K-major) or [K, N] row-major (MN-major operand).
 // All mbarrier waits are bounded (2 s); on expiry CRB_FLAG_WAIT_LIMIT is raised and the kernel
 // drains and returns.
@@ -29,7 +39,14 @@ constexpr int GT_RAW_BYTES = GT_A_BYTES + GT_B_BYTES;       // 48 KiB: hi planes
 constexpr int GT_STAGE_BYTES = 2 * GT_RAW_BYTES;            // + lo planes
 constexpr int GT_EPI_BYTES = 8 * 32 * 33 * 4;                 // per-warp transpose patches of the epilogue
 constexpr int GT_SMEM = GT_STAGES * GT_STAGE_BYTES + 256 + GT_EPI_BYTES + 1024;
-constexpr int GT_THREADS = 448;              // TMA, MMA, 4 splitter warps, 8 epilogue warps
+constexpr int GT_THREADS = 512;              // warpgroups: TMA + MMA (+ 2 idle warps), 4 splitter warps, 2 x 4 epilogue warps
+#ifndef CRB_GEMM_CHUNK_STEPS
+#define CRB_GEMM_CHUNK_STEPS 1
+#endif
+constexpr int GT_CHUNK_STEPS = CRB_GEMM_CHUNK_STEPS;   // K steps (of 32) accumulated in TMEM before the fold into registers
+// registers per thread after the reallocation; the sum over the four warpgroups is 512 = 4 x 128
+constexpr int GT_REGS_IO = 56, GT_REGS_SPLIT = 72, GT_REGS_EPI = 192;
+static_assert(GT_REGS_IO + GT_REGS_SPLIT + 2 * GT_REGS_EPI <= 4 * 128, "register budget of a CTA");
 
 struct GemmArgs {
     float* C;
@@ -136,7 +153,9 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int total = g.m_tiles * g.n_tiles;
-
+    // Each warpgroup first hands over / takes registers (uniform per warpgroup), then runs its role.
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(GT_REGS_IO));
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
@@ -191,53 +210,57 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
                 const int mi = t / g.n_tiles, nj = t % g.n_tiles;
                 if (tile_skipped(g, mi, nj)) continue;
-                const uint32_t buf = unit & 1, use = unit >> 1;
-                ++unit;
-#ifdef CRB_GEMM_PROFILE
-                const unsigned long long pa_ = global_ns();
-#endif
-                ok = mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, abort_flag);
-#ifdef CRB_GEMM_PROFILE
-                prof_te += global_ns() - pa_;
-#endif
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * GT_N;
-                bool first = true;
                 int ks0, ks1;
                 tile_k_range(g, mi, nj, &ks0, &ks1);
-                for (int ks = ks0; ks < ks1; ++ks) {
-                    ok = PROF_WAIT(mbar_wait(ready0 + 8 * stage, phase, abort_flag));
+                for (int kc = ks0; kc < ks1 && ok; kc += GT_CHUNK_STEPS, ++unit) {
+                    const uint32_t buf = unit & 1, use = unit >> 1;
+#ifdef CRB_GEMM_PROFILE
+                    const unsigned long long pa_ = global_ns();
+#endif
+                    ok = mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, abort_flag);
+#ifdef CRB_GEMM_PROFILE
+                    prof_te += global_ns() - pa_;
+#endif
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a_hi = smem_u32(smem + stage * GT_STAGE_BYTES), b_hi = a_hi + GT_A_BYTES;
-                    const uint32_t a_lo = a_hi + GT_RAW_BYTES, b_lo = b_hi + GT_RAW_BYTES;
+                    const uint32_t d_tmem = tmem_base + buf * GT_N;
+                    const int kc1 = min(kc + GT_CHUNK_STEPS, ks1);
+                    bool first = true;
+                    for (int ks = kc; ks < kc1; ++ks) {
+                        ok = PROF_WAIT(mbar_wait(ready0 + 8 * stage, phase, abort_flag));
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t a_hi = smem_u32(smem + stage * GT_STAGE_BYTES), b_hi = a_hi + GT_A_BYTES;
+                        const uint32_t a_lo = a_hi + GT_RAW_BYTES, b_lo = b_hi + GT_RAW_BYTES;
 #pragma unroll
-                    for (int k = 0; k < GT_K / 8; ++k) {
-                        // one MMA consumes K = 8 float32: 32 bytes along a K-major row, or one
-                        // 8-row group (1024 bytes) of an MN-major box
-                        const uint32_t ao = k * 32, bo = g.b_is_nk ? k * 32 : k * 1024;
-                        const uint64_t dah = kmajor_sw128_desc(a_hi + ao), dal = kmajor_sw128_desc(a_lo + ao);
-                        const uint64_t dbh = g.b_is_nk ? kmajor_sw128_desc(b_hi + bo) : mnmajor_sw128_desc(b_hi + bo, 4096);
-                        const uint64_t dbl = g.b_is_nk ? kmajor_sw128_desc(b_lo + bo) : mnmajor_sw128_desc(b_lo + bo, 4096);
-                        umma_tf32(d_tmem, dal, dbh, idesc, !first);      // small terms first
-                        umma_tf32(d_tmem, dah, dbl, idesc, true);
-                        umma_tf32(d_tmem, dah, dbh, idesc, true);
-                        first = false;
+                        for (int k = 0; k < GT_K / 8; ++k) {
+                            // one MMA consumes K = 8 float32: 32 bytes along a K-major row, or one
+                            // 8-row group (1024 bytes) of an MN-major box
+                            const uint32_t ao = k * 32, bo = g.b_is_nk ? k * 32 : k * 1024;
+                            const uint64_t dah = kmajor_sw128_desc(a_hi + ao), dal = kmajor_sw128_desc(a_lo + ao);
+                            const uint64_t dbh = g.b_is_nk ? kmajor_sw128_desc(b_hi + bo) : mnmajor_sw128_desc(b_hi + bo, 4096);
+                            const uint64_t dbl = g.b_is_nk ? kmajor_sw128_desc(b_lo + bo) : mnmajor_sw128_desc(b_lo + bo, 4096);
+                            umma_tf32(d_tmem, dal, dbh, idesc, !first);      // small terms first
+                            umma_tf32(d_tmem, dah, dbl, idesc, true);
+                            umma_tf32(d_tmem, dah, dbh, idesc, true);
+                            first = false;
+                        }
+                        umma_commit(empty0 + 8 * stage);
+                        if (++stage == GT_STAGES) { stage = 0; phase ^= 1; }
                     }
-                    umma_commit(empty0 + 8 * stage);
-                    if (++stage == GT_STAGES) { stage = 0; phase ^= 1; }
+                    if (ok) umma_commit(tfull0 + 8 * buf);
                 }
-                if (ok) umma_commit(tfull0 + 8 * buf);
             }
             PROF_END(2, 7);
 #ifdef CRB_GEMM_PROFILE
             atomicAdd(&g_gemm_prof[3], prof_te);
 #endif
         }
-    } else if (warp < 6) {
+    }   // warps 2 and 3 only fill the first warpgroup
+    } else if (warp < 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(GT_REGS_SPLIT));
         // ---------------- splitter: hi = x with 13 low mantissa bits cleared, lo = x - hi ----------------
-        const int ctid = threadIdx.x - 64;                  // 0..127
+        const int ctid = threadIdx.x - 128;                 // 0..127
         uint32_t stage = 0, phase = 0;
         bool ok = true;
         PROF_DECL
@@ -270,64 +293,69 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 if (++stage == GT_STAGES) { stage = 0; phase ^= 1; }
             }
         }
-        if (threadIdx.x == 64) { PROF_END(1, 6); }
+        if (threadIdx.x == 128) { PROF_END(1, 6); }
     } else {
-        // ---------------- epilogue: warps 6..13; warp w reads TMEM lanes 32 * (w % 4) .. +31 and the
-        // column half (w - 6) / 4 of the accumulator ----------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(GT_REGS_EPI));
+        // ---------------- epilogue: warps 8..15; warp w reads TMEM lanes 32 * (w % 4) .. +31 and the
+        // column half (w - 8) / 4 of the accumulator ----------------
         const int q = warp & 3;
-        const int c_begin = ((warp - 6) >> 2) * (GT_N / 2);
+        const int c_begin = ((warp - 8) >> 2) * (GT_N / 2);
         uint32_t unit = 0;
         bool ok = true;
         PROF_DECL
         for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
             const int mi = t / g.n_tiles, nj = t % g.n_tiles;
             if (tile_skipped(g, mi, nj)) continue;
-            const uint32_t buf = unit & 1, use = unit >> 1;
-            ++unit;
-            // A TMEM load hands every lane one accumulator row (32 columns): written to memory like
-            // that, each instruction would touch 32 different cache lines.  The 32 x 32 chunk is
-            // transposed through a per-warp shared-memory patch instead, so that a warp instruction
-            // covers 4 rows x 128 contiguous bytes.  Lane l then owns rows (l / 8) + 4k, k = 0..7,
-            // and columns 4 (l % 8) .. +3 of the chunk.
+            int ks0, ks1;
+            tile_k_range(g, mi, nj, &ks0, &ks1);
+            // ---- fold the chunks of this tile into registers (thread = one accumulator row) ----
+            float acc[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[c][j] = 0.f;
+            for (int kc = ks0; kc < ks1 && ok; kc += GT_CHUNK_STEPS, ++unit) {
+                const uint32_t buf = unit & 1, use = unit >> 1;
+                ok = PROF_WAIT(mbar_wait(tfull0 + 8 * buf, use & 1, abort_flag));
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * GT_N + c_begin;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float v[32];
+                    tmem_ld32(taddr + 32 * c, v);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[c][j] += v[j];
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty0 + 8 * buf);     // the MMAs may reuse this buffer
+            }
+            if (!ok) break;
+            // ---- write the tile.  Every lane holds one row (32 columns per chunk): written like that,
+            // each instruction would touch 32 different cache lines.  The 32 x 32 chunk is transposed
+            // through a per-warp shared-memory patch instead, so that a warp instruction covers
+            // 4 rows x 128 contiguous bytes.  Lane l then owns rows (l / 8) + 4k, k = 0..7, and
+            // columns 4 (l % 8) .. +3 of the chunk. ----
             const int r_sub = lane >> 3, cg = lane & 7;
             const int row0 = mi * GT_M + q * 32 + r_sub;                 // + 4k
             const int colbase = nj * GT_N + c_begin + 4 * cg;            // + 32c
-            // The old values of C do not depend on the MMAs: their loads are issued two chunks
-            // ahead (the first two before the accumulator is even ready) to keep memory busy.
-            float4 o[2][8];
             auto live = [&](int c, int k) {
                 const int row = row0 + 4 * k, col = colbase + 32 * c;
                 // lower_only: nothing is written above the 128 x 128 block that holds the diagonal,
                 // so that a triangular matrix updated this way keeps exact zeros there
                 return row < g.M && col < g.N && !(g.lower_only && col > (row | 127));
             };
-            // beta == 1 (the rank-128 updates): C += alpha * acc goes out as vector reductions that
+            // beta == 1 (the rank-k updates): C += alpha * acc goes out as vector reductions that
             // the L2 performs, so the SM never waits for the old values of C
             const bool use_red = (g.beta == 1.0f);
-            auto fetch = [&](int c, float4 (&dst)[8]) {
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    dst[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (g.beta != 0.f && !use_red && live(c, k))
-                        dst[k] = *reinterpret_cast<const float4*>(g.C + (int64_t)(row0 + 4 * k) * g.ldc + colbase + 32 * c);
-                }
-            };
-            fetch(0, o[0]);
-            fetch(1, o[1]);
-            ok = PROF_WAIT(mbar_wait(tfull0 + 8 * buf, use & 1, abort_flag));
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * GT_N + c_begin;
-            float* patch = reinterpret_cast<float*>(smem + GT_STAGES * GT_STAGE_BYTES + 256) + (warp - 6) * (32 * 33);
+            float* patch = reinterpret_cast<float*>(smem + GT_STAGES * GT_STAGE_BYTES + 256) + (warp - 8) * (32 * 33);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                float v[32];
-                tmem_ld32(taddr + 32 * c, v);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) patch[lane * 33 + j] = v[j];
+                for (int j = 0; j < 32; ++j) patch[lane * 33 + j] = acc[c][j];
                 __syncwarp();
-                float4 (&oc)[8] = o[c & 1];
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     const float* src = patch + (r_sub + 4 * k) * 33 + 4 * cg;
@@ -338,23 +366,20 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                                          ::"l"(dst), "f"(g.alpha * src[0]), "f"(g.alpha * src[1]),
                                            "f"(g.alpha * src[2]), "f"(g.alpha * src[3]) : "memory");
                         } else {
-                            float4 w;
-                            w.x = fmaf(g.alpha, src[0], g.beta * oc[k].x);
-                            w.y = fmaf(g.alpha, src[1], g.beta * oc[k].y);
-                            w.z = fmaf(g.alpha, src[2], g.beta * oc[k].z);
-                            w.w = fmaf(g.alpha, src[3], g.beta * oc[k].w);
+                            float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (g.beta != 0.f) w = *reinterpret_cast<const float4*>(dst);
+                            w.x = fmaf(g.alpha, src[0], g.beta * w.x);
+                            w.y = fmaf(g.alpha, src[1], g.beta * w.y);
+                            w.z = fmaf(g.alpha, src[2], g.beta * w.z);
+                            w.w = fmaf(g.alpha, src[3], g.beta * w.w);
                             *reinterpret_cast<float4*>(dst) = w;
                         }
                     }
                 }
                 __syncwarp();
-                if (c + 2 < 4) fetch(c + 2, oc);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
         }
-        if (warp == 6 && lane == 0) { PROF_END(4, 5); }
+        if (warp == 8 && lane == 0) { PROF_END(4, 5); }
     }
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag && g.status) atomicOr(g.status, CRB_FLAG_WAIT_LIMIT);
@@ -411,6 +436,12 @@ int gemm_tf32x3(bool b_is_nk, int shape, int M, int N, int K, float alpha, const
     if (!attr_set) {
         if (cudaFuncSetAttribute(k_gemm_tf32x3, cudaFuncAttributeMaxDynamicSharedMemorySize, GT_SMEM) != cudaSuccess)
             return CRB_ERR_LAUNCH;
+        // The register reallocation inside the kernel can only hand out what the CTA was launched
+        // with: refuse to launch a build whose register file share is smaller than the plan needs
+        // (an epilogue warpgroup would wait for registers that never become free).
+        cudaFuncAttributes fa;
+        if (cudaFuncGetAttributes(&fa, k_gemm_tf32x3) != cudaSuccess) return CRB_ERR_LAUNCH;
+        if (fa.numRegs * GT_THREADS < (GT_REGS_IO + GT_REGS_SPLIT + 2 * GT_REGS_EPI) * 128) return CRB_ERR_UNSUPPORTED;
         attr_set = true;
     }
     static int sms = 0;

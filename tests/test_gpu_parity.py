@@ -236,6 +236,42 @@ def test_factor_matches_reference_chain(ops, C):
     assert torch.allclose(d_dev, torch.diag(U_true), rtol=1e-4)
 
 
+def test_factor_accuracy_on_ill_conditioned_hessian(ops):
+    """Two outer panels of the blocked factorisation (C = 2048), a Hessian with a decaying spectrum
+    (condition number ~4e4 after damping): the factor must be about as close to the float64 truth as
+    the reference's float32 library chain is on a GPU, in norm and on the diagonal the block step
+    divides by."""
+    C = 2048
+    g = torch.Generator().manual_seed(77)
+    Z = torch.randn(3 * C, C, generator=g, dtype=torch.float64)
+    Qm, _ = torch.linalg.qr(torch.randn(C, C, generator=g, dtype=torch.float64))
+    X = (Z * torch.logspace(0, -2.5, C, dtype=torch.float64)) @ Qm.t()
+    X[:, :4] *= 30
+    H = ((X.t() @ X) * (2.0 / 64)).float()
+    W = torch.randn(32, C, generator=g)
+    U_cpu = O.hinv_upper_factor(H.clone(), W.clone(), 0.01)           # the oracle's float32 chain (LAPACK)
+    # the same three library calls as the reference issues them on a GPU (bigptq.py:127-129)
+    tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    Hg = H.to(DEV).clone()
+    Hg += torch.eye(C, device=DEV) * (0.01 * torch.mean(torch.diag(Hg)))
+    U_gpu = torch.linalg.cholesky(torch.cholesky_inverse(torch.linalg.cholesky(Hg)), upper=True).cpu()
+    torch.backends.cuda.matmul.allow_tf32 = tf32
+    Hd = H.double() + 0.01 * torch.diag(H.double()).mean() * torch.eye(C, dtype=torch.float64)
+    U_true = torch.linalg.cholesky(torch.linalg.inv(Hd), upper=True)
+    U = ops.hinv_upper_factor(H.to(DEV).clone(), W.to(DEV).clone(), 0.01).cpu()
+    dt = torch.diag(U_true)
+
+    def errors(V):
+        return (float((V.double() - U_true).norm() / U_true.norm()),
+                float(((torch.diag(V).double() - dt).abs() / dt).mean()))
+
+    (e_dev, d_dev), (e_cpu, d_cpu), (e_gpu, d_gpu) = errors(U), errors(U_cpu), errors(U_gpu)
+    assert e_dev <= max(1.5 * e_gpu, 4 * e_cpu), (e_dev, e_gpu, e_cpu)
+    # the diagonal keeps a small systematic part (12 truncating tensor-core adds per K = 32 chunk)
+    assert d_dev <= max(4.0 * d_gpu, 1e-5), (d_dev, d_gpu, d_cpu)
+
+
 def test_factor_retry_and_fallback(ops):
     """A Hessian that is not positive definite takes the retry path and still returns a factor."""
     C = 256
