@@ -294,10 +294,15 @@ def _replay_kwargs(kwargs: dict, batch: int) -> dict:
 
 
 def _stream_pool(dev, n):
-    """Side streams per device, created once: scratch buffers are cached per stream."""
+    """Side streams per device, created once: scratch buffers are cached per stream.
+
+    Slot 0 serves the most expensive linear of a layer, whose serial chain of small kernels decides
+    when the layer is done: it gets the high priority, so that its kernels are placed first whenever
+    an SM frees up among the wide kernels of the other linears."""
     pool = _STREAMS.setdefault(torch.device(dev).index or 0, [])
     while len(pool) < n:
-        pool.append(torch.cuda.Stream(device=dev))
+        prio = -1 if (len(pool) == 0 and os.environ.get("CRB_STREAM_PRIORITY", "1") != "0") else 0
+        pool.append(torch.cuda.Stream(device=dev, priority=prio))
     return pool
 
 
