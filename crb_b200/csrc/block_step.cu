@@ -23,6 +23,27 @@
 
 namespace crb {
 
+#ifdef CRB_BLOCK_PROFILE
+// Development builds only: first start / last end of the parallel part / end of the last-CTA tail
+// of each kernel of the block step (globaltimer, ns).
+__device__ unsigned long long g_bprof[8][4];
+__device__ __forceinline__ unsigned long long bprof_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define BPROF_START(id) do { if (threadIdx.x == 0) atomicMin(&g_bprof[id][0], bprof_ns()); } while (0)
+#define BPROF_PASS(id) do { if (threadIdx.x == 0) atomicMax(&g_bprof[id][1], bprof_ns()); } while (0)
+#define BPROF_END(id) do { if (threadIdx.x == 0) atomicMax(&g_bprof[id][2], bprof_ns()); } while (0)
+__device__ unsigned long long g_bmark[64];
+#define BPROF_MARK(slot) do { if (threadIdx.x == 0) g_bmark[slot] = bprof_ns(); } while (0)
+#else
+#define BPROF_MARK(slot)
+#define BPROF_START(id)
+#define BPROF_PASS(id)
+#define BPROF_END(id)
+#endif
+
 // float32 bit patterns of torch.linspace(0.10, 0.90, 81) (utils/autosearch.py:65).
 __constant__ unsigned c_split_probs[kSplits] = {
     0x3dcccccdu, 0x3de147aeu, 0x3df5c290u, 0x3e051eb8u, 0x3e0f5c29u, 0x3e19999au,
@@ -41,6 +62,8 @@ __constant__ unsigned c_split_probs[kSplits] = {
     0x3f6147aeu, 0x3f63d70au, 0x3f666666u};
 
 constexpr int kL1Bins = 32768;   // key bits 30..16
+constexpr int kL1Smem = (kL1Bins + kL1Bins / 32) * (int)sizeof(unsigned);   // padded, see k_select_l1
+__host__ __device__ constexpr int pad1(int b) { return b + (b >> 5); }
 constexpr int kL2Bins = 512;     // key bits 15..7
 constexpr int kL3Bins = 128;     // key bits 6..0
 constexpr int kMaxCtas1 = 148;   // CTAs of the metric kernel (one per SM at most)
@@ -133,6 +156,7 @@ k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
                   float* __restrict__ M, double* __restrict__ colpart, double* __restrict__ energy,
                   double* __restrict__ fx, unsigned* counters, unsigned char* __restrict__ rank_out,
                   double* __restrict__ trace, unsigned* status) {
+    BPROF_START(0);
     __shared__ float s_d2[kBlock];
     __shared__ double s_e[8];
     __shared__ double s_wcol[8][kBlock];
@@ -192,14 +216,22 @@ k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
         for (int w = 0; w < 8; ++w) v += s_e[w];
         energy[blockIdx.x] = v;
     }
+    BPROF_PASS(0);
     if (!last_cta_done(&counters[0], gridDim.x)) return;
 
-    if (tid < kBlock) {
+    {
+        // column scores: two threads per column, each over half of the CTAs' partial sums, many
+        // independent loads in flight (this tail runs on one SM and is bound by load latency)
+        const int col = tid & (kBlock - 1), half = tid >> 7;
+        const unsigned per = (gridDim.x + 1) / 2;
+        const unsigned c0 = half * per, c1 = min(gridDim.x, c0 + per);
         double v = 0.0;
-#pragma unroll 8
-        for (unsigned c = 0; c < gridDim.x; ++c) v += __ldcg(&colpart[(size_t)c * kBlock + tid]);
-        s_score[tid] = v;
+#pragma unroll 16
+        for (unsigned c = c0; c < c1; ++c) v += __ldcg(&colpart[(size_t)c * kBlock + col]);
+        s_wcol[half][col] = v;
     }
+    __syncthreads();
+    if (tid < kBlock) s_score[tid] = s_wcol[0][tid] + s_wcol[1][tid];
     if (warp == 4) {
         // Candidate error sums are accumulated as 64-bit fixed point so that their value does not
         // depend on the order in which CTAs add to them.  No candidate error exceeds sum(M^2):
@@ -225,6 +257,7 @@ k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
         rank_out[tid] = (unsigned char)r;
         if (r < kSalLimit) trace[6 + r] = (double)tid;
     }
+    BPROF_END(0);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -236,17 +269,28 @@ __device__ __forceinline__ void acc_add(unsigned long long* acc, double v, doubl
     if (q) atomicAdd(acc, q);
 }
 
-// First strict minimum (autosearch.py:53, :78) and the relative gap to the runner-up.
-__device__ void first_strict_min(const double* e, int n, int fallback, int* best_out, double* gap_out) {
-    int best = -1;
+// First strict minimum (autosearch.py:53, :78) and the relative gap to the runner-up, taken by
+// one full warp (candidates strided over the lanes); NaN never wins, `fallback` if nothing does.
+__device__ void warp_first_strict_min(const double* e, int n, int fallback, int* best_out, double* gap_out) {
+    const int lane = threadIdx.x & 31;
     double be = INFINITY;
-    for (int c = 0; c < n; ++c)
-        if (e[c] < be) { be = e[c]; best = c; }
+    int best = 0x7fffffff;
+    for (int c = lane; c < n; c += 32)
+        if (e[c] < be) { be = e[c]; best = c; }            // lowest index of the lane's minimum
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const double ov = __shfl_xor_sync(0xffffffffu, be, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best, o);
+        if (ov < be || (ov == be && oi < best)) { be = ov; best = oi; }
+    }
+    const bool none = !(be < INFINITY);
     double second = INFINITY;
-    for (int c = 0; c < n; ++c)
+    for (int c = lane; c < n; c += 32)
         if (c != best && e[c] < second) second = e[c];
-    *best_out = best < 0 ? fallback : best;
-    *gap_out = (best < 0 || !(be > 0.0)) ? 0.0 : (second - be) / be;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) second = fmin(second, __shfl_xor_sync(0xffffffffu, second, o));
+    *best_out = none ? fallback : best;
+    *gap_out = (none || !(be > 0.0)) ? 0.0 : (second - be) / be;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -284,13 +328,17 @@ __device__ __forceinline__ unsigned block_exclusive_scan_1024(unsigned v, unsign
 __global__ void __launch_bounds__(1024)
 k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
             const int* __restrict__ sel, BlockWs ws) {
-    extern __shared__ __align__(16) unsigned s_hist[];   // kL1Bins
+    BPROF_START(3);
+    // bin b lives at s_hist[pad1(b)]: one spare word per 32 bins, so that the scan of the tail,
+    // in which every thread walks its own 32 consecutive bins, is free of bank conflicts
+    extern __shared__ __align__(16) unsigned s_hist[];   // kL1Smem bytes
     __shared__ unsigned s_warp[32];
     __shared__ unsigned s_tbin[kTargets];
+    __shared__ unsigned s_trank[kTargets];
     __shared__ bool s_sal[kBlock];
     const int tid = threadIdx.x;
     const int isal = sel[0];
-    for (int k = tid; k < kL1Bins; k += blockDim.x) s_hist[k] = 0u;
+    for (int k = tid; k < kL1Bins + kL1Bins / 32; k += blockDim.x) s_hist[k] = 0u;
     if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
     __syncthreads();
     const size_t n4 = (size_t)R * (kBlock / 4);
@@ -300,16 +348,18 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
         const float vv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-            if (!s_sal[c4 + k]) atomicAdd(&s_hist[__float_as_uint(vv[k]) >> 16 & (kL1Bins - 1)], 1u);
+            if (!s_sal[c4 + k]) atomicAdd(&s_hist[pad1(__float_as_uint(vv[k]) >> 16 & (kL1Bins - 1))], 1u);
     }
     __syncthreads();
     for (int k = tid; k < kL1Bins; k += blockDim.x) {
-        const unsigned c = s_hist[k];
+        const unsigned c = s_hist[pad1(k)];
         if (c) atomicAdd(&ws.hist1[k], c);
     }
+    BPROF_PASS(3);
     if (!last_cta_done(&ws.counters[2], gridDim.x)) return;
 
     // ---- scan + locate the 162 target ranks ----
+    BPROF_MARK(0);
     const unsigned N = (unsigned)R * kBlock;
     const unsigned zeros = (unsigned)R * (unsigned)isal;
     {
@@ -319,20 +369,27 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
 #pragma unroll
         for (int u = 0; u < kL1Bins / 4 / 1024; ++u) h[u] = __ldcg(&src[tid + 1024 * u]);
 #pragma unroll
-        for (int u = 0; u < kL1Bins / 4 / 1024; ++u) reinterpret_cast<uint4*>(s_hist)[tid + 1024 * u] = h[u];
+        for (int u = 0; u < kL1Bins / 4 / 1024; ++u) {
+            const int b = pad1(4 * (tid + 1024 * u));                // four bins of one 32-bin group
+            s_hist[b] = h[u].x; s_hist[b + 1] = h[u].y; s_hist[b + 2] = h[u].z; s_hist[b + 3] = h[u].w;
+        }
         __syncthreads();
         if (tid == 0) s_hist[0] += zeros;
     }
     __syncthreads();
+    BPROF_MARK(1);
     {
+        // exclusive prefix over all bins: thread t owns bins 32 t .. 32 t + 31 (words 33 t ..)
         unsigned loc = 0;
-        const int b0 = tid * (kL1Bins / 1024);
+        unsigned* mine = s_hist + tid * 33;
 #pragma unroll 8
-        for (int k = 0; k < kL1Bins / 1024; ++k) loc += s_hist[b0 + k];
+        for (int k = 0; k < 32; ++k) loc += mine[k];
         unsigned run = block_exclusive_scan_1024(loc, s_warp);
-        for (int k = 0; k < kL1Bins / 1024; ++k) { const unsigned c = s_hist[b0 + k]; s_hist[b0 + k] = run; run += c; }
+#pragma unroll 8
+        for (int k = 0; k < 32; ++k) { const unsigned c = mine[k]; mine[k] = run; run += c; }
     }
     __syncthreads();
+    BPROF_MARK(2);
     if (tid < kSplits) {
         // numpy: virtual index (N-1)*p in float32, floor, fractional weight in float32
         const float p = __uint_as_float(c_split_probs[tid]);
@@ -340,22 +397,24 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
         const float lo = floorf(vi);
         ws.tgt_frac[tid] = __fsub_rn(vi, lo);
         const unsigned ilo = (unsigned)lo;
-        ws.tgt_rank[2 * tid] = min(ilo, N - 1);
-        ws.tgt_rank[2 * tid + 1] = min(ilo + 1, N - 1);
+        s_trank[2 * tid] = min(ilo, N - 1);
+        s_trank[2 * tid + 1] = min(ilo + 1, N - 1);
     }
     __syncthreads();
     if (tid < kTargets) {
-        const unsigned r = ws.tgt_rank[tid];
+        const unsigned r = s_trank[tid];
+        ws.tgt_rank[tid] = r;
         int lo = 0, hi = kL1Bins;                 // last bin with exclusive prefix <= r
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
-            if (s_hist[mid] <= r) lo = mid; else hi = mid;
+            if (s_hist[pad1(mid)] <= r) lo = mid; else hi = mid;
         }
         s_tbin[tid] = (unsigned)lo;
         ws.tgt_bin1[tid] = (unsigned)lo;
-        ws.tgt_rem[tid] = r - s_hist[lo];
+        ws.tgt_rem[tid] = r - s_hist[pad1(lo)];
     }
     __syncthreads();
+    BPROF_MARK(3);
     // level-1 slots: the number of distinct bins before each target (targets are rank ordered)
     if (tid < 32) {
         unsigned base = 0;
@@ -372,45 +431,59 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
             base += __popc(m);
         }
     }
+    BPROF_END(3);
 }
 
-// Warp-level search of `rem` inside a histogram row of `nbins` counters (nbins = 32 * per).
-// Returns the bin holding the rem-th element (0-based) and the rank left inside that bin.
+// Warp-level search inside a histogram row of 32 * PER counters (PER a multiple of 4): `load`
+// fetches the lane's PER consecutive counters and their prefix over the warp, `pick` returns the
+// bin holding the rem-th element (0-based) and the rank left inside that bin.  Two targets in the
+// same row (the two order statistics of one quantile nearly always are) share one `load`.
 template <int PER>
-__device__ __forceinline__ void warp_locate(const unsigned* row, unsigned rem, unsigned* bin_out,
-                                            unsigned* rem_out) {
-    const int lane = threadIdx.x & 31;
+struct WarpRow {
     unsigned c[PER];
-    unsigned tot = 0;
+    unsigned exc, inc;
+    __device__ __forceinline__ void load(const unsigned* row) {
+        const int lane = threadIdx.x & 31;
+        const uint4* src = reinterpret_cast<const uint4*>(row + lane * PER);
+        unsigned tot = 0;
 #pragma unroll
-    for (int k = 0; k < PER; ++k) { c[k] = __ldcg(&row[lane * PER + k]); tot += c[k]; }
-    unsigned inc = tot;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const unsigned t = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += t;
-    }
-    const unsigned exc = inc - tot;
-    const bool mine = (exc <= rem) && (rem < inc);
-    const unsigned who = __ballot_sync(0xffffffffu, mine);
-    unsigned bin = 32 * PER - 1, left = 0;
-    if (mine) {
-        unsigned run = exc;
-#pragma unroll
-        for (int k = 0; k < PER; ++k) {
-            if (rem < run + c[k]) { bin = lane * PER + k; left = rem - run; break; }
-            run += c[k];
+        for (int k = 0; k < PER / 4; ++k) {
+            const uint4 v = __ldcg(&src[k]);
+            c[4 * k] = v.x; c[4 * k + 1] = v.y; c[4 * k + 2] = v.z; c[4 * k + 3] = v.w;
+            tot += v.x + v.y + v.z + v.w;
         }
+        inc = tot;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned t = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        exc = inc - tot;
     }
-    const int src = who ? (__ffs(who) - 1) : 0;
-    *bin_out = __shfl_sync(0xffffffffu, bin, src);
-    *rem_out = __shfl_sync(0xffffffffu, left, src);
-}
+    __device__ __forceinline__ void pick(unsigned rem, unsigned* bin_out, unsigned* rem_out) const {
+        const int lane = threadIdx.x & 31;
+        const bool mine = (exc <= rem) && (rem < inc);
+        const unsigned who = __ballot_sync(0xffffffffu, mine);
+        unsigned bin = 32 * PER - 1, left = 0;
+        if (mine) {
+            unsigned run = exc;
+#pragma unroll
+            for (int k = 0; k < PER; ++k) {
+                if (rem < run + c[k]) { bin = lane * PER + k; left = rem - run; break; }
+                run += c[k];
+            }
+        }
+        const int src = who ? (__ffs(who) - 1) : 0;
+        *bin_out = __shfl_sync(0xffffffffu, bin, src);
+        *rem_out = __shfl_sync(0xffffffffu, left, src);
+    }
+};
 
 // Level 2: key bits 15..7 of the elements that fall in a level-1 target bin.
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(1024)
 k_select_l2(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
             const int* __restrict__ sel, BlockWs ws) {
+    BPROF_START(4);
     __shared__ bool s_sal[kBlock];
     __shared__ unsigned s_bin2[kTargets], s_slot1[kTargets], s_rem[kTargets], s_slot2[kTargets];
     __shared__ unsigned s_l2start[kTargets + 1], s_l2bin[kTargets];
@@ -431,49 +504,71 @@ k_select_l2(const float* __restrict__ M, int R, const unsigned char* __restrict_
             if (s) atomicAdd(&ws.hist2[(size_t)(s - 1) * kL2Bins + ((key >> 7) & (kL2Bins - 1))], 1u);
         }
     }
+    BPROF_PASS(4);
     if (!last_cta_done(&ws.counters[3], gridDim.x)) return;
 
+    BPROF_MARK(8);
     if (tid == 0) {
         const unsigned s0 = ws.slot1[0];
         if (s0) atomicAdd(&ws.hist2[(size_t)(s0 - 1) * kL2Bins], (unsigned)R * (unsigned)isal);
     }
     __syncthreads();
+    BPROF_MARK(9);
     const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
     if (tid < kTargets) { s_slot1[tid] = ws.tgt_slot[tid]; s_rem[tid] = ws.tgt_rem[tid]; }
     __syncthreads();
-    for (int t = warp; t < kTargets; t += nw) {
+    for (int p = warp; p < kSplits; p += nw) {            // the two order statistics of quantile p
+        const int ta = 2 * p, tb = ta + 1;
+        WarpRow<kL2Bins / 32> row;
         unsigned bin, left;
-        warp_locate<kL2Bins / 32>(ws.hist2 + (size_t)s_slot1[t] * kL2Bins, s_rem[t], &bin, &left);
-        if (lane == 0) { s_bin2[t] = bin; s_rem[t] = left; }
+        row.load(ws.hist2 + (size_t)s_slot1[ta] * kL2Bins);
+        row.pick(s_rem[ta], &bin, &left);
+        if (lane == 0) { s_bin2[ta] = bin; s_rem[ta] = left; }
+        if (s_slot1[tb] != s_slot1[ta]) row.load(ws.hist2 + (size_t)s_slot1[tb] * kL2Bins);
+        row.pick(s_rem[tb], &bin, &left);
+        if (lane == 0) { s_bin2[tb] = bin; s_rem[tb] = left; }
     }
     __syncthreads();
-    if (tid == 0) {
-        // level-2 slots: distinct (level-1 slot, bin2) pairs in rank order (shared memory only)
-        unsigned slot2 = 0, prev1 = 0xffffffffu;
-        for (int t = 0; t < kTargets; ++t) {
-            const unsigned s1 = s_slot1[t];
-            const bool fresh = (t == 0) || s1 != prev1 || s_bin2[t] != s_bin2[t - 1];
-            if (t > 0 && fresh) ++slot2;
-            if (s1 != prev1) { s_l2start[s1] = slot2; prev1 = s1; }   // level-1 slots are consecutive
-            if (fresh) s_l2bin[slot2] = s_bin2[t];
-            s_slot2[t] = slot2;
+    BPROF_MARK(10);
+    if (warp == 0) {
+        // level-2 slots: distinct (level-1 slot, bin2) pairs in rank order; level-1 slots are consecutive
+        unsigned base = 0;
+        for (int t0 = 0; t0 < kTargets; t0 += 32) {
+            const int t = t0 + lane;
+            const bool in = t < kTargets;
+            const unsigned s1 = in ? s_slot1[t] : 0u, b2 = in ? s_bin2[t] : 0u;
+            const bool new1 = in && (t == 0 || s1 != s_slot1[t - 1]);
+            const bool fresh = in && t > 0 && (new1 || b2 != s_bin2[t - 1]);
+            const unsigned m = __ballot_sync(0xffffffffu, fresh);
+            const unsigned slot2 = base + __popc(m & (0xffffffffu >> (31 - lane)));
+            if (in) {
+                s_slot2[t] = slot2;
+                if (fresh || t == 0) s_l2bin[slot2] = b2;
+                if (new1) s_l2start[s1] = slot2;
+                if (t == kTargets - 1) {
+                    s_l2start[s1 + 1] = slot2 + 1;
+                    ws.sel[3] = (int)slot2 + 1;
+                    ws.sel[2] = (int)s1 + 1;
+                }
+            }
+            base += __popc(m);
         }
-        s_l2start[prev1 + 1] = slot2 + 1;
-        ws.sel[3] = (int)slot2 + 1;
-        ws.sel[2] = (int)prev1 + 1;
     }
     __syncthreads();
+    BPROF_MARK(11);
     if (tid < kTargets) {
         ws.tgt_bin2[tid] = s_bin2[tid]; ws.tgt_rem[tid] = s_rem[tid]; ws.tgt_slot[tid] = s_slot2[tid];
         ws.l2_bin[tid] = s_l2bin[tid];
     }
     if (tid <= kTargets) ws.l2_start[tid] = s_l2start[tid];
+    BPROF_END(4);
 }
 
 // Level 3: key bits 6..0, then the 81 interpolated split candidates.
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(1024)
 k_select_l3(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
             const int* __restrict__ sel, BlockWs ws) {
+    BPROF_START(5);
     __shared__ bool s_sal[kBlock];
     __shared__ float s_val[kTargets];
     const int tid = threadIdx.x;
@@ -497,6 +592,7 @@ k_select_l3(const float* __restrict__ M, int R, const unsigned char* __restrict_
                 if (ws.l2_bin[j] == b2) { atomicAdd(&ws.hist3[(size_t)j * kL3Bins + (key & (kL3Bins - 1))], 1u); break; }
         }
     }
+    BPROF_PASS(5);
     if (!last_cta_done(&ws.counters[4], gridDim.x)) return;
 
     if (tid == 0) {
@@ -514,10 +610,16 @@ k_select_l3(const float* __restrict__ M, int R, const unsigned char* __restrict_
         s_hi[tid] = (ws.tgt_bin1[tid] << 16) | (ws.tgt_bin2[tid] << 7);
     }
     __syncthreads();
-    for (int t = warp; t < kTargets; t += nw) {
+    for (int p = warp; p < kSplits; p += nw) {
+        const int ta = 2 * p, tb = ta + 1;
+        WarpRow<kL3Bins / 32> row;
         unsigned bin, left;
-        warp_locate<kL3Bins / 32>(ws.hist3 + (size_t)s_slot[t] * kL3Bins, s_rem[t], &bin, &left);
-        if (lane == 0) s_val[t] = __uint_as_float(s_hi[t] | bin);
+        row.load(ws.hist3 + (size_t)s_slot[ta] * kL3Bins);
+        row.pick(s_rem[ta], &bin, &left);
+        if (lane == 0) s_val[ta] = __uint_as_float(s_hi[ta] | bin);
+        if (s_slot[tb] != s_slot[ta]) row.load(ws.hist3 + (size_t)s_slot[tb] * kL3Bins);
+        row.pick(s_rem[tb], &bin, &left);
+        if (lane == 0) s_val[tb] = __uint_as_float(s_hi[tb] | bin);
     }
     __syncthreads();
     if (tid < kSplits) {
@@ -528,6 +630,7 @@ k_select_l3(const float* __restrict__ M, int R, const unsigned char* __restrict_
         const float v1 = __fsub_rn(b, __fmul_rn(diff, __fsub_rn(1.0f, t)));
         ws.pvals[tid] = (t >= 0.5f) ? v1 : v0;
     }
+    BPROF_END(5);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -541,6 +644,7 @@ __device__ __forceinline__ bool key_less(unsigned ka, int ca, unsigned kb, int c
 
 __global__ void __launch_bounds__(256)
 k_sort_rows(const float* __restrict__ M, int R, float* __restrict__ sv, unsigned char* __restrict__ sc) {
+    BPROF_START(1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * 8 + warp;
     if (row >= R) return;
@@ -592,6 +696,7 @@ k_sort_rows(const float* __restrict__ M, int R, float* __restrict__ sv, unsigned
         make_float4(__uint_as_float(k[0]), __uint_as_float(k[1]), __uint_as_float(k[2]), __uint_as_float(k[3]));
     *reinterpret_cast<uchar4*>(sc + (int64_t)row * kBlock + 4 * lane) =
         make_uchar4((unsigned char)c[0], (unsigned char)c[1], (unsigned char)c[2], (unsigned char)c[3]);
+    BPROF_PASS(1);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -640,6 +745,7 @@ k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restr
                       const float* __restrict__ pvals_in, unsigned long long* __restrict__ acc,
                       const double* __restrict__ fx, unsigned* counters, int* __restrict__ sel,
                       float* __restrict__ pvals_out, double* __restrict__ trace, unsigned* status) {
+    BPROF_START(6);
     extern __shared__ __align__(16) unsigned char s_raw[];
     double* s_P1 = reinterpret_cast<double*>(s_raw);                         // [rows][pitch]
     double* s_P2 = s_P1 + kSplitRows * kRowPitch;
@@ -763,27 +869,34 @@ k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restr
         for (int r = 0; r < kSplitRows; ++r) t += s_acc[tid * kSplitRows + r];
         acc_add(&acc[kAccSplit + tid], t, fx[0]);        // slot kAccSplit + 81 is the salient-group term
     }
+    BPROF_PASS(6);
     if (!last_cta_done(&counters[5], gridDim.x)) return;
 
     if (tid <= kSplits) s_tot[tid] = (double)__ldcg(&acc[kAccSplit + tid]) * fx[1];
     __syncthreads();
-    if (tid == 0) {
-        int best; double gap;
-        const double e3 = s_tot[kSplits];
-        for (int c = 0; c < kSplits; ++c) s_tot[c] += e3;
-        first_strict_min(s_tot, kSplits, kSplits / 2, &best, &gap);
-        sel[1] = best;
-        const float p = s_p[best];
-        pvals_out[kSplits] = p;
-        trace[1] = (double)best;
-        trace[2] = (double)p;
-        trace[4] = gap;
-        const double inv = 1.0 / ((double)R * kBlock);
-        trace[5] = e3 * inv;
-        bool bad = false;
-        for (int c = 0; c < kSplits; ++c) { trace[105 + c] = s_tot[c] * inv; bad |= !isfinite(s_tot[c]); }
-        if (bad) atomicOr(status, CRB_FLAG_NONFINITE);
+    const double e3 = s_tot[kSplits];
+    __syncthreads();
+    if (tid < kSplits) s_tot[tid] += e3;
+    __syncthreads();
+    const double inv = 1.0 / ((double)R * kBlock);
+    if (tid < kSplits) {
+        trace[105 + tid] = s_tot[tid] * inv;
+        if (!isfinite(s_tot[tid])) atomicOr(status, CRB_FLAG_NONFINITE);
     }
+    if (warp == 0) {
+        int best; double gap;
+        warp_first_strict_min(s_tot, kSplits, kSplits / 2, &best, &gap);
+        if (lane == 0) {
+            sel[1] = best;
+            const float p = s_p[best];
+            pvals_out[kSplits] = p;
+            trace[1] = (double)best;
+            trace[2] = (double)p;
+            trace[4] = gap;
+            trace[5] = e3 * inv;
+        }
+    }
+    BPROF_END(6);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -812,20 +925,34 @@ __device__ __forceinline__ int lower_bound_d(const float* v, int n, double t) {
     return lo;
 }
 
+// The hole passes and the direct float32 evaluation of the i top values walk the same list: they
+// are fused pairwise (five passes over tv[0..i) in all).
 __device__ __forceinline__ double salient_candidate_err(const float* v, const double* P1, const double* P2,
                                                         const float* tv, int i) {
     const int n = kBlock - i;
-    // ---- the complement of the i top columns ----
+    const float fi = (float)i;
+    // pass 1: sums of the holes (complement) and of the salient values
     double H1 = 0.0, H2 = 0.0;
-    for (int h = 0; h < i; ++h) { const double t = (double)tv[h]; H1 += t; H2 += t * t; }
+    float s = 0.f;
+    for (int h = 0; h < i; ++h) {
+        const float x = tv[h];
+        const double t = (double)x;
+        H1 += t; H2 += t * t;
+        s += x;
+    }
     const double S1 = P1[kBlock] - H1, S2 = P2[kBlock] - H2;
     const float mu1 = __fdiv_rn((float)S1, (float)n);
+    const float mu = __fdiv_rn(s, fi);
     int cf = lower_bound_f(v, 0, kBlock, mu1);
     double c1 = (double)cf, a1 = P1[cf], b1 = P2[cf];
+    // pass 2: holes below mu1; first scale of the salient group
+    float a = 0.f;
     for (int h = 0; h < i; ++h) {
         const float t = tv[h];
         if (t < mu1) { c1 -= 1.0; a1 -= (double)t; b1 -= (double)t * (double)t; }
+        a += fabsf(t - mu);
     }
+    const float al = __fdiv_rn(a, fi);
     const double dmu1 = (double)mu1, dn = (double)n;
     const double A1 = dmu1 * c1 - a1 + (S1 - a1) - dmu1 * (dn - c1);
     const float al1 = __fdiv_rn((float)A1, (float)n);
@@ -838,27 +965,22 @@ __device__ __forceinline__ double salient_candidate_err(const float* v, const do
     double c2 = (double)cf, a2 = P1[cf];
     cf = lower_bound_d(v, kBlock, t2);
     double c3 = (double)cf, a3 = P1[cf];
+    // pass 3: holes below the second-pass thresholds; residual mean of the salient group
+    s = 0.f;
     for (int h = 0; h < i; ++h) {
-        const double t = (double)tv[h];
+        const float x = tv[h];
+        const double t = (double)x;
         if (t < t1) { c2 -= 1.0; a2 -= t; }
         if (t < t2) { c3 -= 1.0; a3 -= t; }
+        s += x - __fadd_rn(al * sgnf(x - mu), mu);
     }
     c3 -= c1; a3 -= a1;                                     // elements in [mu1, t2)
     const double cu = dn - c1, au = S1 - a1, bu = S2 - b1;  // the group at or above mu1
     const double A2 = (tlo * c2 - a2 + (a1 - a2) - tlo * (c1 - c2)) + (thi * c3 - a3 + (au - a3) - thi * (cu - c3));
     const double al2 = (double)__fdiv_rn((float)A2, (float)n);
     const double SS = (b1 - 2.0 * tlo * a1 + c1 * tlo * tlo) + (bu - 2.0 * thi * au + cu * thi * thi);
-    double err = SS - 2.0 * al2 * A2 + dn * al2 * al2;
-    // ---- the i top columns themselves, evaluated like the reference in float32 ----
-    const float fi = (float)i;
-    float s = 0.f;
-    for (int h = 0; h < i; ++h) s += tv[h];
-    const float mu = __fdiv_rn(s, fi);
-    float a = 0.f;
-    for (int h = 0; h < i; ++h) a += fabsf(tv[h] - mu);
-    const float al = __fdiv_rn(a, fi);
-    s = 0.f;
-    for (int h = 0; h < i; ++h) s += tv[h] - __fadd_rn(al * sgnf(tv[h] - mu), mu);
+    const double err = SS - 2.0 * al2 * A2 + dn * al2 * al2;
+    // passes 4 and 5: the i top columns themselves, evaluated like the reference in float32
     const float m2 = __fdiv_rn(s, fi);
     a = 0.f;
     for (int h = 0; h < i; ++h) a += fabsf((tv[h] - __fadd_rn(al * sgnf(tv[h] - mu), mu)) - m2);
@@ -873,12 +995,22 @@ __device__ __forceinline__ double salient_candidate_err(const float* v, const do
     return err + (double)e;
 }
 
+// Which candidates (salient counts) a thread evaluates: thread t works on row t % 16 of the tile
+// with schedule slot t / 16.  A candidate costs about i + 8 units; the slots are balanced
+// (longest-processing-time order), 94..108 units each instead of 177 for a plain round robin.
+__constant__ unsigned char c_sal_sched[16][4] = {
+    {49, 18, 17, 0}, {48, 19, 16, 0}, {47, 20, 15, 0}, {46, 21, 14, 0}, {45, 22, 13, 0}, {44, 23, 12, 0},
+    {43, 24, 11, 0}, {42, 25, 10, 0}, {41, 26, 9, 0}, {40, 27, 8, 0}, {39, 28, 7, 0}, {38, 29, 6, 0},
+    {37, 30, 5, 0}, {36, 31, 4, 0}, {35, 32, 3, 0}, {34, 33, 2, 1}};
+static_assert(kSalRows == 16 && kSalCand == 49, "c_sal_sched is laid out for 16 rows x 16 slots and 49 candidates");
+
 __global__ void __launch_bounds__(256)
 k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __restrict__ sc, int R,
                         int rows_per_cta, const unsigned char* __restrict__ rank,
                         unsigned long long* __restrict__ acc, const double* __restrict__ fx,
                         unsigned* counters, int* __restrict__ sel, double* __restrict__ trace,
                         unsigned* status) {
+    BPROF_START(2);
     extern __shared__ __align__(16) unsigned char s_raw[];
     double* s_P1 = reinterpret_cast<double*>(s_raw);                         // [rows][pitch]
     double* s_P2 = s_P1 + kSalRows * kRowPitch;
@@ -931,12 +1063,18 @@ k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __res
             }
         }
         __syncthreads();
-        // ---- phase B: one thread per (row, candidate) ----
-        for (int task = tid; task < kSalRows * kSalCand; task += blockDim.x) {
-            const int r = task % kSalRows, cand = task / kSalRows;
-            if (row_base + p0 + r >= R) continue;
-            s_acc[cand * kSalRows + r] += salient_candidate_err(s_v + r * kRowPitch, s_P1 + r * kRowPitch,
-                                                                s_P2 + r * kRowPitch, s_tv + r * kTopPitch, cand + 1);
+        // ---- phase B: one thread per (row, schedule slot) ----
+        {
+            const int r = tid & (kSalRows - 1), slot = tid >> 4;
+            if (row_base + p0 + r < R) {
+#pragma unroll 1
+                for (int k = 0; k < 4; ++k) {
+                    const int i = c_sal_sched[slot][k];
+                    if (i == 0) break;
+                    s_acc[(i - 1) * kSalRows + r] += salient_candidate_err(s_v + r * kRowPitch, s_P1 + r * kRowPitch,
+                                                                           s_P2 + r * kRowPitch, s_tv + r * kTopPitch, i);
+                }
+            }
         }
         __syncthreads();
     }
@@ -946,21 +1084,25 @@ k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __res
         for (int r = 0; r < kSalRows; ++r) t += s_acc[tid * kSalRows + r];
         acc_add(&acc[tid], t, fx[0]);
     }
+    BPROF_PASS(2);
     if (!last_cta_done(&counters[1], gridDim.x)) return;
 
     if (tid < kSalCand) s_tot[tid] = (double)__ldcg(&acc[tid]) * fx[1];
     __syncthreads();
-    if (tid == 0) {
-        int best; double gap;
-        first_strict_min(s_tot, kSalCand, max(1, kSalLimit / 3) - 1, &best, &gap);
-        sel[0] = best + 1;
-        trace[0] = (double)(best + 1);
-        trace[3] = gap;
-        bool bad = false;
-        const double inv = 1.0 / ((double)R * kBlock);
-        for (int c = 0; c < kSalCand; ++c) { trace[56 + c] = s_tot[c] * inv; bad |= !isfinite(s_tot[c]); }
-        if (bad) atomicOr(status, CRB_FLAG_NONFINITE);
+    if (tid < kSalCand) {
+        trace[56 + tid] = s_tot[tid] * (1.0 / ((double)R * kBlock));
+        if (!isfinite(s_tot[tid])) atomicOr(status, CRB_FLAG_NONFINITE);
     }
+    if (warp == 0) {
+        int best; double gap;
+        warp_first_strict_min(s_tot, kSalCand, max(1, kSalLimit / 3) - 1, &best, &gap);
+        if (lane == 0) {
+            sel[0] = best + 1;
+            trace[0] = (double)(best + 1);
+            trace[3] = gap;
+        }
+    }
+    BPROF_END(2);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1139,6 +1281,7 @@ k_finalize(float* __restrict__ W, int R, int64_t ldw, int col0, const float* __r
            const float* __restrict__ pvals, int technique, float lam, float corr_damp,
            float* __restrict__ Err, int64_t ld_err, float* __restrict__ Losses,
            unsigned char* __restrict__ codes, int64_t ld_codes, float* __restrict__ scales) {
+    BPROF_START(7);
     __shared__ float s_d[kBlock];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = row_in_warp(lane), l = lane_in_row(lane);
@@ -1218,6 +1361,7 @@ k_finalize(float* __restrict__ W, int R, int64_t ldw, int col0, const float* __r
 #pragma unroll
         for (int k = 0; k < 8; ++k) scales[(int64_t)row * 8 + k] = sc[k];
     }
+    BPROF_PASS(7);
 }
 
 // Stand-alone group binarizer on a [R, 128] block with an arbitrary element mask:
@@ -1264,6 +1408,19 @@ static int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 size_t block_workspace_bytes(int R) { return carve_block_ws(nullptr, R, nullptr); }
 
+#ifdef CRB_BLOCK_PROFILE
+extern "C" void crb_block_profile_read(unsigned long long* out32, int reset) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out32, g_bprof, sizeof(unsigned long long) * 32);
+    cudaMemcpyFromSymbol(out32 + 32, g_bmark, sizeof(unsigned long long) * 64);
+    if (reset) {
+        unsigned long long z[32];
+        for (int k = 0; k < 32; ++k) z[k] = (k % 4 == 0) ? ~0ull : 0ull;
+        cudaMemcpyToSymbol(g_bprof, z, sizeof(z));
+    }
+}
+#endif
+
 int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu, int block,
                       int technique, float lam, float corr_damp, int metric, float* Err, int64_t ld_err,
                       float* Losses, unsigned char* codes, int64_t ld_codes, float* scales,
@@ -1283,8 +1440,7 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
 
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(k_select_l1, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kL1Bins * (int)sizeof(unsigned)) != cudaSuccess ||
+        if (cudaFuncSetAttribute(k_select_l1, cudaFuncAttributeMaxDynamicSharedMemorySize, kL1Smem) != cudaSuccess ||
             cudaFuncSetAttribute(k_split_search_sorted, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kSplitSmem) != cudaSuccess ||
             cudaFuncSetAttribute(k_salient_search_sorted, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1309,12 +1465,12 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
     // K3-K5
     const int n4 = R * (kBlock / 4);
     const int g1 = min(148, ceil_div(n4, 1024 * 4));
-    k_select_l1<<<g1, 1024, kL1Bins * sizeof(unsigned), st>>>(ws.M, R, ws.rank, ws.sel, ws);
+    k_select_l1<<<g1, 1024, kL1Smem, st>>>(ws.M, R, ws.rank, ws.sel, ws);
     CRB_LAUNCHED();
-    const int g2 = min(2 * 148, ceil_div(n4, 512 * 2));
-    k_select_l2<<<g2, 512, 0, st>>>(ws.M, R, ws.rank, ws.sel, ws);
+    const int g2 = min(148, ceil_div(n4, 1024));
+    k_select_l2<<<g2, 1024, 0, st>>>(ws.M, R, ws.rank, ws.sel, ws);
     CRB_LAUNCHED();
-    k_select_l3<<<g2, 512, 0, st>>>(ws.M, R, ws.rank, ws.sel, ws);
+    k_select_l3<<<g2, 1024, 0, st>>>(ws.M, R, ws.rank, ws.sel, ws);
     CRB_LAUNCHED();
     // K6: split search on the sorted rows
     const int rows_sp = kSplitRows * ceil_div(R, kSplitRows * kMaxTiles);
