@@ -914,7 +914,8 @@ k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restr
 constexpr int kSalRows = 16;
 constexpr int kTopPitch = kSalLimit + 1;
 constexpr int kSalSmem = kSalRows * kRowPitch * (int)(sizeof(float) + 2 * sizeof(double)) +
-                         kSalRows * kTopPitch * (int)sizeof(float) + kSalCand * kSalRows * (int)sizeof(double);
+                         kSalRows * kTopPitch * (int)(2 * sizeof(float) + 2 * sizeof(double)) +
+                         kSalCand * kSalRows * (int)sizeof(double);
 
 __device__ __forceinline__ int lower_bound_d(const float* v, int n, double t) {
     int lo = 0, len = n;                         // first index with v[idx] >= t
@@ -926,26 +927,23 @@ __device__ __forceinline__ int lower_bound_d(const float* v, int n, double t) {
 }
 
 // The hole passes and the direct float32 evaluation of the i top values walk the same list: they
-// are fused pairwise (five passes over tv[0..i) in all).
+// are fused pairwise (four passes over tv[0..i) in all; the plain sums come from per-row running
+// sums in score order).
 __device__ __forceinline__ double salient_candidate_err(const float* v, const double* P1, const double* P2,
-                                                        const float* tv, int i) {
+                                                        const float* tv, const double* hp1, const double* hp2,
+                                                        const float* fs, int i) {
     const int n = kBlock - i;
     const float fi = (float)i;
-    // pass 1: sums of the holes (complement) and of the salient values
-    double H1 = 0.0, H2 = 0.0;
-    float s = 0.f;
-    for (int h = 0; h < i; ++h) {
-        const float x = tv[h];
-        const double t = (double)x;
-        H1 += t; H2 += t * t;
-        s += x;
-    }
+    // sums of the i holes (complement) and of the salient values: running sums in score order,
+    // prepared once per row
+    const double H1 = hp1[i], H2 = hp2[i];
+    float s = fs[i];
     const double S1 = P1[kBlock] - H1, S2 = P2[kBlock] - H2;
     const float mu1 = __fdiv_rn((float)S1, (float)n);
     const float mu = __fdiv_rn(s, fi);
     int cf = lower_bound_f(v, 0, kBlock, mu1);
     double c1 = (double)cf, a1 = P1[cf], b1 = P2[cf];
-    // pass 2: holes below mu1; first scale of the salient group
+    // pass 1: holes below mu1; first scale of the salient group
     float a = 0.f;
     for (int h = 0; h < i; ++h) {
         const float t = tv[h];
@@ -965,7 +963,7 @@ __device__ __forceinline__ double salient_candidate_err(const float* v, const do
     double c2 = (double)cf, a2 = P1[cf];
     cf = lower_bound_d(v, kBlock, t2);
     double c3 = (double)cf, a3 = P1[cf];
-    // pass 3: holes below the second-pass thresholds; residual mean of the salient group
+    // pass 2: holes below the second-pass thresholds; residual mean of the salient group
     s = 0.f;
     for (int h = 0; h < i; ++h) {
         const float x = tv[h];
@@ -980,7 +978,7 @@ __device__ __forceinline__ double salient_candidate_err(const float* v, const do
     const double al2 = (double)__fdiv_rn((float)A2, (float)n);
     const double SS = (b1 - 2.0 * tlo * a1 + c1 * tlo * tlo) + (bu - 2.0 * thi * au + cu * thi * thi);
     const double err = SS - 2.0 * al2 * A2 + dn * al2 * al2;
-    // passes 4 and 5: the i top columns themselves, evaluated like the reference in float32
+    // passes 3 and 4: the i top columns themselves, evaluated like the reference in float32
     const float m2 = __fdiv_rn(s, fi);
     a = 0.f;
     for (int h = 0; h < i; ++h) a += fabsf((tv[h] - __fadd_rn(al * sgnf(tv[h] - mu), mu)) - m2);
@@ -1017,6 +1015,9 @@ k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __res
     double* s_acc = s_P2 + kSalRows * kRowPitch;                             // [kSalCand][rows]
     float* s_v = reinterpret_cast<float*>(s_acc + kSalCand * kSalRows);      // [rows][pitch]
     float* s_tv = s_v + kSalRows * kRowPitch;                                // [rows][kTopPitch]
+    float* s_fs = s_tv + kSalRows * kTopPitch;                               // [rows][kTopPitch] float32 running sum
+    double* s_hp1 = reinterpret_cast<double*>(s_fs + kSalRows * kTopPitch);  // [rows][kTopPitch] running sum
+    double* s_hp2 = s_hp1 + kSalRows * kTopPitch;                            // [rows][kTopPitch] running sum of squares
     __shared__ unsigned char s_rank[kBlock];
     __shared__ double s_tot[kSalCand];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -1061,6 +1062,27 @@ k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __res
                 r1 += (double)x[q]; r2 += (double)x[q] * (double)x[q];
                 P1[4 * lane + q + 1] = r1; P2[4 * lane + q + 1] = r2;
             }
+            // running sums of the top-column values in score order ([i] = the first i of them):
+            // three lanes, one sequential sum each (the float32 one in the order a plain loop adds)
+            __syncwarp();
+            if (lane < 3) {
+                const float* tvr = s_tv + r * kTopPitch;
+                if (lane == 0) {
+                    float f = 0.f;
+                    float* o = s_fs + r * kTopPitch;
+                    o[0] = 0.f;
+                    for (int h = 0; h < kSalCand; ++h) { f += tvr[h]; o[h + 1] = f; }
+                } else {
+                    double d = 0.0;
+                    double* o = (lane == 1 ? s_hp1 : s_hp2) + r * kTopPitch;
+                    o[0] = 0.0;
+                    for (int h = 0; h < kSalCand; ++h) {
+                        const double t = (double)tvr[h];
+                        d += (lane == 1) ? t : t * t;
+                        o[h + 1] = d;
+                    }
+                }
+            }
         }
         __syncthreads();
         // ---- phase B: one thread per (row, schedule slot) ----
@@ -1071,8 +1093,9 @@ k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __res
                 for (int k = 0; k < 4; ++k) {
                     const int i = c_sal_sched[slot][k];
                     if (i == 0) break;
-                    s_acc[(i - 1) * kSalRows + r] += salient_candidate_err(s_v + r * kRowPitch, s_P1 + r * kRowPitch,
-                                                                           s_P2 + r * kRowPitch, s_tv + r * kTopPitch, i);
+                    s_acc[(i - 1) * kSalRows + r] += salient_candidate_err(
+                        s_v + r * kRowPitch, s_P1 + r * kRowPitch, s_P2 + r * kRowPitch, s_tv + r * kTopPitch,
+                        s_hp1 + r * kTopPitch, s_hp2 + r * kTopPitch, s_fs + r * kTopPitch, i);
                 }
             }
         }

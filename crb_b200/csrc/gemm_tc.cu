@@ -1,10 +1,14 @@
 // float32-faithful GEMM on the tensor cores:  C = alpha * A * op(B) + beta * C,  all float32.
 //
 // The reference multiplies in full float32 (TF32 is switched off, bigptq.py:11-12), so a plain
-// TF32 product (10-bit mantissa) would not do.  Every operand tile is split in shared memory
-// into hi = x with the low 13 mantissa bits cleared (exactly a TF32 number) and lo = x - hi
-// (exact in float32), and three tcgen05.mma kind::tf32 products hi*hi + hi*lo + lo*hi are
-// accumulated in float32 in TMEM: 21-22 significand bits per product, float32 accumulation.
+// TF32 product (10-bit mantissa) would not do.  Every operand tile x is taken as hi + lo with
+// hi = x with the low 13 mantissa bits cleared (exactly a TF32 number) and lo = x - hi (exact in
+// float32), and three tcgen05.mma kind::tf32 products hi*hi + hi*lo + lo*hi are accumulated:
+// 21-22 significand bits per product.  The tensor core reads only the upper 19 bits of a TF32
+// operand, so the raw float32 tile as TMA delivered it IS the hi plane; the splitter warps only
+// write the lo plane next to it (the accuracy test of the GEMM pins this behaviour: a part that
+// rounded instead of truncating would fail it at the 1e-3 level).  The kernel is bound by
+// shared-memory bandwidth (every MMA re-reads its 4-byte operands), not by the MMA rate.
 //
 // Used by the trailing update W[:, i2:] -= Err @ U[i1:i2, i2:] (bigptq.py:264) and by the
 // panel / rank-128 / inverse-merge products of the blocked factorisation.
@@ -31,17 +35,24 @@
 
 namespace crb {
 
-constexpr int GT_M = 128, GT_N = 256, GT_K = 32;          // K = 32 float32 = one 128-byte swizzle row
-constexpr int GT_STAGES = 2;
-constexpr int GT_A_BYTES = GT_M * GT_K * 4;                 // 16 KiB
-constexpr int GT_B_BYTES = GT_N * GT_K * 4;                 // 32 KiB
-constexpr int GT_RAW_BYTES = GT_A_BYTES + GT_B_BYTES;       // 48 KiB: hi planes (TMA destination)
+#ifndef CRB_GEMM_STAGE_K
+#define CRB_GEMM_STAGE_K 16
+#endif
+// K per shared-memory stage: 32 (128-byte rows, 2 stages) or 16 (64-byte rows, 4 stages: the
+// deeper ring hides the TMA latency between "MMAs retired" and "next tile split").
+constexpr int GT_M = 128, GT_N = 256, GT_K = CRB_GEMM_STAGE_K;
+static_assert(GT_K == 32 || GT_K == 16, "stage depth");
+constexpr int GT_STAGES = GT_K == 32 ? 2 : 4;
+constexpr int GT_A_BYTES = GT_M * GT_K * 4;                 // 16 / 8 KiB
+constexpr int GT_B_BYTES = GT_N * GT_K * 4;                 // 32 / 16 KiB
+constexpr int GT_RAW_BYTES = GT_A_BYTES + GT_B_BYTES;       // hi planes (TMA destination)
 constexpr int GT_STAGE_BYTES = 2 * GT_RAW_BYTES;            // + lo planes
+constexpr int GT_BOX_BYTES = 32 * GT_K * 4;                 // MN-major B: one box of 32 columns x GT_K k-rows
 constexpr int GT_EPI_BYTES = 8 * 32 * 33 * 4;                 // per-warp transpose patches of the epilogue
 constexpr int GT_SMEM = GT_STAGES * GT_STAGE_BYTES + 256 + GT_EPI_BYTES + 1024;
 constexpr int GT_THREADS = 512;              // warpgroups: TMA + MMA (+ 2 idle warps), 4 splitter warps, 2 x 4 epilogue warps
 #ifndef CRB_GEMM_CHUNK_STEPS
-#define CRB_GEMM_CHUNK_STEPS 1
+#define CRB_GEMM_CHUNK_STEPS (32 / CRB_GEMM_STAGE_K)
 #endif
 constexpr int GT_CHUNK_STEPS = CRB_GEMM_CHUNK_STEPS;   // K steps (of 32) accumulated in TMEM before the fold into registers
 // registers per thread after the reallocation; the sum over the four warpgroups is 512 = 4 x 128
@@ -62,14 +73,15 @@ struct GemmArgs {
     unsigned* status;
 };
 
-// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+// K-major operand: rows of GT_K floats (128 bytes with the 128-byte swizzle, 64 bytes with the
+// 64-byte swizzle), 8-row groups 8 rows apart.
 __device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t saddr) {
     uint64_t d = 0;
     d |= (uint64_t)((saddr >> 4) & 0x3fffu);
     d |= (uint64_t)1 << 16;                               // leading offset: unused for swizzled K-major
-    d |= (uint64_t)(1024 >> 4) << 32;                     // stride between 8-row groups
+    d |= (uint64_t)((8 * GT_K * 4) >> 4) << 32;           // stride between 8-row groups
     d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
+    d |= (uint64_t)(GT_K == 32 ? 2 : 4) << 61;            // SWIZZLE_128B / SWIZZLE_64B
     return d;
 }
 // MN-major 32-bit operand: the only shared-memory layout the tensor core accepts is the 128-byte
@@ -184,7 +196,7 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     } else {
 #pragma unroll
                         for (int b = 0; b < GT_N / 32; ++b)                               // 32 cols x 32 k-rows each
-                            tma_load_2d(sb + b * 4096, &map_b, nj * GT_N + b * 32, ks * GT_K, fb);
+                            tma_load_2d(sb + b * GT_BOX_BYTES, &map_b, nj * GT_N + b * 32, ks * GT_K, fb);
                     }
                     if (++stage == GT_STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -238,8 +250,8 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                             // 8-row group (1024 bytes) of an MN-major box
                             const uint32_t ao = k * 32, bo = g.b_is_nk ? k * 32 : k * 1024;
                             const uint64_t dah = kmajor_sw128_desc(a_hi + ao), dal = kmajor_sw128_desc(a_lo + ao);
-                            const uint64_t dbh = g.b_is_nk ? kmajor_sw128_desc(b_hi + bo) : mnmajor_sw128_desc(b_hi + bo, 4096);
-                            const uint64_t dbl = g.b_is_nk ? kmajor_sw128_desc(b_lo + bo) : mnmajor_sw128_desc(b_lo + bo, 4096);
+                            const uint64_t dbh = g.b_is_nk ? kmajor_sw128_desc(b_hi + bo) : mnmajor_sw128_desc(b_hi + bo, GT_BOX_BYTES);
+                            const uint64_t dbl = g.b_is_nk ? kmajor_sw128_desc(b_lo + bo) : mnmajor_sw128_desc(b_lo + bo, GT_BOX_BYTES);
                             umma_tf32(d_tmem, dal, dbh, idesc, !first);      // small terms first
                             umma_tf32(d_tmem, dah, dbl, idesc, true);
                             umma_tf32(d_tmem, dah, dbh, idesc, true);
@@ -259,7 +271,7 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     }   // warps 2 and 3 only fill the first warpgroup
     } else if (warp < 8) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(GT_REGS_SPLIT));
-        // ---------------- splitter: hi = x with 13 low mantissa bits cleared, lo = x - hi ----------------
+        // ---------------- splitter: lo = x - (x with 13 low mantissa bits cleared) ----------------
         const int ctid = threadIdx.x - 128;                 // 0..127
         uint32_t stage = 0, phase = 0;
         bool ok = true;
@@ -283,8 +295,7 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     h.y = __uint_as_float(__float_as_uint(x.y) & 0xffffe000u); l.y = x.y - h.y;
                     h.z = __uint_as_float(__float_as_uint(x.z) & 0xffffe000u); l.z = x.z - h.z;
                     h.w = __uint_as_float(__float_as_uint(x.w) & 0xffffe000u); l.w = x.w - h.w;
-                    hi[i] = h;
-                    lo[i] = l;
+                    lo[i] = l;          // the raw tile itself serves as the hi plane (see the file header)
                 }
                 // make the generic-proxy writes visible to the tensor core (async proxy)
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -390,7 +401,7 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
 }
 
 // C[M,N] = alpha * A[M,K] * op(B) + beta * C on the tensor cores.
-// Requirements: K % 32 == 0, N % 32 == 0, leading dimensions % 4 == 0, 16-byte aligned bases.
+// Requirements: K % 16 == 0, N % 32 == 0, leading dimensions % 4 == 0, 16-byte aligned bases.
 // `status` (device, may be NULL) receives CRB_FLAG_WAIT_LIMIT if a bounded wait ran out.
 // `shape` is a set of GEMM_* flags: GEMM_LOWER_ONLY writes only the 128 x 128 blocks on or below
 // the diagonal of C; GEMM_B_LOWER / GEMM_A_LOWER promise a lower-triangular [K, N] operand B /
@@ -406,12 +417,13 @@ int gemm_tf32x3(bool b_is_nk, int shape, int M, int N, int K, float alpha, const
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
         return CRB_ERR_BAD_ARG;
     CUtensorMap map_a, map_b;
+    const CUtensorMapSwizzle ksw = GT_K == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     int rc = make_tensor_map_2d(&map_a, A, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)K, (uint64_t)M, (uint64_t)lda,
-                                GT_K, GT_M);
+                                GT_K, GT_M, ksw);
     if (rc != CRB_OK) return rc;
     if (b_is_nk)
         rc = make_tensor_map_2d(&map_b, B, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)K, (uint64_t)N, (uint64_t)ldb,
-                                GT_K, GT_N);
+                                GT_K, GT_N, ksw);
     int b_slabs = 0;
     if (!b_is_nk) {
         // one 3-D copy for the eight 32-column slabs of a stage when the driver accepts that shape

@@ -147,7 +147,7 @@ int crb_trailing_update(float *W_dev, int R, int C, int64_t ldw, const float *Er
  * LOWER_ONLY writes only the 128 x 128 blocks of C on or below its diagonal; B_LOWER promises
  * a lower-triangular [K, N] operand B (needs b_is_nk == 0, N <= K) and A_LOWER a
  * lower-triangular A (M <= K): the zero part of such an operand is not multiplied.
- * K % 32 == 0, N % 32 == 0, leading dimensions % 4 == 0; status (device, may be NULL).   */
+ * K % 16 == 0, N % 32 == 0, leading dimensions % 4 == 0; status (device, may be NULL).   */
 #define CRB_GEMM_LOWER_ONLY 1
 #define CRB_GEMM_B_LOWER 2
 #define CRB_GEMM_A_LOWER 4

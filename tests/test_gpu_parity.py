@@ -405,7 +405,7 @@ def test_config1_blocks(ops, config1, bi):
 def test_block_step_is_deterministic_and_row_count_agnostic(ops):
     """Full-size properties: two runs are bit-identical; ragged row counts work."""
     g = torch.Generator().manual_seed(77)
-    for R in (1, 7, 4096, 16384 + 40):
+    for R in (1, 7, 4096, 16384 + 40, 36864):            # 36864: the tallest linear of the largest configuration
         W = torch.randn(R, 256, generator=g) * 0.02
         d = 0.5 + torch.rand(256, generator=g)
         U = torch.diag(d).to(DEV)
