@@ -45,6 +45,7 @@ SIGNATURES = {
     "crb_linear_workspace_bytes": (_sz, [_i]),
     "crb_quantize_linear": (_i, [_vp, _i, _i, _i64, _vp, _i64, _i, _f, _f, _i, _vp, _vp, _vp, _vp,
                                  _vp, _sz, _vp]),
+    "crb_dequantize": (_i, [_vp, _i, _i, _i64, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "crb_read_status": (_i, [_vp, _vp]),
     "crb_launch_count": (C.c_ulonglong, []),
 }

@@ -52,6 +52,8 @@ class BRAGPTQ:
         self.last_trace = None
         self.last_timing = {}
         self.verbose = True         # the reference prints time and error per linear (bigptq.py:273-274)
+        self.pack = False           # set to keep the packed form of the result in `self.packed`
+        self.packed = None
 
     # ---- the Hessian as the reference exposes it ------------------------------------------
     @property
@@ -190,7 +192,7 @@ class BRAGPTQ:
             lam = float(getattr(self.braq_quantizer, "lam", 1e-5))
             corr_damp = float(getattr(self.braq_quantizer, "corr_damp", 0.1))
             st["out"] = ops.quantize_linear(W, U, st["technique"], lam, corr_damp, self.salient_metric,
-                                            want_codes=False, want_trace=True)
+                                            want_codes=bool(self.pack), want_trace=True)
             st["ev"][2].record()
         return st
 
@@ -206,6 +208,9 @@ class BRAGPTQ:
             self.last_flags = flags
             ev = st["ev"]
             self.last_timing = {"factor_ms": ev[0].elapsed_time(ev[1]), "blocks_ms": ev[1].elapsed_time(ev[2])}
+            if self.pack:
+                from .packed import pack_linear
+                self.packed = pack_linear(out["codes"], out["scales"], W, st["technique"])
             if self.verbose:
                 print("time %.2f" % (time.time() - st["tick"]))
                 print("error", error)

@@ -16,6 +16,10 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
 int binarize_group_launch(const float* W, int R, int64_t ldw, const unsigned char* mask, int64_t ldm,
                           int order, int technique, float lam, float corr_damp, float* Q, int64_t ldq,
                           cudaStream_t st);
+// dequant.cu
+int dequantize_launch(float* W, int R, int C, int64_t ldw, int technique, const unsigned char* b1,
+                      const unsigned char* lm, const unsigned char* salcol, const unsigned char* b2,
+                      const long long* b2_off, const int* b2_pitch, const float* scales, cudaStream_t st);
 // hessian.cu
 size_t hessian_workspace_bytes(int C, int64_t T, int dtype);
 int hessian_accumulate_launch(const void* X, int dtype, int64_t T, int C, int64_t ldx, float* S,
@@ -174,6 +178,14 @@ int crb_quantize_linear(float* W, int R, int C, int64_t ldw, const float* U, int
         }
     }
     return CRB_OK;
+}
+
+int crb_dequantize(float* W, int R, int C, int64_t ldw, int technique, const uint8_t* b1, const uint8_t* lm,
+                   const uint8_t* salcol, const uint8_t* b2, const int64_t* b2_off, const int32_t* b2_pitch,
+                   const float* scales, void* stream) {
+    return dequantize_launch(W, R, C, ldw, technique, b1, lm, salcol, b2,
+                             reinterpret_cast<const long long*>(b2_off), b2_pitch, scales,
+                             static_cast<cudaStream_t>(stream));
 }
 
 int crb_read_status(const void* workspace, void* stream) {

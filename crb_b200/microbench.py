@@ -5,6 +5,7 @@
     python -m crb_b200.microbench block    --R 4096 --technique crb
     python -m crb_b200.microbench trailing --R 4096 --C 4096
     python -m crb_b200.microbench linear   --R 4096 --C 4096 --technique crb
+    python -m crb_b200.microbench dequant  --R 4096 --C 4096 --technique crb
 
 Each run does `--warmup` untimed and `--iters` timed calls bracketed by CUDA events on the
 launching stream and prints one JSON line with the time per call and the algorithmic
@@ -51,7 +52,7 @@ def _synthetic_factor(C, dev, seed=0):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["hessian", "factor", "block", "trailing", "linear"])
+    ap.add_argument("what", choices=["hessian", "factor", "block", "trailing", "linear", "dequant"])
     ap.add_argument("--R", type=int, default=4096)
     ap.add_argument("--C", type=int, default=4096)
     ap.add_argument("--T", type=int, default=16384)
@@ -101,6 +102,18 @@ def main(argv=None):
         n = a.C - 128
         out.update(ms=ms, tflops=2.0 * a.R * 128 * n / ms / 1e9, gbs=(8.0 * a.R * n + 4 * a.R * 128 + 4 * 128 * n) / ms / 1e6,
                    note="first block of the loop: flop 2*R*128*(C-128); bytes read+write W[:,128:] + Err + U rows")
+    elif a.what == "dequant":
+        from . import packed
+        W = torch.randn(a.R, a.C, generator=g, device=dev) * 0.02
+        U = _synthetic_factor(a.C, dev)
+        o = ops.quantize_linear(W, U, a.technique, want_codes=True, want_trace=False)
+        p = packed.pack_linear(o["codes"], o["scales"], W, a.technique)
+        Wout = torch.empty_like(W)
+        ms = _time(lambda: packed.dequantize(p, Wout), a.warmup, a.iters)
+        assert torch.equal(Wout, W)
+        out.update(ms=ms, technique=a.technique, bits_per_weight=p.bits_per_weight(),
+                   gbs=(4.0 * a.R * a.C + p.nbytes()) / ms / 1e6,
+                   note="bytes: float32 weights written + packed planes and scales read")
     else:
         W = torch.randn(a.R, a.C, generator=g, device=dev) * 0.02
         U = _synthetic_factor(a.C, dev)

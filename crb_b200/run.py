@@ -55,7 +55,8 @@ def default_args(**overrides) -> SimpleNamespace:
                         nsamples=128, seed=0, percdamp=0.01, blocksize=128, salient_metric="hessian",
                         partition=3, global_scale=False, disable_gptq=False, minlayer=-1, maxlayer=1000,
                         quant_only="", invert=False, corr_damp=0.1, lam=1e-5, coupling=0.5,
-                        device="cuda:0", seqlen=None, forward_batch=8, act_offload_gib=64.0, verbose=True)
+                        device="cuda:0", seqlen=None, forward_batch=8, act_offload_gib=64.0, verbose=True,
+                        save_packed=None)
     for k, v in overrides.items():
         setattr(a, k, v)
     return a
@@ -372,6 +373,7 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
         gptq[name] = BRAGPTQ(subset[name], quantizer, salient_metric=args.salient_metric,
                              disable_gptq=args.disable_gptq)
         gptq[name].verbose = bool(args.verbose)
+        gptq[name].pack = bool(getattr(args, "save_packed", None))
 
     # ---- pass 1: Hessians.  Linears fed by the very same tensor share one accumulator. ----
     alias: Dict[str, str] = {}
@@ -481,6 +483,11 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
                 info = gptq[name].fasterquant(percdamp=args.percdamp, blocksize=args.blocksize,
                                               partition=args.partition, global_scale=args.global_scale)
             errors[name] = info["error"]
+            if gptq[name].packed is not None:
+                from . import packed as _packed
+                os.makedirs(args.save_packed, exist_ok=True)
+                _packed.save(os.path.join(args.save_packed, f"layer{index}.{name}.npz"), gptq[name].packed)
+                gptq[name].packed = None
             for k, v in gptq[name].last_timing.items():
                 timer.ms[k] = timer.ms.get(k, 0.0) + v
         states.clear()
@@ -607,6 +614,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--layers", type=int, default=None, help="synthetic models only: number of decoder layers")
     p.add_argument("--forward_batch", type=int, default=8, help="sequences per layer forward")
     p.add_argument("--act_offload_gib", type=float, default=64.0)
+    p.add_argument("--save_packed", type=str, default=None,
+                   help="directory that receives the packed form (bit planes + scales) of every binarized linear")
     p.add_argument("--quiet", action="store_true")
     return p
 

@@ -155,6 +155,22 @@ int crb_gemm_f32(int b_is_nk, int shape, int M, int N, int K, float alpha, const
                  int64_t lda, const float *B_dev, int64_t ldb, float beta, float *C_dev, int64_t ldc,
                  unsigned *status_dev, void *stream);
 
+/* ---- packed result -> float32 weights ---------------------------------------------
+ * Rebuilds W [R, C] from the packed form of a binarized linear (the reference only keeps the
+ * de-quantized weights, bigptq.py:276-280; its --save is commented out, run.py:1033-1039).
+ * All planes are LSB-first bit planes over the columns of a row:
+ *   b1 [R, C/8]      first sign (+1 if set)        lm [R, C/8]   mid group (else low)
+ *   salcol [C]       position of the column in its block's salient set, 255 = not salient
+ *   b2               per block b an [R, b2_pitch[b]] plane at byte offset b2_off[b]: second sign
+ *                    of the k-th salient column
+ *   scales [C/128, R, 8]  as written by crb_block_step / crb_quantize_linear
+ * Elements with a sign of 0 or outside every group are not representable and must be patched
+ * by the caller (crb_b200/packed.py lists them with their values).                      */
+int crb_dequantize(float *W_dev, int R, int C, int64_t ldw, int technique, const uint8_t *b1_dev,
+                   const uint8_t *lm_dev, const uint8_t *salcol_dev, const uint8_t *b2_dev,
+                   const int64_t *b2_off_dev, const int32_t *b2_pitch_dev, const float *scales_dev,
+                   void *stream);
+
 /* ---- whole linear ----------------------------------------------------------------
  * The block loop of BRAGPTQ.fasterquant (bigptq.py:131-264) for all C/128 blocks:
  * block step + trailing update, no host synchronisation.  The updates are grouped: a block's
