@@ -279,6 +279,8 @@ def run_ours(args):
 
     def host_steps(first, count):
         nonlocal host_in, host_out
+        if count <= 0:
+            return
         nxt = crun._Resident(layers[first], dev).prefetch()
         leaving = None
         for i in range(first, first + count):

@@ -942,14 +942,18 @@ __device__ __forceinline__ double salient_candidate_err(const float* v, const do
     const float mu1 = __fdiv_rn((float)S1, (float)n);
     const float mu = __fdiv_rn(s, fi);
     int cf = lower_bound_f(v, 0, kBlock, mu1);
-    double c1 = (double)cf, a1 = P1[cf], b1 = P2[cf];
+    int n1 = cf;                                            // elements below mu1 (whole row, then minus holes)
+    double a1 = P1[cf], b1 = P2[cf];
     // pass 1: holes below mu1; first scale of the salient group
     float a = 0.f;
+#pragma unroll 4
     for (int h = 0; h < i; ++h) {
         const float t = tv[h];
-        if (t < mu1) { c1 -= 1.0; a1 -= (double)t; b1 -= (double)t * (double)t; }
+        const double td = (double)t;
+        if (t < mu1) { --n1; a1 -= td; b1 = fma(-td, td, b1); }
         a += fabsf(t - mu);
     }
+    const double c1 = (double)n1;
     const float al = __fdiv_rn(a, fi);
     const double dmu1 = (double)mu1, dn = (double)n;
     const double A1 = dmu1 * c1 - a1 + (S1 - a1) - dmu1 * (dn - c1);
@@ -960,19 +964,24 @@ __device__ __forceinline__ double salient_candidate_err(const float* v, const do
     const double tlo = (double)ylo + (double)mu2, thi = (double)yhi + (double)mu2;
     const double t1 = fmin(tlo, dmu1), t2 = fmax(thi, dmu1);
     cf = lower_bound_d(v, kBlock, t1);
-    double c2 = (double)cf, a2 = P1[cf];
+    int n2 = cf;
+    double a2 = P1[cf];
     cf = lower_bound_d(v, kBlock, t2);
-    double c3 = (double)cf, a3 = P1[cf];
+    int n3 = cf;
+    double a3 = P1[cf];
     // pass 2: holes below the second-pass thresholds; residual mean of the salient group
     s = 0.f;
+#pragma unroll 4
     for (int h = 0; h < i; ++h) {
         const float x = tv[h];
         const double t = (double)x;
-        if (t < t1) { c2 -= 1.0; a2 -= t; }
-        if (t < t2) { c3 -= 1.0; a3 -= t; }
+        if (t < t1) { --n2; a2 -= t; }
+        if (t < t2) { --n3; a3 -= t; }
         s += x - __fadd_rn(al * sgnf(x - mu), mu);
     }
-    c3 -= c1; a3 -= a1;                                     // elements in [mu1, t2)
+    const double c2 = (double)n2;
+    const double c3 = (double)(n3 - n1);                    // elements in [mu1, t2)
+    a3 -= a1;
     const double cu = dn - c1, au = S1 - a1, bu = S2 - b1;  // the group at or above mu1
     const double A2 = (tlo * c2 - a2 + (a1 - a2) - tlo * (c1 - c2)) + (thi * c3 - a3 + (au - a3) - thi * (cu - c3));
     const double al2 = (double)__fdiv_rn((float)A2, (float)n);
@@ -981,9 +990,11 @@ __device__ __forceinline__ double salient_candidate_err(const float* v, const do
     // passes 3 and 4: the i top columns themselves, evaluated like the reference in float32
     const float m2 = __fdiv_rn(s, fi);
     a = 0.f;
+#pragma unroll 4
     for (int h = 0; h < i; ++h) a += fabsf((tv[h] - __fadd_rn(al * sgnf(tv[h] - mu), mu)) - m2);
     const float al2s = __fdiv_rn(a, fi);
     float e = 0.f;
+#pragma unroll 4
     for (int h = 0; h < i; ++h) {
         const float y1 = __fadd_rn(al * sgnf(tv[h] - mu), mu);
         const float r = (tv[h] - y1) - m2;
