@@ -2,7 +2,7 @@
 
 Run where the reference checkout is available:
 
-    python tests/golden/make_golden.py [--reference /root/reference] [--config1]
+    python tests/golden/make_golden.py --reference <checkout of the reference> [--config1]
 
 The reference is imported as it lies (nothing is copied); two modules it
 imports but never uses (`exceptiongroup`, `pyparsing`) are stubbed, and
@@ -211,7 +211,7 @@ def gen_config1(bigptq, binary, autosearch, out, keep_blocks=(0, 9)):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of an unmodified checkout of the reference project")
     ap.add_argument("--config1", action="store_true")
     args = ap.parse_args()
     torch.set_num_threads(max(1, os.cpu_count() or 1))
