@@ -483,7 +483,7 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
                 info = gptq[name].fasterquant(percdamp=args.percdamp, blocksize=args.blocksize,
                                               partition=args.partition, global_scale=args.global_scale)
             errors[name] = info["error"]
-            if gptq[name].packed is not None:
+            if getattr(gptq[name], "packed", None) is not None:
                 from . import packed as _packed
                 os.makedirs(args.save_packed, exist_ok=True)
                 _packed.save(os.path.join(args.save_packed, f"layer{index}.{name}.npz"), gptq[name].packed)
