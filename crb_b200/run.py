@@ -192,7 +192,7 @@ class _Feeder:
     copied one batch ahead on a side stream into two device buffers, so that the copy of batch
     j + 1 overlaps the layer forward of batch j."""
 
-    _buffers: Dict[tuple, torch.Tensor] = {}
+    _buffers: Dict[tuple, list] = {}        # per shape: [device buffers, events "slot no longer read"]
 
     def __init__(self, inps: torch.Tensor, fb: int, dev):
         self.inps, self.fb, self.dev = inps, fb, torch.device(dev)
@@ -202,14 +202,14 @@ class _Feeder:
             return
         key = (self.dev.index or 0, fb, tuple(inps.shape[1:]), inps.dtype)
         if key not in _Feeder._buffers:
-            _Feeder._buffers[key] = torch.empty((2, fb) + tuple(inps.shape[1:]), dtype=inps.dtype, device=self.dev)
-        self.buf = _Feeder._buffers[key]
-        self.h2d, d2h = _copy_streams(self.dev)
+            buf = torch.empty((2, fb) + tuple(inps.shape[1:]), dtype=inps.dtype, device=self.dev)
+            first = torch.cuda.Event()
+            first.record(torch.cuda.current_stream(self.dev))       # the buffers exist from here on
+            _Feeder._buffers[key] = [buf, [first, first]]
+        self.buf, self.free = _Feeder._buffers[key]    # `free` is shared: the next feeder continues it
+        self.h2d = _copy_streams(self.dev)[0]
         self.main = torch.cuda.current_stream(self.dev)
-        self.h2d.wait_stream(d2h)              # these inputs may be outputs still on their way to the host
-        self.h2d.wait_stream(self.main)        # and the buffers may still be read by earlier work
         self.ready = [None, None]
-        self.free = [None, None]
         self._stage(0)
 
     def _stage(self, idx):
@@ -217,8 +217,10 @@ class _Feeder:
         if j >= self.n:
             return
         slot = idx & 1
-        if self.free[slot] is not None:
-            self.h2d.wait_event(self.free[slot])
+        self.h2d.wait_event(self.free[slot])           # the slot's previous batch has been consumed
+        written = _WRITTEN.get((self.inps.data_ptr(), j))
+        if written is not None:
+            self.h2d.wait_event(written)               # these rows were an output on its way to the host
         with torch.cuda.stream(self.h2d):
             m = min(self.fb, self.n - j)
             self.buf[slot, :m].copy_(self.inps[j:j + m], non_blocking=True)
@@ -240,8 +242,14 @@ class _Feeder:
 
     def done(self, idx):
         if self.staged:
-            self.free[idx & 1] = torch.cuda.Event()
-            self.free[idx & 1].record(self.main)
+            ev = torch.cuda.Event()
+            ev.record(self.main)
+            self.free[idx & 1] = ev
+
+
+# (host buffer address, first row) -> event "these rows have arrived in host memory"; a feeder that
+# later reads the rows back waits for exactly that copy instead of for the whole copy stream
+_WRITTEN: Dict[tuple, object] = {}
 
 
 def _store_outputs(outs: torch.Tensor, j: int, y: torch.Tensor, dev):
@@ -251,6 +259,9 @@ def _store_outputs(outs: torch.Tensor, j: int, y: torch.Tensor, dev):
         d2h.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(d2h):
             outs[j:j + y.shape[0]].copy_(y, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(d2h)
+        _WRITTEN[(outs.data_ptr(), j)] = ev
         y.record_stream(d2h)
     else:
         outs[j:j + y.shape[0]].copy_(y, non_blocking=True)
@@ -428,6 +439,7 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
         seen.clear()
     for h in handles:
         h.remove()
+    feed2 = _Feeder(inps, fb, dev)            # the first batch of pass 2 travels while the linears are quantized
     leaders = [n for n in gptq if n not in alias]
     with timer.span("hessian_allreduce"):
         if ws > 1:
@@ -500,7 +512,7 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
 
     # ---- pass 2: re-propagate with the quantized weights (run.py:376-377) ----
     with timer.span("forward_repropagate"):
-        feed = _Feeder(inps, fb, dev)
+        feed = feed2
         for b in range(len(feed)):
             x = feed.batch(b)
             y = _layer_out(layer(x, **_replay_kwargs(layer_kwargs, x.shape[0])))
