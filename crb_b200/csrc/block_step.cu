@@ -711,7 +711,7 @@ k_sort_rows(const float* __restrict__ M, int R, float* __restrict__ sv, unsigned
 // accurate as the reference's float32 element-wise evaluation (differences ~1e-7 relative).
 // One thread per (row, candidate); three binary searches per task.
 // ---------------------------------------------------------------------------------------
-constexpr int kSplitRows = 16;                   // rows per pass of a CTA (small: more CTAs in flight, the phases are latency bound)
+constexpr int kSplitRows = 8;                    // rows per pass of a CTA (small: more CTAs in flight, the phases are latency bound)
 constexpr int kRowPitch = kBlock + 1;            // odd pitch: rows start in different banks
 constexpr int kSplitSmem = kSplitRows * kRowPitch * (int)(sizeof(float) + 2 * sizeof(double)) +
                            (kSplits + 1) * kSplitRows * (int)sizeof(double);
