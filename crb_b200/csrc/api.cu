@@ -12,7 +12,7 @@ size_t block_workspace_bytes(int R);
 int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu, int block,
                       int technique, float lam, float corr_damp, int metric, float* Err, int64_t ld_err,
                       float* Losses, unsigned char* codes, int64_t ld_codes, float* scales,
-                      double* trace, void* workspace, size_t workspace_bytes, cudaStream_t st);
+                      double* trace, void* workspace, size_t workspace_bytes, cudaStream_t st, bool reset_tickets = true);
 int binarize_group_launch(const float* W, int R, int64_t ldw, const unsigned char* mask, int64_t ldm,
                           int order, int technique, float lam, float corr_damp, float* Q, int64_t ldq,
                           cudaStream_t st);
@@ -164,7 +164,7 @@ int crb_quantize_linear(float* W, int R, int C, int64_t ldw, const float* U, int
         float* Err = ErrG + (size_t)(b - g0) * kBlock;
         int rc = block_step_launch(W, R, ldw, U, ldu, b, technique, lam, corr_damp, metric, Err, ld_err, Losses, codes,
                                    C, scales ? scales + (size_t)b * R * 8 : nullptr,
-                                   trace ? trace + (size_t)b * CRB_TRACE_DOUBLES : nullptr, workspace, bws, st);
+                                   trace ? trace + (size_t)b * CRB_TRACE_DOUBLES : nullptr, workspace, bws, st, b == 0);
         if (rc != CRB_OK) return rc;
         const int ed = (b + 1) * kBlock;
         rc = gemm_tf32x3(false, 0, R, g1 * kBlock - ed, kBlock, -1.0f, Err, ld_err,

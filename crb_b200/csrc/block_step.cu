@@ -155,7 +155,7 @@ k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
                   const float* __restrict__ U, int64_t ldu, int rows_per_cta,
                   float* __restrict__ M, double* __restrict__ colpart, double* __restrict__ energy,
                   double* __restrict__ fx, unsigned* counters, unsigned char* __restrict__ rank_out,
-                  double* __restrict__ trace, unsigned* status) {
+                  double* __restrict__ trace, unsigned* status, uint4* __restrict__ zero_ptr, int zero_vecs) {
     BPROF_START(0);
     __shared__ float s_d2[kBlock];
     __shared__ double s_e[8];
@@ -163,6 +163,10 @@ k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
     __shared__ double s_score[kBlock];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = row_in_warp(lane), l = lane_in_row(lane);
+    // histograms and accumulators of the later kernels of this block step start at zero: cleared
+    // here instead of by a separate memset node in front of every block
+    for (int k = blockIdx.x * blockDim.x + tid; k < zero_vecs; k += gridDim.x * blockDim.x)
+        zero_ptr[k] = make_uint4(0u, 0u, 0u, 0u);
     if (tid < kBlock) {
         const float d = U[(int64_t)(col0 + tid) * ldu + col0 + tid];
         s_d2[tid] = __fmul_rn(d, d);
@@ -1458,7 +1462,7 @@ extern "C" void crb_block_profile_read(unsigned long long* out32, int reset) {
 int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu, int block,
                       int technique, float lam, float corr_damp, int metric, float* Err, int64_t ld_err,
                       float* Losses, unsigned char* codes, int64_t ld_codes, float* scales,
-                      double* trace, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+                      double* trace, void* workspace, size_t workspace_bytes, cudaStream_t st, bool reset_tickets) {
     if (!W || !U || !Err || !Losses || !workspace || R <= 0 || block < 0) return CRB_ERR_BAD_ARG;
     if (ld_err < kBlock || (ld_err & 3)) return CRB_ERR_BAD_ARG;
     if (technique < CRB_TECH_BRAQ || technique > CRB_TECH_CRB) return CRB_ERR_BAD_ARG;
@@ -1482,12 +1486,16 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
             return CRB_ERR_LAUNCH;
         attr_set = true;
     }
-    if (cudaMemsetAsync(ws.zero_begin, 0, ws.zero_bytes, st) != cudaSuccess) return CRB_ERR_LAUNCH;
+    // the last-CTA tickets reset themselves; a caller that cannot vouch for them (first use of a
+    // workspace, stand-alone calls) asks for a reset
+    if (reset_tickets && cudaMemsetAsync(ws.counters, 0, 64, st) != cudaSuccess) return CRB_ERR_LAUNCH;
 
     // K1
     const int rows1 = 32 * ceil_div(R, 32 * kMaxCtas1);
     k_metric_colscore<<<ceil_div(R, rows1), 256, 0, st>>>(W, R, ldw, col0, U, ldu, rows1, ws.M, ws.colpart,
-                                                          ws.energy, ws.fx, ws.counters, ws.rank, tr, ws.status);
+                                                          ws.energy, ws.fx, ws.counters, ws.rank, tr, ws.status,
+                                                          reinterpret_cast<uint4*>(ws.zero_begin + 64),
+                                                          (int)((ws.zero_bytes - 64) / 16));
     CRB_LAUNCHED();
     k_sort_rows<<<ceil_div(R, 8), 256, 0, st>>>(ws.M, R, ws.sv, ws.sc);
     CRB_LAUNCHED();

@@ -67,6 +67,7 @@ __device__ __forceinline__ void store_row16(float* __restrict__ row, int l, cons
 
 // "Last CTA done" election: returns true in exactly one CTA of the grid, after every other
 // CTA's global writes (made before the call) are visible to it.  No CTA waits on another.
+// The ticket counter must be 0 at launch; the elected CTA leaves it at 0 again.
 __device__ __forceinline__ bool last_cta_done(unsigned* counter, unsigned total) {
     __shared__ bool s_last;
     __threadfence();
@@ -74,6 +75,7 @@ __device__ __forceinline__ bool last_cta_done(unsigned* counter, unsigned total)
     if (threadIdx.x == 0) {
         const unsigned t = atomicAdd(counter, 1u);
         s_last = (t == total - 1);
+        if (s_last) *counter = 0u;          // nobody else touches it any more: ready for the next launch
     }
     __syncthreads();
     if (s_last) __threadfence();

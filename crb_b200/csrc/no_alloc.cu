@@ -32,7 +32,7 @@ size_t block_workspace_bytes(int R);
 int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu, int block,
                       int technique, float lam, float corr_damp, int metric, float* Err, int64_t ld_err,
                       float* Losses, unsigned char* codes, int64_t ld_codes, float* scales,
-                      double* trace, void* workspace, size_t workspace_bytes, cudaStream_t st);
+                      double* trace, void* workspace, size_t workspace_bytes, cudaStream_t st, bool reset_tickets = true);
 
 constexpr int kStaticMaxRows = CRB_STATIC_MAX_ROWS;
 // fixed tables of the block step (< 1 MiB) + per row 512 bytes of metric values, 512 bytes of
