@@ -26,40 +26,33 @@ k_dequantize(float* __restrict__ W, int R, int C, int64_t ldw, int technique,
              const unsigned char* __restrict__ salcol, const unsigned char* __restrict__ b2,
              const long long* __restrict__ b2_off, const int* __restrict__ b2_pitch,
              const float* __restrict__ scales) {
-    // one warp per (row, block): lane l rebuilds columns 4 l .. 4 l + 3 of the block
+    // one warp per (row, block): lane l rebuilds columns 4 l .. 4 l + 3 of the block.  The grid is
+    // (blocks, row groups of 8), so no index needs a division.
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nblk = C / kBlock;
-    const long long unit = (long long)blockIdx.x * 8 + warp;
-    if (unit >= (long long)R * nblk) return;
-    const int row = (int)(unit / nblk), blk = (int)(unit % nblk);
+    const int row = blockIdx.y * 8 + warp, blk = blockIdx.x;
+    if (row >= R) return;
     const int col = blk * kBlock + 4 * lane;
     const float* sc = scales + ((size_t)blk * R + row) * 8;
-    float s[8];
-    {
-        const float4 s0 = *reinterpret_cast<const float4*>(sc), s1 = *reinterpret_cast<const float4*>(sc + 4);
-        s[0] = s0.x; s[1] = s0.y; s[2] = s0.z; s[3] = s0.w; s[4] = s1.x; s[5] = s1.y; s[6] = s1.z; s[7] = s1.w;
-    }
-    const size_t bit_base = (size_t)row * (C / 8) + (col >> 3);
+    const float4 s0 = *reinterpret_cast<const float4*>(sc), s1 = *reinterpret_cast<const float4*>(sc + 4);
+    const size_t bit_base = (size_t)row * (C >> 3) + (col >> 3);
     const unsigned sh = (lane & 1) * 4;                       // this lane's four bits inside the byte
-    const unsigned v1 = (b1[bit_base] >> sh) & 15u, vg = (lm[bit_base] >> sh) & 15u;
-    const uchar4 scol = *reinterpret_cast<const uchar4*>(salcol + col);
-    const unsigned char sk[4] = {scol.x, scol.y, scol.z, scol.w};
+    const unsigned v1 = (unsigned)b1[bit_base] >> sh, vg = (unsigned)lm[bit_base] >> sh;
+    const unsigned scol = *reinterpret_cast<const unsigned*>(salcol + col);      // four column entries
     const unsigned char* b2row = b2 + b2_off[blk] + (size_t)row * b2_pitch[blk];
+    const bool braq = technique == CRB_TECH_BRAQ;
     float q[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-        const float B1 = ((v1 >> e) & 1u) ? 1.f : -1.f;
-        if (sk[e] == 255) {
-            const int g = (vg >> e) & 1u;                     // 0 low, 1 mid
-            q[e] = __fadd_rn(s[2 * g + 1] * B1, s[2 * g]);
+        // +1 / -1 from a bit: flip the sign bit of -1.0f
+        const float B1 = __uint_as_float(0xbf800000u ^ (((v1 >> e) & 1u) << 31));
+        const unsigned sk = (scol >> (8 * e)) & 255u;
+        if (sk == 255u) {
+            const bool mid = (vg >> e) & 1u;                  // else low
+            q[e] = __fadd_rn((mid ? s0.w : s0.y) * B1, mid ? s0.z : s0.x);
         } else {
-            const float B2 = ((b2row[sk[e] >> 3] >> (sk[e] & 7)) & 1u) ? 1.f : -1.f;
-            if (technique == CRB_TECH_BRAQ) {
-                const float y1 = __fadd_rn(s[5] * B1, s[4]);
-                q[e] = __fadd_rn(y1, __fadd_rn(s[7] * B2, s[6]));
-            } else {
-                q[e] = __fadd_rn(__fadd_rn(s[4], __fmul_rn(s[5], B1)), __fmul_rn(s[6], B2));
-            }
+            const float B2 = __uint_as_float(0xbf800000u ^ ((((unsigned)b2row[sk >> 3] >> (sk & 7u)) & 1u) << 31));
+            q[e] = braq ? __fadd_rn(__fadd_rn(s1.y * B1, s1.x), __fadd_rn(s1.w * B2, s1.z))
+                        : __fadd_rn(__fadd_rn(s1.x, __fmul_rn(s1.y, B1)), __fmul_rn(s1.z, B2));
         }
     }
     *reinterpret_cast<float4*>(W + (int64_t)row * ldw + col) = make_float4(q[0], q[1], q[2], q[3]);
@@ -74,10 +67,10 @@ int dequantize_launch(float* W, int R, int C, int64_t ldw, int technique, const 
     if ((ldw & 3) || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(scales) & 15) ||
         (reinterpret_cast<uintptr_t>(salcol) & 3))
         return CRB_ERR_BAD_ARG;
-    const long long units = (long long)R * (C / kBlock);
-    const long long ctas = (units + 7) / 8;
-    if (ctas > 0x7fffffffLL) return CRB_ERR_UNSUPPORTED;
-    k_dequantize<<<(unsigned)ctas, 256, 0, st>>>(W, R, C, ldw, technique, b1, lm, salcol, b2, b2_off, b2_pitch, scales);
+    const int row_groups = (R + 7) / 8;
+    if (row_groups > 65535) return CRB_ERR_UNSUPPORTED;
+    k_dequantize<<<dim3(C / kBlock, row_groups), 256, 0, st>>>(W, R, C, ldw, technique, b1, lm, salcol, b2, b2_off,
+                                                              b2_pitch, scales);
     CRB_LAUNCHED();
     return CRB_OK;
 }
