@@ -13,8 +13,9 @@ uniform random (no checkpoints or datasets offline).
 `e2e` times the same step when the layer weights and the calibration activations start
 in pinned host memory and the quantized weights and layer outputs are copied back.
 
---impl reference times the CPU port of the reference's path (the oracle) on the host
-cores on a bounded sample and extrapolates it to the same workload.
+--impl reference times the reference's own CPU code of the path (oracle/_ref when it was
+built, else the CPU restatement in oracle/) on the host cores on one fixed bounded sample
+and extrapolates it to the same workload.
 """
 from __future__ import annotations
 
@@ -95,64 +96,125 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------
-def cpu_port_sample(threads=None, rows=2048, cols=4096, nseq=2, technique="crb"):
-    """Times the CPU port of the reference's path on a bounded sample and extrapolates.
+CPU_SAMPLE_ROWS, CPU_SAMPLE_COLS, CPU_SAMPLE_SEQS = 4096, 4096, 2
 
-    Sample: a `rows` x 4096 slice of a q_proj-shaped linear; Hessian from `nseq` sequences of
-    2048 tokens; factorisation of the 4096 x 4096 Hessian; the full block loop on the slice.
-    Extrapolation to one OPT-6.7b decoder layer: Hessian time scales with tokens x C^2 per
-    distinct input, factorisation with C^3 per linear, block loop with rows x cols per linear.
-    Layer forwards are NOT included (hot path only).
+
+def cpu_reference_sample(technique="crb"):
+    """Times the reference's path on the host cores on ONE fixed, bounded sample and extrapolates.
+
+    Sample (the same wherever this is called): one whole q_proj-shaped linear, 4096 x 4096 --
+    Hessian from 2 sequences of 2048 tokens through add_batch, then fasterquant (damping,
+    factorisation chain, all 32 block steps with their trailing updates).  The code timed is the
+    reference's own (`oracle/_ref`, its modules byte-compiled where they lie) when that was built,
+    else the CPU restatement in `oracle/`.  Every host thread is used whatever OMP_NUM_THREADS the
+    launcher exported.
+    Extrapolation to one OPT-6.7b decoder layer: add_batch time scales with tokens x C^2 and runs
+    once per linear in the reference (q, k, v recompute the same Hessian: run.py:341-353); the
+    factorisation scales with C^3; the block loop with rows x cols (whole linear measured, so the
+    per-block fixed costs are in the figure).  Layer forwards are NOT included (hot path only).
     """
-    from oracle import crb_oracle as O
-    if threads:
-        torch.set_num_threads(threads)
+    import contextlib
+    import io
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    rows, cols, nseq = CPU_SAMPLE_ROWS, CPU_SAMPLE_COLS, CPU_SAMPLE_SEQS
     g = torch.Generator().manual_seed(0)
     W = torch.randn(rows, cols, generator=g) * 0.02
-    H = torch.zeros(cols, cols)
-    t0 = time.time()
-    n = 0
-    for j in range(nseq):
-        x = torch.randn(SEQLEN, cols, generator=g).half()
-        n = O.hessian_add_batch(H, n, x.unsqueeze(0))
-    t_hess = time.time() - t0
-    # the sample Hessian comes from few tokens: lift the diagonal so that it stays well conditioned
-    H += torch.eye(cols) * H.diagonal().mean() * 0.1
-    t0 = time.time()
-    Wc = W.clone()
-    U = O.hinv_upper_factor(H, Wc, 0.01)
-    t_factor = time.time() - t0
-    t0 = time.time()
-    O.quantize_linear(Wc, None, technique, U=U, keep_blocks=False)
-    t_blocks = time.time() - t0
+    xs = [torch.randn(1, SEQLEN, cols, generator=g).half() for _ in range(nseq)]
+    from oracle import build_ref
+    kind = "reference" if build_ref.available() else "port"
+    if kind == "reference":
+        bigptq, binary, _ = build_ref.load()
+        lin = torch.nn.Linear(cols, rows, bias=False)
+        lin.weight.data = W.clone()
+        gq = bigptq.BRAGPTQ(lin, binary.Binarization(lin.weight, method=technique, groupsize=128), "hessian")
+        t0 = time.time()
+        for x in xs:
+            gq.add_batch(x, None)
+        t_hess = time.time() - t0
+        # few tokens: lift the diagonal so that the factorisation needs no retry
+        gq.H += torch.eye(cols) * gq.H.diagonal().mean() * 0.1
+        chol = torch.linalg.cholesky
+        t_fac = [0.0]
+
+        def timed_chol(*a, **k):
+            t = time.time()
+            out = chol(*a, **k)
+            t_fac[0] += time.time() - t
+            return out
+
+        inv = torch.cholesky_inverse
+
+        def timed_inv(*a, **k):
+            t = time.time()
+            out = inv(*a, **k)
+            t_fac[0] += time.time() - t
+            return out
+
+        torch.linalg.cholesky, torch.cholesky_inverse = timed_chol, timed_inv
+        try:
+            t0 = time.time()
+            with contextlib.redirect_stdout(io.StringIO()):
+                gq.fasterquant(blocksize=128, percdamp=0.01, partition=3)
+            t_quant = time.time() - t0
+        finally:
+            torch.linalg.cholesky, torch.cholesky_inverse = chol, inv
+        t_factor, t_blocks = t_fac[0], t_quant - t_fac[0]
+    else:
+        from oracle import crb_oracle as O
+        H = torch.zeros(cols, cols)
+        t0 = time.time()
+        n = 0
+        for x in xs:
+            n = O.hessian_add_batch(H, n, x)
+        t_hess = time.time() - t0
+        H += torch.eye(cols) * H.diagonal().mean() * 0.1
+        t0 = time.time()
+        Wc = W.clone()
+        U = O.hinv_upper_factor(H, Wc, 0.01)
+        t_factor = time.time() - t0
+        t0 = time.time()
+        O.quantize_linear(Wc, None, technique, U=U, keep_blocks=False)
+        t_blocks = time.time() - t0
     d, f = 4096, 16384
-    hess_unit = t_hess / (nseq * SEQLEN * cols * cols)             # s per token*C^2
-    layer_hess = hess_unit * NSAMPLES * SEQLEN * (5 * d * d + f * f)   # q,k,v,out,fc1 inputs + fc2 input
-    fac_unit = t_factor / cols ** 3
-    layer_factor = fac_unit * (5 * d ** 3 + f ** 3)
-    blk_unit = t_blocks / (rows * cols)
-    layer_blocks = blk_unit * (4 * d * d + 2 * d * f)
+    hess_unit = t_hess / (nseq * SEQLEN * cols * cols)             # s per token * C^2
+    # the reference accumulates one Hessian per linear: q, k, v, out, fc1 on 4096 inputs, fc2 on 16384
+    layer_hess = hess_unit * NSAMPLES * SEQLEN * (5 * d * d + f * f)
+    layer_factor = t_factor / cols ** 3 * (5 * d ** 3 + f ** 3)
+    layer_blocks = t_blocks / (rows * cols) * (4 * d * d + 2 * d * f)
     layer_s = layer_hess + layer_factor + layer_blocks
-    return dict(layer_s=layer_s, sample_s=t_hess + t_factor + t_blocks,
+    return dict(layer_s=layer_s, sample_s=t_hess + t_factor + t_blocks, kind=kind,
                 phases=dict(hessian_s=layer_hess, factor_s=layer_factor, blocks_s=layer_blocks),
+                sample_phases=dict(hessian_s=t_hess, factor_s=t_factor, blocks_s=t_blocks),
                 cores=torch.get_num_threads(),
-                sample=(f"CPU port of the reference path: {rows}x{cols} slice of q_proj, Hessian from {nseq}x{SEQLEN} "
-                        f"tokens, 4096^2 factorisation, 32-block loop; extrapolated per phase to one "
-                        f"{MODEL} layer (forwards excluded)"))
+                sample=(("the reference's own code (oracle/_ref)" if kind == "reference" else "CPU port of the reference path")
+                        + f": one whole {rows}x{cols} linear (q_proj shape), add_batch on {nseq}x{SEQLEN} tokens, "
+                          f"fasterquant with its factorisation chain and all 32 block steps; extrapolated per phase to one "
+                          f"{MODEL} layer (forwards excluded)"))
+
+
+CPU_ARM_BUDGET_S = 200.0
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    times = []
-    info = None
-    # bounded sample: about 150 s of CPU work for the whole run
-    per_step = 150.0 / max(1, args.warmup + args.steps)
-    rows = 2048 if per_step >= 14 else 1024 if per_step >= 8 else 512 if per_step >= 5 else 256
+    # every step is the same fixed sample; when W + K of them would not fit the budget, fewer
+    # repeats are run (at least one timed), never a smaller sample
+    times, info, spent, done_warm = [], None, 0.0, 0
     for i in range(args.warmup + args.steps):
-        info = cpu_port_sample(rows=rows)
-        if i >= args.warmup:
+        warm = i < args.warmup
+        if info is not None and spent + info["sample_s"] * 1.3 > CPU_ARM_BUDGET_S and (warm or times):
+            continue
+        if warm and done_warm >= 1 and spent + 2 * info["sample_s"] * 1.3 > CPU_ARM_BUDGET_S:
+            continue                          # keep room for one timed repeat
+        t0 = time.time()
+        info = cpu_reference_sample(args.technique)
+        spent += time.time() - t0
+        if warm:
+            done_warm += 1
+        else:
             times.append(info["layer_s"])
     layer_s = sum(times) / len(times)
     value = layer_s * MODEL_LAYERS
@@ -160,8 +222,9 @@ def run_reference(args):
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": layer_s * 1e3,
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic", "config": workload_config(args),
-            "cpu_baseline": {"value": value, "unit": "s", "cores": info["cores"], "kind": "port",
-                             "sample": info["sample"]},
+            "cpu_baseline": {"value": value, "unit": "s", "cores": info["cores"], "kind": info["kind"],
+                             "sample": info["sample"], "sample_s": info["sample_s"],
+                             "repeats_timed": len(times), "repeats_warmup": done_warm},
             "e2e": {"value": value, "unit": "s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "phases_s_per_layer": info["phases"]}
     print(json.dumps(line))
@@ -272,7 +335,7 @@ def run_ours(args):
 
     # ---- arm 2 (`e2e`): the same call on HOST buffers.  Weights and activations start every step in
     # pinned host memory and end there; quantize_layer streams the activations through the device
-    # batch by batch (twice in, once out) and the weights of the next / previous layer move while a
+    # batch by batch (once in, once out) and the weights of the next / previous layer move while a
     # layer is being quantized.  Timed as a whole: first copy in to last copy out. ----
     host_in.copy_(dev_in)
     torch.cuda.synchronize()
@@ -319,23 +382,27 @@ def run_ours(args):
     peaks = read_peaks()
     d, f = hidden, model.config.ffn_dim if hasattr(model.config, "ffn_dim") else model.config.intermediate_size
     roof = hessian_roofline(dev, d, f, args, peaks)
+    roof_extra = extra_rooflines(dev, d, f, args.technique, peaks) if rank == 0 else None
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        info = cpu_port_sample()
-        cpu = {"value": info["layer_s"] * MODEL_LAYERS, "unit": "s", "cores": info["cores"], "kind": "port",
-               "sample": info["sample"], "sample_s": info["sample_s"]}
+        info = cpu_reference_sample(args.technique)
+        cpu = {"value": info["layer_s"] * MODEL_LAYERS, "unit": "s", "cores": info["cores"], "kind": info["kind"],
+               "sample": info["sample"], "sample_s": info["sample_s"], "phases_s_per_layer": info["phases"]}
 
     if rank == 0:
         line = {"metric": "wall_s_to_binarize_opt_6.7b_crb", "value": value, "unit": "s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32 (fp16 operands on the Hessian tensor cores)",
                 "data": "synthetic", "config": workload_config(args),
-                "e2e": {"value": e2e_value, "unit": "s", "h2d_bytes_per_step": layer_bytes + 2 * act_bytes,
+                "e2e": {"value": e2e_value, "unit": "s", "h2d_bytes_per_step": layer_bytes + act_bytes,
                         "d2h_bytes_per_step": layer_bytes + act_bytes + 8 * 6,
-                        "note": "same call on pinned host buffers; activations stream in twice (calibration and "
-                                "re-propagation pass) and out once per step, copies overlap compute"},
-                "gpu_launches": launches, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
+                        "note": "same call on pinned host buffers; per step the layer's weights and this rank's "
+                                "activation shard are copied in once (the shard stays on the device for the "
+                                "re-propagation pass) and the quantized weights and the layer outputs are copied "
+                                "out; copies overlap compute"},
+                "gpu_launches": launches, "clocks": clocks, "roofline": roof, "roofline_extra": roof_extra,
+                "cpu_baseline": cpu,
                 "phases_ms_per_step": {k: v / args.steps for k, v in phases.items()},
                 "block_error_sum_per_layer": err_sum / args.steps, "wall_clock_s_timed_region": wall,
                 "peaks": peaks["source"]}
@@ -347,7 +414,7 @@ def run_ours(args):
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of k_hessian_umma_pair on fp16
 # X [T, C], from an ncu capture of exactly that launch (profiles/k_hessian_umma_pair_fp16.txt);
 # the algorithmic bytes of the launch are T*C*2 + 2 * 4 * C*(C+256)/2 = 1.63e9.
-HESSIAN_DRAM_BYTES = {(16384, 16384): 8895349504 + 552018432}
+HESSIAN_DRAM_BYTES = {(16384, 16384): 9099327744 + 559308544}
 
 
 def hessian_roofline(dev, d, f, args, peaks):
@@ -380,6 +447,58 @@ def hessian_roofline(dev, d, f, args, peaks):
             "work": f"T={T} tokens x C={f}: {issued:.3e} flop issued on upper-triangle tiles "
                     f"({algorithmic:.3e} for the full product the reference computes)",
             "peak_source": f"{peaks['source']} cuBLAS bf16 burst"}
+
+
+def _time_ms(fn, reps, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+def extra_rooflines(dev, d, f, technique, peaks):
+    """The other two kernels the metric names, each timed alone with CUDA events on the launching
+    stream at the workload's shapes: the trailing-update GEMM (K = 128, fc2-shaped: 4096 rows,
+    16384 columns, first block) and the block step (fc1-shaped: 16384 rows; q_proj-shaped: 4096)."""
+    from crb_b200 import ops
+    out = []
+    # ---- trailing update W[:, 128:] -= Err @ U[0:128, 128:]  (bigptq.py:264) ----
+    R, C = d, f
+    W = torch.randn(R, C, device=dev) * 0.02
+    Err = torch.randn(R, 128, device=dev) * 0.01
+    U = torch.triu(torch.randn(C, C, device=dev) * 0.01)
+    ms = _time_ms(lambda: ops.trailing_update(W, Err, U, 0), reps=20)
+    flops = 2.0 * R * 128 * (C - 128)
+    nbytes = 8.0 * R * (C - 128) + 4.0 * R * 128 + 4.0 * 128 * (C - 128)
+    out.append({"kernel": "k_gemm_tf32x3 (trailing update, K=128)", "bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9,
+                "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                "launch_ms": ms, "tflops_fp32_equivalent": flops / (ms * 1e-3) / 1e12,
+                "tensor_frac_of_bf16_peak": 3.0 * flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+                "work": f"R={R}, N={C - 128}, K=128: {flops:.3e} flop (three TF32 MMAs per term), "
+                        f"{nbytes:.3e} B (W read + written, Err, U rows); 32 flop/B: HBM bound",
+                "peak_source": f"{peaks['source']} copy bandwidth"})
+    del W, Err, U
+    # ---- block step: 8 dependent kernels per 128-column block ----
+    for R in (f, d):
+        W = torch.randn(R, 256, device=dev) * 0.02
+        U = torch.diag(0.5 + torch.rand(256, device=dev))
+        losses = torch.zeros(R, device=dev)
+        ms = _time_ms(lambda: ops.block_step(W, U, 0, technique, losses=losses, want_codes=False), reps=20)
+        nbytes = 1536.0 * R + 65536.0
+        out.append({"kernel": "block step (8 kernels)", "bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9,
+                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                    "launch_ms": ms,
+                    "work": f"R={R}: {nbytes:.3e} algorithmic B per block (W block read, Q and Err written, U block, "
+                            f"losses); the searches cost about 1e3 flop per element, so the step is latency / issue bound",
+                    "peak_source": f"{peaks['source']} copy bandwidth"})
+        del W, U
+    return out
 
 
 def main():

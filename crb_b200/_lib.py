@@ -12,8 +12,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "_lib", "libcrb_b200.so")
 
 BLOCK = 128
-TRACE_DOUBLES = 192
-TECHNIQUES = {"braq": 0, "crbog": 1, "crb": 2}
+TRACE_DOUBLES = 272
+TECHNIQUES = {"braq": 0, "crbog": 1, "crb": 2, "crb_norefine": 3, "crb_symdamp": 4,
+              "crb_symdamp_norefine": 5}
+ORDERS_DEFAULT = 112
 METRICS = {"hessian": 0, "magnitude": 1}
 DTYPES = {"float32": 0, "float16": 1, "bfloat16": 2}
 
@@ -34,20 +36,21 @@ SIGNATURES = {
     "crb_factor_workspace_bytes": (_sz, [_i]),
     "crb_hinv_upper_factor": (_i, [_vp, _i, _vp, _i, _i64, _f, _i, _vp, _sz, _vp, _vp]),
     "crb_block_workspace_bytes": (_sz, [_i]),
-    "crb_block_step": (_i, [_vp, _i, _i64, _vp, _i64, _i, _i, _f, _f, _i, _vp, _vp, _vp, _vp, _vp,
+    "crb_block_step": (_i, [_vp, _i, _i64, _vp, _i64, _i, _i, _i, _f, _f, _i, _vp, _vp, _vp, _vp, _vp,
                             _vp, _sz, _vp]),
     "crb_block_step_static_max_rows": (_i, []),
-    "crb_block_step_static": (_i, [_vp, _i, _i64, _vp, _i64, _i, _i, _f, _f, _i, _vp, _vp, _vp, _vp, _vp,
+    "crb_block_step_static": (_i, [_vp, _i, _i64, _vp, _i64, _i, _i, _i, _f, _f, _i, _vp, _vp, _vp, _vp, _vp,
                                    _vp, _vp]),
     "crb_binarize_group": (_i, [_vp, _i, _i64, _vp, _i64, _i, _i, _f, _f, _vp, _i64, _vp]),
     "crb_trailing_update": (_i, [_vp, _i, _i, _i64, _vp, _vp, _i64, _i, _vp]),
     "crb_gemm_f32": (_i, [_i, _i, _i, _i, _i, _f, _vp, _i64, _vp, _i64, _f, _vp, _i64, _vp, _vp]),
     "crb_linear_workspace_bytes": (_sz, [_i]),
-    "crb_quantize_linear": (_i, [_vp, _i, _i, _i64, _vp, _i64, _i, _f, _f, _i, _vp, _vp, _vp, _vp,
+    "crb_quantize_linear": (_i, [_vp, _i, _i, _i64, _vp, _i64, _i, _i, _f, _f, _i, _vp, _vp, _vp, _vp,
                                  _vp, _sz, _vp]),
     "crb_dequantize": (_i, [_vp, _i, _i, _i64, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "crb_read_status": (_i, [_vp, _vp]),
     "crb_launch_count": (C.c_ulonglong, []),
+    "crb_selftest_wait_limit": (_i, [_vp, _sz, C.c_uint, _vp, _vp]),
 }
 
 _lib = None
@@ -72,6 +75,14 @@ def lib():
             fn.restype, fn.argtypes = res, args
         _lib = handle
     return _lib
+
+
+def orders_code(orders) -> int:
+    """(low, mid, salient) expansion counts -> the decimal-digit code of the C ABI (112 = (1, 1, 2))."""
+    o = tuple(int(v) for v in orders)
+    if len(o) != 3 or any(v not in (1, 2) for v in o):
+        raise NotImplementedError(f"orders {orders!r}: three values, each 1 or 2, are implemented")
+    return 100 * o[0] + 10 * o[1] + o[2]
 
 
 def check(rc: int, what: str) -> None:

@@ -6,8 +6,9 @@ kernels of libcrb_b200.so:
     add_batch    -> tcgen05 Hessian accumulation      (bigptq.py:37-54)
     fasterquant  -> device factorisation + block loop  (bigptq.py:56-291)
 
-Only the path of the techniques braq / crbog / crb is implemented (partition=3,
-orders=(1,1,2), blocksize 128, Hessian salience metric); anything else raises
+Only the path of the techniques braq / crbog / crb (and the crb_norefine / crb_symdamp /
+crb_symdamp_norefine variants of crb) is implemented: partition=3, orders with one or two
+expansions per group, blocksize 128, Hessian salience metric; anything else raises
 NotImplementedError instead of silently taking another route.
 """
 from __future__ import annotations
@@ -18,7 +19,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
-from ._lib import BLOCK, FLAG_BAD_PIVOT, FLAG_NONFINITE, CrbError
+from ._lib import BLOCK, TECHNIQUES, orders_code, FLAG_BAD_PIVOT, FLAG_NONFINITE, FLAG_WAIT_LIMIT, CrbError
 
 try:  # transformers.Conv1D weights are stored transposed (bigptq.py:28-29)
     import transformers
@@ -48,6 +49,7 @@ class BRAGPTQ:
         self._S = torch.zeros((self.columns, self.columns), device=self.dev, dtype=torch.float32)
         self._H_set = None          # a Hessian assigned from outside (diagnostics inject g.H)
         self._H_keep = None
+        self._hess_ws = None        # workspace of the Hessian kernel: its first word holds the status flags
         self.last_flags = 0
         self.last_trace = None
         self.last_timing = {}
@@ -92,7 +94,7 @@ class BRAGPTQ:
             # continue from an injected Hessian: S = H * n / 2
             self._S = self._H_set * (self.nsamples / 2.0)
             self._H_set = None
-        ops.hessian_accumulate(self._S, x)
+        self._hess_ws = ops.hessian_accumulate(self._S, x)
         self.nsamples += batch
 
     def _restore_hessian(self, H):
@@ -119,10 +121,11 @@ class BRAGPTQ:
     def fasterquant_begin(self, blocksize=128, percdamp=0.01, partition=3, orders=(1, 1, 2),
                           global_scale=False, factor_from=None):
         technique = getattr(self.braq_quantizer, "method", None)
-        if technique not in ("braq", "crbog", "crb"):
-            raise NotImplementedError(f"technique {technique!r}: only braq, crbog and crb are implemented")
-        if partition != 3 or tuple(orders) != (1, 1, 2):
-            raise NotImplementedError("only partition=3 with orders=(1,1,2) is implemented")
+        if technique not in TECHNIQUES:
+            raise NotImplementedError(f"technique {technique!r}: implemented are {sorted(TECHNIQUES)}")
+        if partition != 3:
+            raise NotImplementedError("only partition=3 is implemented")
+        orders_code(orders)                                         # raises for anything but 1 / 2 per group
         if blocksize != BLOCK:
             raise NotImplementedError(f"only blocksize {BLOCK} is implemented")
         if self.disable_gptq:
@@ -134,7 +137,7 @@ class BRAGPTQ:
             raise NotImplementedError(f"in_features must be a multiple of {BLOCK}")
 
         st = {"tick": time.time(), "percdamp": percdamp, "technique": technique,
-              "stream": torch.cuda.current_stream(self.dev), "leader": factor_from,
+              "stream": torch.cuda.current_stream(self.dev), "leader": factor_from, "orders": tuple(orders),
               "ev": [torch.cuda.Event(enable_timing=True) for _ in range(3)]}
         W = self.layer.weight.data.clone()
         if isinstance(self.layer, nn.Conv2d):
@@ -158,7 +161,11 @@ class BRAGPTQ:
             ops.hessian_finalize(H, 2.0 / max(self.nsamples, 1))
         st["H"] = H
         st["diag0"] = torch.diagonal(H).clone()
+        # status[0]: flags of the factorisation; status[1]: flags the Hessian kernel left (read together
+        # with the factorisation's, so checking them costs no extra synchronisation)
         st["status"] = torch.zeros(4, dtype=torch.int32, device=self.dev)
+        if self._hess_ws is not None:
+            st["status"][1:2].copy_(self._hess_ws[:4].view(torch.int32))
         ops.factor_enqueue(H, st["W"], percdamp, 0, st["status"])
         return st
 
@@ -176,13 +183,20 @@ class BRAGPTQ:
             else:
                 H = st["H"]
                 attempt = 0
-                while int(st["status"][0].item()) & FLAG_BAD_PIVOT:          # bigptq.py:115-123
-                    attempt += 1
-                    if attempt > 10:
+                while True:
+                    f_factor, f_hessian = st["status"][:2].tolist()
+                    if (f_factor | f_hessian) & FLAG_WAIT_LIMIT:
+                        raise CrbError("a bounded wait inside the %s kernels ran out (CRB_FLAG_WAIT_LIMIT): "
+                                       "the result would be incomplete"
+                                       % ("Hessian" if f_hessian & FLAG_WAIT_LIMIT else "factorisation"))
+                    if not (f_factor & FLAG_BAD_PIVOT):
+                        break
+                    attempt += 1                                          # bigptq.py:115-123: extras 0 .. 9
+                    if attempt >= 10:
                         ops.diagonal_fallback(H, st["diag0"], st["percdamp"])   # bigptq.py:124-126
                         break
                     self._restore_hessian(H)
-                    st["status"].zero_()
+                    st["status"][0] = 0
                     ops.factor_enqueue(H, W, st["percdamp"], attempt, st["status"])
                 U = H
                 st["factor_done"] = torch.cuda.Event()
@@ -192,7 +206,7 @@ class BRAGPTQ:
             lam = float(getattr(self.braq_quantizer, "lam", 1e-5))
             corr_damp = float(getattr(self.braq_quantizer, "corr_damp", 0.1))
             st["out"] = ops.quantize_linear(W, U, st["technique"], lam, corr_damp, self.salient_metric,
-                                            want_codes=bool(self.pack), want_trace=True)
+                                            want_codes=bool(self.pack), want_trace=True, orders=st["orders"])
             st["ev"][2].record()
         return st
 

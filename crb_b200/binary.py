@@ -8,6 +8,8 @@ techniques implemented are the three of the calibration path:
     crbog  coupled expansion, float64 2x2 solve  (binary.py:577-687)
     crb    CRB v7: Tikhonov-regularised joint scale solve, correlation damping,
            two-way sign refinement                (binary.py:1544-1638)
+    crb_norefine, crb_symdamp, crb_symdamp_norefine
+           the same function with skip_refinement / symmetric_damp set (binary.py:2885-2890)
 """
 from __future__ import annotations
 
@@ -15,7 +17,7 @@ import math
 
 import torch.nn as nn
 
-SUPPORTED_METHODS = ("braq", "crbog", "crb")
+SUPPORTED_METHODS = ("braq", "crbog", "crb", "crb_norefine", "crb_symdamp", "crb_symdamp_norefine")
 
 
 class Binarization(nn.Module):

@@ -5,12 +5,12 @@
 
 namespace crb {
 
-unsigned long long g_launches = 0;
+std::atomic<unsigned long long> g_launches{0};
 
 // block_step.cu
 size_t block_workspace_bytes(int R);
 int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu, int block,
-                      int technique, float lam, float corr_damp, int metric, float* Err, int64_t ld_err,
+                      int technique, int orders, float lam, float corr_damp, int metric, float* Err, int64_t ld_err,
                       float* Losses, unsigned char* codes, int64_t ld_codes, float* scales,
                       double* trace, void* workspace, size_t workspace_bytes, cudaStream_t st, bool reset_tickets = true);
 int binarize_group_launch(const float* W, int R, int64_t ldw, const unsigned char* mask, int64_t ldm,
@@ -38,7 +38,7 @@ using namespace crb;
 
 extern "C" {
 
-int crb_version(void) { return 1; }
+int crb_version(void) { return 2; }
 
 const char* crb_arch(void) { return "sm_100a"; }
 
@@ -54,7 +54,7 @@ const char* crb_status_string(int status) {
     }
 }
 
-unsigned long long crb_launch_count(void) { return g_launches; }
+unsigned long long crb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 size_t crb_hessian_workspace_bytes(int C, int64_t T, int dtype) { return hessian_workspace_bytes(C, T, dtype); }
 
@@ -80,13 +80,13 @@ int crb_hinv_upper_factor(float* H, int C, float* W, int R, int64_t ldw, float p
 size_t crb_block_workspace_bytes(int R) { return R > 0 ? block_workspace_bytes(R) : 0; }
 
 int crb_block_step(float* W, int R, int64_t ldw, const float* U, int64_t ldu, int block,
-                   int technique, float lam, float corr_damp, int metric, float* Err, float* Losses,
+                   int technique, int orders, float lam, float corr_damp, int metric, float* Err, float* Losses,
                    uint8_t* codes, float* scales, double* trace, void* workspace,
                    size_t workspace_bytes, void* stream) {
     // `codes` is [R, 128] for a single block: offset the base so that column (block*128 + j)
     // of a virtual [R, ldw]-wide buffer lands on codes[r, j].
     uint8_t* codes_base = codes ? codes - (int64_t)block * kBlock : nullptr;
-    return block_step_launch(W, R, ldw, U, ldu, block, technique, lam, corr_damp, metric, Err, kBlock, Losses,
+    return block_step_launch(W, R, ldw, U, ldu, block, technique, orders, lam, corr_damp, metric, Err, kBlock, Losses,
                              codes_base, kBlock, scales, trace, workspace, workspace_bytes,
                              static_cast<cudaStream_t>(stream));
 }
@@ -125,18 +125,6 @@ int crb_gemm_f32(int b_is_nk, int shape, int M, int N, int K, float alpha, const
 // group instead of once per block.
 constexpr int kGroup = 8;
 
-// CRB_LINEAR_GROUP (1..8) overrides the group size for experiments; 1 is the per-block update.
-static int group_blocks() {
-    static int v = 0;
-    if (!v) {
-        v = kGroup;
-        if (const char* e = getenv("CRB_LINEAR_GROUP")) {
-            const int x = atoi(e);
-            if (x >= 1 && x <= kGroup) v = x;
-        }
-    }
-    return v;
-}
 static_assert(CRB_GEMM_LOWER_ONLY == GEMM_LOWER_ONLY && CRB_GEMM_B_LOWER == GEMM_B_LOWER &&
               CRB_GEMM_A_LOWER == GEMM_A_LOWER, "shape flags of the header and of the kernel");
 
@@ -146,7 +134,7 @@ size_t crb_linear_workspace_bytes(int R) {
 }
 
 int crb_quantize_linear(float* W, int R, int C, int64_t ldw, const float* U, int64_t ldu,
-                        int technique, float lam, float corr_damp, int metric, float* Losses,
+                        int technique, int orders, float lam, float corr_damp, int metric, float* Losses,
                         uint8_t* codes, float* scales, double* trace, void* workspace,
                         size_t workspace_bytes, void* stream) {
     if (!W || !U || !Losses || !workspace || R <= 0 || C <= 0) return CRB_ERR_BAD_ARG;
@@ -158,11 +146,11 @@ int crb_quantize_linear(float* W, int R, int C, int64_t ldw, const float* U, int
     const int64_t ld_err = (int64_t)kGroup * kBlock;
     unsigned* status = static_cast<unsigned*>(workspace);
     if (cudaMemsetAsync(workspace, 0, 64, st) != cudaSuccess) return CRB_ERR_LAUNCH;   // status word
-    const int nblk = C / kBlock, grp = group_blocks();
+    const int nblk = C / kBlock, grp = kGroup;
     for (int b = 0; b < nblk; ++b) {
         const int g0 = b / grp * grp, g1 = g0 + grp < nblk ? g0 + grp : nblk;
         float* Err = ErrG + (size_t)(b - g0) * kBlock;
-        int rc = block_step_launch(W, R, ldw, U, ldu, b, technique, lam, corr_damp, metric, Err, ld_err, Losses, codes,
+        int rc = block_step_launch(W, R, ldw, U, ldu, b, technique, orders, lam, corr_damp, metric, Err, ld_err, Losses, codes,
                                    C, scales ? scales + (size_t)b * R * 8 : nullptr,
                                    trace ? trace + (size_t)b * CRB_TRACE_DOUBLES : nullptr, workspace, bws, st, b == 0);
         if (rc != CRB_OK) return rc;
@@ -186,6 +174,22 @@ int crb_dequantize(float* W, int R, int C, int64_t ldw, int technique, const uin
     return dequantize_launch(W, R, C, ldw, technique, b1, lm, salcol, b2,
                              reinterpret_cast<const long long*>(b2_off), b2_pitch, scales,
                              static_cast<cudaStream_t>(stream));
+}
+
+int crb_selftest_wait_limit(void* scratch, size_t scratch_bytes, unsigned limit_us, unsigned* status,
+                            void* stream) {
+    constexpr int M = 128, N = 256, K = 32;
+    if (!scratch || !status || scratch_bytes < (size_t)256 * 1024 || limit_us == 0) return CRB_ERR_BAD_ARG;
+    if (reinterpret_cast<uintptr_t>(scratch) & 255) return CRB_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(scratch, 0, (size_t)256 * 1024, st) != cudaSuccess) return CRB_ERR_LAUNCH;
+    float* A = static_cast<float*>(scratch);
+    float* B = A + M * K;
+    float* C = B + N * K;
+    GemmSelfTest t;
+    t.wait_ns = (unsigned long long)limit_us * 1000ull;
+    t.withhold_loads = 1;
+    return gemm_tf32x3(true, 0, M, N, K, 1.0f, A, K, B, K, 0.0f, C, N, status, st, &t);
 }
 
 int crb_read_status(const void* workspace, void* stream) {

@@ -23,27 +23,6 @@
 
 namespace crb {
 
-#ifdef CRB_BLOCK_PROFILE
-// Development builds only: first start / last end of the parallel part / end of the last-CTA tail
-// of each kernel of the block step (globaltimer, ns).
-__device__ unsigned long long g_bprof[8][4];
-__device__ __forceinline__ unsigned long long bprof_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define BPROF_START(id) do { if (threadIdx.x == 0) atomicMin(&g_bprof[id][0], bprof_ns()); } while (0)
-#define BPROF_PASS(id) do { if (threadIdx.x == 0) atomicMax(&g_bprof[id][1], bprof_ns()); } while (0)
-#define BPROF_END(id) do { if (threadIdx.x == 0) atomicMax(&g_bprof[id][2], bprof_ns()); } while (0)
-__device__ unsigned long long g_bmark[64];
-#define BPROF_MARK(slot) do { if (threadIdx.x == 0) g_bmark[slot] = bprof_ns(); } while (0)
-#else
-#define BPROF_MARK(slot)
-#define BPROF_START(id)
-#define BPROF_PASS(id)
-#define BPROF_END(id)
-#endif
-
 // float32 bit patterns of torch.linspace(0.10, 0.90, 81) (utils/autosearch.py:65).
 __constant__ unsigned c_split_probs[kSplits] = {
     0x3dcccccdu, 0x3de147aeu, 0x3df5c290u, 0x3e051eb8u, 0x3e0f5c29u, 0x3e19999au,
@@ -156,7 +135,6 @@ k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
                   float* __restrict__ M, double* __restrict__ colpart, double* __restrict__ energy,
                   double* __restrict__ fx, unsigned* counters, unsigned char* __restrict__ rank_out,
                   double* __restrict__ trace, unsigned* status, uint4* __restrict__ zero_ptr, int zero_vecs) {
-    BPROF_START(0);
     __shared__ float s_d2[kBlock];
     __shared__ double s_e[8];
     __shared__ double s_wcol[8][kBlock];
@@ -220,7 +198,6 @@ k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
         for (int w = 0; w < 8; ++w) v += s_e[w];
         energy[blockIdx.x] = v;
     }
-    BPROF_PASS(0);
     if (!last_cta_done(&counters[0], gridDim.x)) return;
 
     {
@@ -261,7 +238,6 @@ k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
         rank_out[tid] = (unsigned char)r;
         if (r < kSalLimit) trace[6 + r] = (double)tid;
     }
-    BPROF_END(0);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -332,7 +308,6 @@ __device__ __forceinline__ unsigned block_exclusive_scan_1024(unsigned v, unsign
 __global__ void __launch_bounds__(1024)
 k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
             const int* __restrict__ sel, BlockWs ws) {
-    BPROF_START(3);
     // bin b lives at s_hist[pad1(b)]: one spare word per 32 bins, so that the scan of the tail,
     // in which every thread walks its own 32 consecutive bins, is free of bank conflicts
     extern __shared__ __align__(16) unsigned s_hist[];   // kL1Smem bytes
@@ -359,11 +334,9 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
         const unsigned c = s_hist[pad1(k)];
         if (c) atomicAdd(&ws.hist1[k], c);
     }
-    BPROF_PASS(3);
     if (!last_cta_done(&ws.counters[2], gridDim.x)) return;
 
     // ---- scan + locate the 162 target ranks ----
-    BPROF_MARK(0);
     const unsigned N = (unsigned)R * kBlock;
     const unsigned zeros = (unsigned)R * (unsigned)isal;
     {
@@ -381,7 +354,6 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
         if (tid == 0) s_hist[0] += zeros;
     }
     __syncthreads();
-    BPROF_MARK(1);
     {
         // exclusive prefix over all bins: thread t owns bins 32 t .. 32 t + 31 (words 33 t ..)
         unsigned loc = 0;
@@ -393,7 +365,6 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
         for (int k = 0; k < 32; ++k) { const unsigned c = mine[k]; mine[k] = run; run += c; }
     }
     __syncthreads();
-    BPROF_MARK(2);
     if (tid < kSplits) {
         // numpy: virtual index (N-1)*p in float32, floor, fractional weight in float32
         const float p = __uint_as_float(c_split_probs[tid]);
@@ -418,7 +389,6 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
         ws.tgt_rem[tid] = r - s_hist[pad1(lo)];
     }
     __syncthreads();
-    BPROF_MARK(3);
     // level-1 slots: the number of distinct bins before each target (targets are rank ordered)
     if (tid < 32) {
         unsigned base = 0;
@@ -435,7 +405,6 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
             base += __popc(m);
         }
     }
-    BPROF_END(3);
 }
 
 // Warp-level search inside a histogram row of 32 * PER counters (PER a multiple of 4): `load`
@@ -487,7 +456,6 @@ struct WarpRow {
 __global__ void __launch_bounds__(1024)
 k_select_l2(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
             const int* __restrict__ sel, BlockWs ws) {
-    BPROF_START(4);
     __shared__ bool s_sal[kBlock];
     __shared__ unsigned s_bin2[kTargets], s_slot1[kTargets], s_rem[kTargets], s_slot2[kTargets];
     __shared__ unsigned s_l2start[kTargets + 1], s_l2bin[kTargets];
@@ -508,16 +476,12 @@ k_select_l2(const float* __restrict__ M, int R, const unsigned char* __restrict_
             if (s) atomicAdd(&ws.hist2[(size_t)(s - 1) * kL2Bins + ((key >> 7) & (kL2Bins - 1))], 1u);
         }
     }
-    BPROF_PASS(4);
     if (!last_cta_done(&ws.counters[3], gridDim.x)) return;
-
-    BPROF_MARK(8);
     if (tid == 0) {
         const unsigned s0 = ws.slot1[0];
         if (s0) atomicAdd(&ws.hist2[(size_t)(s0 - 1) * kL2Bins], (unsigned)R * (unsigned)isal);
     }
     __syncthreads();
-    BPROF_MARK(9);
     const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
     if (tid < kTargets) { s_slot1[tid] = ws.tgt_slot[tid]; s_rem[tid] = ws.tgt_rem[tid]; }
     __syncthreads();
@@ -533,7 +497,6 @@ k_select_l2(const float* __restrict__ M, int R, const unsigned char* __restrict_
         if (lane == 0) { s_bin2[tb] = bin; s_rem[tb] = left; }
     }
     __syncthreads();
-    BPROF_MARK(10);
     if (warp == 0) {
         // level-2 slots: distinct (level-1 slot, bin2) pairs in rank order; level-1 slots are consecutive
         unsigned base = 0;
@@ -559,20 +522,17 @@ k_select_l2(const float* __restrict__ M, int R, const unsigned char* __restrict_
         }
     }
     __syncthreads();
-    BPROF_MARK(11);
     if (tid < kTargets) {
         ws.tgt_bin2[tid] = s_bin2[tid]; ws.tgt_rem[tid] = s_rem[tid]; ws.tgt_slot[tid] = s_slot2[tid];
         ws.l2_bin[tid] = s_l2bin[tid];
     }
     if (tid <= kTargets) ws.l2_start[tid] = s_l2start[tid];
-    BPROF_END(4);
 }
 
 // Level 3: key bits 6..0, then the 81 interpolated split candidates.
 __global__ void __launch_bounds__(1024)
 k_select_l3(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
             const int* __restrict__ sel, BlockWs ws) {
-    BPROF_START(5);
     __shared__ bool s_sal[kBlock];
     __shared__ float s_val[kTargets];
     const int tid = threadIdx.x;
@@ -596,7 +556,6 @@ k_select_l3(const float* __restrict__ M, int R, const unsigned char* __restrict_
                 if (ws.l2_bin[j] == b2) { atomicAdd(&ws.hist3[(size_t)j * kL3Bins + (key & (kL3Bins - 1))], 1u); break; }
         }
     }
-    BPROF_PASS(5);
     if (!last_cta_done(&ws.counters[4], gridDim.x)) return;
 
     if (tid == 0) {
@@ -634,7 +593,6 @@ k_select_l3(const float* __restrict__ M, int R, const unsigned char* __restrict_
         const float v1 = __fsub_rn(b, __fmul_rn(diff, __fsub_rn(1.0f, t)));
         ws.pvals[tid] = (t >= 0.5f) ? v1 : v0;
     }
-    BPROF_END(5);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -648,7 +606,6 @@ __device__ __forceinline__ bool key_less(unsigned ka, int ca, unsigned kb, int c
 
 __global__ void __launch_bounds__(256)
 k_sort_rows(const float* __restrict__ M, int R, float* __restrict__ sv, unsigned char* __restrict__ sc) {
-    BPROF_START(1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * 8 + warp;
     if (row >= R) return;
@@ -700,7 +657,6 @@ k_sort_rows(const float* __restrict__ M, int R, float* __restrict__ sv, unsigned
         make_float4(__uint_as_float(k[0]), __uint_as_float(k[1]), __uint_as_float(k[2]), __uint_as_float(k[3]));
     *reinterpret_cast<uchar4*>(sc + (int64_t)row * kBlock + 4 * lane) =
         make_uchar4((unsigned char)c[0], (unsigned char)c[1], (unsigned char)c[2], (unsigned char)c[3]);
-    BPROF_PASS(1);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -749,7 +705,6 @@ k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restr
                       const float* __restrict__ pvals_in, unsigned long long* __restrict__ acc,
                       const double* __restrict__ fx, unsigned* counters, int* __restrict__ sel,
                       float* __restrict__ pvals_out, double* __restrict__ trace, unsigned* status) {
-    BPROF_START(6);
     extern __shared__ __align__(16) unsigned char s_raw[];
     double* s_P1 = reinterpret_cast<double*>(s_raw);                         // [rows][pitch]
     double* s_P2 = s_P1 + kSplitRows * kRowPitch;
@@ -873,7 +828,6 @@ k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restr
         for (int r = 0; r < kSplitRows; ++r) t += s_acc[tid * kSplitRows + r];
         acc_add(&acc[kAccSplit + tid], t, fx[0]);        // slot kAccSplit + 81 is the salient-group term
     }
-    BPROF_PASS(6);
     if (!last_cta_done(&counters[5], gridDim.x)) return;
 
     if (tid <= kSplits) s_tot[tid] = (double)__ldcg(&acc[kAccSplit + tid]) * fx[1];
@@ -885,6 +839,7 @@ k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restr
     const double inv = 1.0 / ((double)R * kBlock);
     if (tid < kSplits) {
         trace[105 + tid] = s_tot[tid] * inv;
+        trace[186 + tid] = (double)s_p[tid];
         if (!isfinite(s_tot[tid])) atomicOr(status, CRB_FLAG_NONFINITE);
     }
     if (warp == 0) {
@@ -900,7 +855,6 @@ k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restr
             trace[5] = e3 * inv;
         }
     }
-    BPROF_END(6);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1023,7 +977,6 @@ k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __res
                         unsigned long long* __restrict__ acc, const double* __restrict__ fx,
                         unsigned* counters, int* __restrict__ sel, double* __restrict__ trace,
                         unsigned* status) {
-    BPROF_START(2);
     extern __shared__ __align__(16) unsigned char s_raw[];
     double* s_P1 = reinterpret_cast<double*>(s_raw);                         // [rows][pitch]
     double* s_P2 = s_P1 + kSalRows * kRowPitch;
@@ -1122,7 +1075,6 @@ k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __res
         for (int r = 0; r < kSalRows; ++r) t += s_acc[tid * kSalRows + r];
         acc_add(&acc[tid], t, fx[0]);
     }
-    BPROF_PASS(2);
     if (!last_cta_done(&counters[1], gridDim.x)) return;
 
     if (tid < kSalCand) s_tot[tid] = (double)__ldcg(&acc[tid]) * fx[1];
@@ -1140,7 +1092,6 @@ k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __res
             trace[3] = gap;
         }
     }
-    BPROF_END(2);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1149,9 +1100,10 @@ k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __res
 // (binary.py:18-39 braq, 577-687 crbog, 1544-1638 crb)
 // ---------------------------------------------------------------------------------------
 // CRB v7 joint scale solve (binary.py:1582-1596), float32 like the reference.
+// `symdamp` damps the correlation whatever its sign (the crb_symdamp variants, binary.py:1584-1587).
 __device__ __forceinline__ void crb_solve(float c12, float c1w, float c2w, float d, float lam,
-                                          float corr_damp, float* a1, float* a2) {
-    if (c12 > 0.f) c12 = __fmul_rn(c12, __fsub_rn(1.0f, corr_damp));
+                                          float corr_damp, bool symdamp, float* a1, float* a2) {
+    if (symdamp || c12 > 0.f) c12 = __fmul_rn(c12, __fsub_rn(1.0f, corr_damp));
     const float A = __fadd_rn(d, lam);
     const float den = __fsub_rn(__fmul_rn(A, A), __fmul_rn(c12, c12));
     const bool ok = fabsf(den) > 1e-12f;
@@ -1256,7 +1208,11 @@ __device__ __forceinline__ void group_order2(const float (&w)[16], const bool (&
             }
         sc[0] = mu; sc[1] = al1; sc[2] = al2;
     } else {
-        // CRB v7, binary.py:1598-1636 (d_safe = max(count, 1), A = count + lam)
+        // CRB v7, binary.py:1598-1636 (d_safe = max(count, 1), A = count + lam); the *_norefine
+        // variants stop after the first joint solve (binary.py:1617), the *_symdamp ones damp the
+        // correlation symmetrically (dispatch binary.py:2883-2890)
+        const bool norefine = technique == CRB_TECH_CRB_NOREFINE || technique == CRB_TECH_CRB_SYMDAMP_NOREFINE;
+        const bool symdamp = technique == CRB_TECH_CRB_SYMDAMP || technique == CRB_TECH_CRB_SYMDAMP_NOREFINE;
         float t[16];
         auto centred_sign = [&](float (&B)[16]) {
             float ts = 0.f;
@@ -1282,17 +1238,19 @@ __device__ __forceinline__ void group_order2(const float (&w)[16], const bool (&
         for (int j = 0; j < 16; ++j) t[j] = in[j] ? (c[j] - a_init * B1[j]) : 0.f;
         centred_sign(B2);                                         // step 3
         float c1w = dot_c(B1), c2w = dot_c(B2), a1, a2;
-        crb_solve(dot_b(), c1w, c2w, d, lam, corr_damp, &a1, &a2);   // step 4
+        crb_solve(dot_b(), c1w, c2w, d, lam, corr_damp, symdamp, &a1, &a2);   // step 4
+        if (!norefine) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) t[j] = in[j] ? (c[j] - a1 * B1[j]) : 0.f;
-        centred_sign(B2);                                         // step 5
-        c2w = dot_c(B2);
-        crb_solve(dot_b(), c1w, c2w, d, lam, corr_damp, &a1, &a2);
+            for (int j = 0; j < 16; ++j) t[j] = in[j] ? (c[j] - a1 * B1[j]) : 0.f;
+            centred_sign(B2);                                     // step 5
+            c2w = dot_c(B2);
+            crb_solve(dot_b(), c1w, c2w, d, lam, corr_damp, symdamp, &a1, &a2);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) t[j] = in[j] ? (c[j] - a2 * B2[j]) : 0.f;
-        centred_sign(B1);                                         // step 6
-        c1w = dot_c(B1);
-        crb_solve(dot_b(), c1w, c2w, d, lam, corr_damp, &a1, &a2);
+            for (int j = 0; j < 16; ++j) t[j] = in[j] ? (c[j] - a2 * B2[j]) : 0.f;
+            centred_sign(B1);                                     // step 6
+            c1w = dot_c(B1);
+            crb_solve(dot_b(), c1w, c2w, d, lam, corr_damp, symdamp, &a1, &a2);
+        }
         float rs = 0.f;                                           // step 7
 #pragma unroll
         for (int j = 0; j < 16; ++j)
@@ -1316,10 +1274,9 @@ __device__ __forceinline__ void group_order2(const float (&w)[16], const bool (&
 __global__ void __launch_bounds__(256)
 k_finalize(float* __restrict__ W, int R, int64_t ldw, int col0, const float* __restrict__ U,
            int64_t ldu, const unsigned char* __restrict__ rank, const int* __restrict__ sel,
-           const float* __restrict__ pvals, int technique, float lam, float corr_damp,
+           const float* __restrict__ pvals, int technique, int orders, float lam, float corr_damp,
            float* __restrict__ Err, int64_t ld_err, float* __restrict__ Losses,
            unsigned char* __restrict__ codes, int64_t ld_codes, float* __restrict__ scales) {
-    BPROF_START(7);
     __shared__ float s_d[kBlock];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = row_in_warp(lane), l = lane_in_row(lane);
@@ -1350,22 +1307,27 @@ k_finalize(float* __restrict__ W, int R, int64_t ldw, int col0, const float* __r
     int b1[16], b2[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) { q[j] = 0.f; b1[j] = 0; b2[j] = 0; }
+    // expansions per group (bigptq.py:246-247 hands orders[i] to the quantizer): decimal digits of
+    // `orders`, 112 = (low 1, mid 1, salient 2), the only combination whose scales fit `sc`
 #pragma unroll
-    for (int gi = 0; gi < 2; ++gi) {
+    for (int k = 0; k < 8; ++k) sc[k] = 0.f;
+#pragma unroll 1
+    for (int gi = 0; gi < 3; ++gi) {
+        const int order = (gi == 0) ? orders / 100 : ((gi == 1) ? (orders / 10) % 10 : orders % 10);
         bool in[16];
         int n = 0;
 #pragma unroll
         for (int j = 0; j < 16; ++j) { in[j] = grp[j] == gi; n += in[j]; }
         n = red8i(n);
-        group_order1(w, in, n, q, b1, &sc[2 * gi], &sc[2 * gi + 1]);
-    }
-    {
-        bool in[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) in[j] = grp[j] == 2;
-        float s2[4];
-        group_order2(w, in, isal, technique, lam, corr_damp, q, b1, b2, s2);
-        sc[4] = s2[0]; sc[5] = s2[1]; sc[6] = s2[2]; sc[7] = s2[3];
+        if (order == 1) {
+            float mu, al;
+            group_order1(w, in, n, q, b1, &mu, &al);
+            if (gi == 0) { sc[0] = mu; sc[1] = al; } else if (gi == 1) { sc[2] = mu; sc[3] = al; } else { sc[4] = mu; sc[5] = al; }
+        } else {
+            float s2[4];
+            group_order2(w, in, n, technique, lam, corr_damp, q, b1, b2, s2);
+            if (gi == 2) { sc[4] = s2[0]; sc[5] = s2[1]; sc[6] = s2[2]; sc[7] = s2[3]; }
+        }
     }
 
     // ---- column epilogue (bigptq.py:249-263) ----
@@ -1399,7 +1361,6 @@ k_finalize(float* __restrict__ W, int R, int64_t ldw, int col0, const float* __r
 #pragma unroll
         for (int k = 0; k < 8; ++k) scales[(int64_t)row * 8 + k] = sc[k];
     }
-    BPROF_PASS(7);
 }
 
 // Stand-alone group binarizer on a [R, 128] block with an arbitrary element mask:
@@ -1446,26 +1407,22 @@ static int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 size_t block_workspace_bytes(int R) { return carve_block_ws(nullptr, R, nullptr); }
 
-#ifdef CRB_BLOCK_PROFILE
-extern "C" void crb_block_profile_read(unsigned long long* out32, int reset) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out32, g_bprof, sizeof(unsigned long long) * 32);
-    cudaMemcpyFromSymbol(out32 + 32, g_bmark, sizeof(unsigned long long) * 64);
-    if (reset) {
-        unsigned long long z[32];
-        for (int k = 0; k < 32; ++k) z[k] = (k % 4 == 0) ? ~0ull : 0ull;
-        cudaMemcpyToSymbol(g_bprof, z, sizeof(z));
-    }
+// `orders`: expansions of the low / mid / salient group as decimal digits (112 = the reference's
+// default orders=(1, 1, 2), bigptq.py:56); each digit 1 or 2.
+bool orders_valid(int orders) {
+    const int a = orders / 100, b = orders / 10 % 10, c = orders % 10;
+    return orders > 0 && orders < 1000 && (a == 1 || a == 2) && (b == 1 || b == 2) && (c == 1 || c == 2);
 }
-#endif
 
 int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu, int block,
-                      int technique, float lam, float corr_damp, int metric, float* Err, int64_t ld_err,
+                      int technique, int orders, float lam, float corr_damp, int metric, float* Err, int64_t ld_err,
                       float* Losses, unsigned char* codes, int64_t ld_codes, float* scales,
                       double* trace, void* workspace, size_t workspace_bytes, cudaStream_t st, bool reset_tickets) {
     if (!W || !U || !Err || !Losses || !workspace || R <= 0 || block < 0) return CRB_ERR_BAD_ARG;
     if (ld_err < kBlock || (ld_err & 3)) return CRB_ERR_BAD_ARG;
-    if (technique < CRB_TECH_BRAQ || technique > CRB_TECH_CRB) return CRB_ERR_BAD_ARG;
+    if (technique < CRB_TECH_BRAQ || technique > CRB_TECH_CRB_SYMDAMP_NOREFINE) return CRB_ERR_BAD_ARG;
+    if (!orders_valid(orders)) return CRB_ERR_BAD_ARG;
+    if (orders != CRB_ORDERS_DEFAULT && scales) return CRB_ERR_UNSUPPORTED;   // the 8 scale slots hold (1, 1, 2) only
     if (metric != CRB_METRIC_HESSIAN) return CRB_ERR_UNSUPPORTED;
     if ((ldw & 3) || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(Err) & 15))
         return CRB_ERR_BAD_ARG;
@@ -1476,16 +1433,17 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
     double* tr = trace ? trace : ws.trace_dummy;
     const int col0 = block * kBlock;
 
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceSetup once;
+    int rc_setup = once.run([] {
         if (cudaFuncSetAttribute(k_select_l1, cudaFuncAttributeMaxDynamicSharedMemorySize, kL1Smem) != cudaSuccess ||
             cudaFuncSetAttribute(k_split_search_sorted, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kSplitSmem) != cudaSuccess ||
             cudaFuncSetAttribute(k_salient_search_sorted, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kSalSmem) != cudaSuccess)
-            return CRB_ERR_LAUNCH;
-        attr_set = true;
-    }
+            return (int)CRB_ERR_LAUNCH;
+        return (int)CRB_OK;
+    });
+    if (rc_setup != CRB_OK) return rc_setup;
     // the last-CTA tickets reset themselves; a caller that cannot vouch for them (first use of a
     // workspace, stand-alone calls) asks for a reset
     if (reset_tickets && cudaMemsetAsync(ws.counters, 0, 64, st) != cudaSuccess) return CRB_ERR_LAUNCH;
@@ -1521,7 +1479,7 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
     CRB_LAUNCHED();
     // K7
     k_finalize<<<ceil_div(R, 32), 256, 0, st>>>(W, R, ldw, col0, U, ldu, ws.rank, ws.sel, ws.pvals, technique,
-                                               lam, corr_damp, Err, ld_err, Losses, codes, ld_codes, scales);
+                                               orders, lam, corr_damp, Err, ld_err, Losses, codes, ld_codes, scales);
     CRB_LAUNCHED();
     return CRB_OK;
 }
@@ -1531,7 +1489,7 @@ int binarize_group_launch(const float* W, int R, int64_t ldw, const unsigned cha
                           cudaStream_t st) {
     if (!W || !mask || !Q || R <= 0) return CRB_ERR_BAD_ARG;
     if (order != 1 && order != 2) return CRB_ERR_UNSUPPORTED;
-    if (technique < CRB_TECH_BRAQ || technique > CRB_TECH_CRB) return CRB_ERR_BAD_ARG;
+    if (technique < CRB_TECH_BRAQ || technique > CRB_TECH_CRB_SYMDAMP_NOREFINE) return CRB_ERR_BAD_ARG;
     if ((ldw & 3) || (ldq & 3) || (ldm & 3) || ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(Q)) & 15) ||
         (reinterpret_cast<uintptr_t>(mask) & 3))
         return CRB_ERR_BAD_ARG;

@@ -4,18 +4,50 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "../../include/crb_b200.h"
 
 namespace crb {
 
-// Host-side count of kernels launched by this library (crb_launch_count()).
-extern unsigned long long g_launches;
+// Host-side count of kernels launched by this library (crb_launch_count()); several host
+// threads may drive different streams at once.
+extern std::atomic<unsigned long long> g_launches;
 
 #define CRB_LAUNCHED()                                   \
     do {                                                 \
-        ++::crb::g_launches;                             \
+        ::crb::g_launches.fetch_add(1, std::memory_order_relaxed); \
         if (cudaGetLastError() != cudaSuccess) return CRB_ERR_LAUNCH; \
     } while (0)
+
+// Per-device one-time set-up.  Function attributes (the dynamic shared-memory limit of a kernel)
+// and device properties belong to a DEVICE, not to the process: a host that drives several GPUs
+// has to set them once on each.  `run(setup)` calls `setup()` (returning a crbStatus) the first
+// time it is reached with a given device current, under a mutex, and reports that device's
+// multiprocessor count.
+constexpr int kMaxDevices = 64;
+struct PerDeviceSetup {
+    std::mutex lock;
+    bool done[kMaxDevices] = {};
+    int sms[kMaxDevices] = {};
+    template <class F>
+    int run(F setup, int* sm_count = nullptr) {
+        int dev = -1;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return CRB_ERR_LAUNCH;
+        std::lock_guard<std::mutex> guard(lock);
+        if (!done[dev]) {
+            const int rc = setup();
+            if (rc != CRB_OK) return rc;
+            int n = 0;
+            if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+            sms[dev] = n;
+            done[dev] = true;
+        }
+        if (sm_count) *sm_count = sms[dev];
+        return CRB_OK;
+    }
+};
 
 constexpr int kBlock = CRB_BLOCK;            // 128 columns per block step
 constexpr int kSalLimit = CRB_SALIENT_LIMIT; // 50
@@ -86,8 +118,15 @@ __device__ __forceinline__ bool last_cta_done(unsigned* counter, unsigned total)
 constexpr int GEMM_LOWER_ONLY = 1;   // write only the 128 x 128 blocks of C on or below the diagonal
 constexpr int GEMM_B_LOWER = 2;      // the [K, N] operand B is lower triangular (zero for k < n)
 constexpr int GEMM_A_LOWER = 4;      // the [M, K] operand A is lower triangular (zero for k > m)
+// `selftest` (normally NULL) shortens the barrier waits and can make the producer warp withhold
+// its loads, so that a wait runs out on purpose: the kernel must then raise CRB_FLAG_WAIT_LIMIT,
+// drain and return (crb_selftest_wait_limit).
+struct GemmSelfTest {
+    unsigned long long wait_ns;
+    int withhold_loads;
+};
 int gemm_tf32x3(bool b_is_nk, int shape, int M, int N, int K, float alpha, const float* A, int64_t lda,
                 const float* B, int64_t ldb, float beta, float* C, int64_t ldc, unsigned* status,
-                cudaStream_t st);
+                cudaStream_t st, const GemmSelfTest* selftest = nullptr);
 
 }  // namespace crb

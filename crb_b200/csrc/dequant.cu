@@ -63,7 +63,7 @@ int dequantize_launch(float* W, int R, int C, int64_t ldw, int technique, const 
                       const long long* b2_off, const int* b2_pitch, const float* scales, cudaStream_t st) {
     if (!W || !b1 || !lm || !salcol || !b2 || !b2_off || !b2_pitch || !scales || R <= 0 || C <= 0) return CRB_ERR_BAD_ARG;
     if (C % kBlock) return CRB_ERR_UNSUPPORTED;
-    if (technique < CRB_TECH_BRAQ || technique > CRB_TECH_CRB) return CRB_ERR_BAD_ARG;
+    if (technique < CRB_TECH_BRAQ || technique > CRB_TECH_CRB_SYMDAMP_NOREFINE) return CRB_ERR_BAD_ARG;
     if ((ldw & 3) || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(scales) & 15) ||
         (reinterpret_cast<uintptr_t>(salcol) & 3))
         return CRB_ERR_BAD_ARG;

@@ -21,20 +21,7 @@
 namespace crb {
 
 constexpr int FB = 128;    // panel width
-constexpr int kOuterDefault = 8;  // diagonal blocks per outer panel of the factorisation
-
-// CRB_FACTOR_OUTER overrides the outer panel width (in 128-column blocks) for experiments.
-static int outer_blocks() {
-    static int v = 0;
-    if (!v) {
-        v = kOuterDefault;
-        if (const char* e = getenv("CRB_FACTOR_OUTER")) {
-            const int x = atoi(e);
-            if (x >= 1 && x <= 64) v = x;
-        }
-    }
-    return v;
-}
+constexpr int kOuter = 8;  // diagonal blocks per outer panel of the factorisation
 
 // diag statistics: dead columns, mean of the diagonal after the dead fix, total damping.
 __global__ void __launch_bounds__(1024)
@@ -340,17 +327,16 @@ int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
     CRB_LAUNCHED();
     const int nb = C / FB;
     constexpr int kDiagSmem = kDiagSmemFloats * (int)sizeof(float);
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(k_chol_diag, cudaFuncAttributeMaxDynamicSharedMemorySize, kDiagSmem) != cudaSuccess)
-            return CRB_ERR_LAUNCH;
-        attr_set = true;
-    }
+    static PerDeviceSetup once;
+    const int rc_setup = once.run([] {
+        return cudaFuncSetAttribute(k_chol_diag, cudaFuncAttributeMaxDynamicSharedMemorySize, kDiagSmem) == cudaSuccess
+                   ? (int)CRB_OK : (int)CRB_ERR_LAUNCH;
+    });
+    if (rc_setup != CRB_OK) return rc_setup;
     // Two levels of blocking: inside an outer panel of kOuter diagonal blocks the rank-128 updates
     // touch the panel's own columns only; everything right of the panel gets one update with
     // K = 8 * 128 afterwards, which is compute bound instead of re-reading the whole trailing
     // matrix once per diagonal block.
-    const int kOuter = outer_blocks();
     for (int k0 = 0; k0 < nb; k0 += kOuter) {
         const int k1 = k0 + kOuter < nb ? k0 + kOuter : nb;
         for (int k = k0; k < k1; ++k) {

@@ -14,15 +14,15 @@
 // panel / rank-128 / inverse-merge products of the blocked factorisation.
 //
 // One persistent CTA per SM over 128 x 256 output tiles, four warpgroups: warp 0 TMA producer
-// (float32 tiles, 128-byte swizzle), warp 1 MMA issuer (owns TMEM), warps 4-7 split the
-// landed tiles into hi / lo in place, warps 8-15 epilogue.  Two shared-memory stages of K = 32,
-// two 256-column TMEM accumulators.
+// (float32 tiles, 64-byte swizzle), warp 1 MMA issuer (owns TMEM), warps 4-7 write the lo plane
+// of the landed tiles, warps 8-15 epilogue.  Four shared-memory stages of K = 16, two 256-column
+// TMEM accumulators.
 //
 // The tensor core truncates (rounds toward zero) every time it adds to its float32 accumulator,
 // a bias that grows with the length of the chain (measured on a 4096 x 4096 factorisation with
 // condition number 6e4: chains of K = 1024 gave a factor 7 x less accurate than the float32
 // library chain, K = 128 chains 5 x its error on the diagonal, K = 32 chains parity).  The MMAs
-// therefore accumulate one shared-memory stage (K = 32, 12 instructions) in TMEM; the epilogue
+// therefore accumulate two shared-memory stages (K = 32, 12 instructions) in TMEM; the epilogue
 // warps fold every such chunk into float32 REGISTER accumulators with round-to-nearest adds while
 // the next chunk runs in the other TMEM buffer, and write C once per tile.  The epilogue warpgroups hold 128 accumulator registers per
 // thread; setmaxnreg moves registers to them from the producer / splitter warpgroups.
@@ -35,12 +35,9 @@
 
 namespace crb {
 
-#ifndef CRB_GEMM_STAGE_K
-#define CRB_GEMM_STAGE_K 16
-#endif
 // K per shared-memory stage: 32 (128-byte rows, 2 stages) or 16 (64-byte rows, 4 stages: the
 // deeper ring hides the TMA latency between "MMAs retired" and "next tile split").
-constexpr int GT_M = 128, GT_N = 256, GT_K = CRB_GEMM_STAGE_K;
+constexpr int GT_M = 128, GT_N = 256, GT_K = 16;
 static_assert(GT_K == 32 || GT_K == 16, "stage depth");
 constexpr int GT_STAGES = GT_K == 32 ? 2 : 4;
 constexpr int GT_A_BYTES = GT_M * GT_K * 4;                 // 16 / 8 KiB
@@ -51,10 +48,7 @@ constexpr int GT_BOX_BYTES = 32 * GT_K * 4;                 // MN-major B: one b
 constexpr int GT_EPI_BYTES = 8 * 32 * 33 * 4;                 // per-warp transpose patches of the epilogue
 constexpr int GT_SMEM = GT_STAGES * GT_STAGE_BYTES + 256 + GT_EPI_BYTES + 1024;
 constexpr int GT_THREADS = 512;              // warpgroups: TMA + MMA (+ 2 idle warps), 4 splitter warps, 2 x 4 epilogue warps
-#ifndef CRB_GEMM_CHUNK_STEPS
-#define CRB_GEMM_CHUNK_STEPS (32 / CRB_GEMM_STAGE_K)
-#endif
-constexpr int GT_CHUNK_STEPS = CRB_GEMM_CHUNK_STEPS;   // K steps (of 32) accumulated in TMEM before the fold into registers
+constexpr int GT_CHUNK_STEPS = 32 / GT_K;     // stages accumulated in TMEM (K = 32) before the fold into registers
 // registers per thread after the reallocation; the sum over the four warpgroups is 512 = 4 x 128
 constexpr int GT_REGS_IO = 56, GT_REGS_SPLIT = 72, GT_REGS_EPI = 192;
 static_assert(GT_REGS_IO + GT_REGS_SPLIT + 2 * GT_REGS_EPI <= 4 * 128, "register budget of a CTA");
@@ -71,6 +65,8 @@ struct GemmArgs {
                           // bit 1: A[m][k] = 0 for k > m (lower-triangular A): K ends with the tile's last row
     int m_tiles, n_tiles;
     unsigned* status;
+    unsigned long long wait_ns;   // limit of every barrier wait
+    int withhold_loads;   // self-test only: the producer issues nothing, so the first wait runs out
 };
 
 // K-major operand: rows of GT_K floats (128 bytes with the 128-byte swizzle, 64 bytes with the
@@ -109,20 +105,6 @@ __device__ __forceinline__ uint32_t tf32_idesc(int b_mn_major) {
     return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)b_mn_major << 16) |
            ((uint32_t)(GT_N >> 3) << 17) | ((uint32_t)(GT_M >> 4) << 24);
 }
-
-#ifdef CRB_GEMM_PROFILE
-// Wait-time accounting per warp role (development builds only): nanoseconds spent in each kind of
-// barrier wait, summed over CTAs.  0 producer/empty, 1 splitter/full, 2 mma/ready, 3 mma/tmem-empty,
-// 4 epilogue/tmem-full, 5 epilogue/total, 6 splitter/total, 7 mma/total, 8 producer/total.
-__device__ unsigned long long g_gemm_prof[16];
-#define PROF_DECL unsigned long long prof_t = 0, prof_t0 = global_ns();
-#define PROF_WAIT(expr) ([&]() { const unsigned long long a_ = global_ns(); const bool r_ = (expr); prof_t += global_ns() - a_; return r_; })()
-#define PROF_END(slot_wait, slot_total) do { atomicAdd(&g_gemm_prof[slot_wait], prof_t); atomicAdd(&g_gemm_prof[slot_total], global_ns() - prof_t0); } while (0)
-#else
-#define PROF_DECL
-#define PROF_WAIT(expr) (expr)
-#define PROF_END(a, b)
-#endif
 
 __device__ __forceinline__ bool tile_skipped(const GemmArgs& g, int mi, int nj) {
     return g.lower_only && (nj * GT_N > mi * GT_M + GT_M - 1);
@@ -173,14 +155,13 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         if (lane == 0) {
             uint32_t stage = 0, phase = 0, armed = 0, armed_phase = 0;
             bool ok = true;
-            PROF_DECL
-            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+            for (int t = blockIdx.x; t < total && ok && !g.withhold_loads; t += gridDim.x) {
                 const int mi = t / g.n_tiles, nj = t % g.n_tiles;
                 if (tile_skipped(g, mi, nj)) continue;
                 int ks0, ks1;
                 tile_k_range(g, mi, nj, &ks0, &ks1);
                 for (int ks = ks0; ks < ks1; ++ks) {
-                    ok = PROF_WAIT(mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag));
+                    ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, g.wait_ns);
                     if (!ok) break;
                     const uint32_t sa = smem_u32(smem + stage * GT_STAGE_BYTES);
                     const uint32_t sb = sa + GT_A_BYTES;
@@ -201,12 +182,11 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     if (++stage == GT_STAGES) { stage = 0; phase ^= 1; }
                 }
             }
-            PROF_END(0, 8);
             for (int s = 0; s < GT_STAGES; ++s) {          // drain copies in flight before smem goes away
                 if (!(armed >> s & 1u)) continue;
                 const unsigned long long t0 = global_ns();
                 while (!mbar_try_wait(full0 + 8 * s, (armed_phase >> s) & 1u))
-                    if (global_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; break; }
+                    if (global_ns() - t0 > g.wait_ns) { *abort_flag = 1; break; }
             }
         }
     } else if (warp == 1) {
@@ -215,10 +195,6 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             const uint32_t idesc = tf32_idesc(g.b_is_nk ? 0 : 1);
             uint32_t stage = 0, phase = 0, unit = 0;
             bool ok = true;
-            PROF_DECL
-#ifdef CRB_GEMM_PROFILE
-            unsigned long long prof_te = 0;
-#endif
             for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
                 const int mi = t / g.n_tiles, nj = t % g.n_tiles;
                 if (tile_skipped(g, mi, nj)) continue;
@@ -226,20 +202,14 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 tile_k_range(g, mi, nj, &ks0, &ks1);
                 for (int kc = ks0; kc < ks1 && ok; kc += GT_CHUNK_STEPS, ++unit) {
                     const uint32_t buf = unit & 1, use = unit >> 1;
-#ifdef CRB_GEMM_PROFILE
-                    const unsigned long long pa_ = global_ns();
-#endif
-                    ok = mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, abort_flag);
-#ifdef CRB_GEMM_PROFILE
-                    prof_te += global_ns() - pa_;
-#endif
+                    ok = mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, abort_flag, g.wait_ns);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + buf * GT_N;
                     const int kc1 = min(kc + GT_CHUNK_STEPS, ks1);
                     bool first = true;
                     for (int ks = kc; ks < kc1; ++ks) {
-                        ok = PROF_WAIT(mbar_wait(ready0 + 8 * stage, phase, abort_flag));
+                        ok = mbar_wait(ready0 + 8 * stage, phase, abort_flag, g.wait_ns);
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t a_hi = smem_u32(smem + stage * GT_STAGE_BYTES), b_hi = a_hi + GT_A_BYTES;
@@ -263,10 +233,6 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     if (ok) umma_commit(tfull0 + 8 * buf);
                 }
             }
-            PROF_END(2, 7);
-#ifdef CRB_GEMM_PROFILE
-            atomicAdd(&g_gemm_prof[3], prof_te);
-#endif
         }
     }   // warps 2 and 3 only fill the first warpgroup
     } else if (warp < 8) {
@@ -275,14 +241,13 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const int ctid = threadIdx.x - 128;                 // 0..127
         uint32_t stage = 0, phase = 0;
         bool ok = true;
-        PROF_DECL
         for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
             const int mi = t / g.n_tiles, nj = t % g.n_tiles;
             if (tile_skipped(g, mi, nj)) continue;
             int ks0, ks1;
             tile_k_range(g, mi, nj, &ks0, &ks1);
             for (int ks = ks0; ks < ks1; ++ks) {
-                ok = PROF_WAIT(mbar_wait(full0 + 8 * stage, phase, abort_flag));
+                ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, g.wait_ns);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 float4* hi = reinterpret_cast<float4*>(smem + stage * GT_STAGE_BYTES);
@@ -304,7 +269,6 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 if (++stage == GT_STAGES) { stage = 0; phase ^= 1; }
             }
         }
-        if (threadIdx.x == 128) { PROF_END(1, 6); }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(GT_REGS_EPI));
         // ---------------- epilogue: warps 8..15; warp w reads TMEM lanes 32 * (w % 4) .. +31 and the
@@ -313,7 +277,6 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const int c_begin = ((warp - 8) >> 2) * (GT_N / 2);
         uint32_t unit = 0;
         bool ok = true;
-        PROF_DECL
         for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
             const int mi = t / g.n_tiles, nj = t % g.n_tiles;
             if (tile_skipped(g, mi, nj)) continue;
@@ -327,7 +290,7 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 for (int j = 0; j < 32; ++j) acc[c][j] = 0.f;
             for (int kc = ks0; kc < ks1 && ok; kc += GT_CHUNK_STEPS, ++unit) {
                 const uint32_t buf = unit & 1, use = unit >> 1;
-                ok = PROF_WAIT(mbar_wait(tfull0 + 8 * buf, use & 1, abort_flag));
+                ok = mbar_wait(tfull0 + 8 * buf, use & 1, abort_flag, g.wait_ns);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
@@ -390,7 +353,6 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 __syncwarp();
             }
         }
-        if (warp == 8 && lane == 0) { PROF_END(4, 5); }
     }
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag && g.status) atomicOr(g.status, CRB_FLAG_WAIT_LIMIT);
@@ -408,7 +370,7 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
 // [M, K] operand A, whose zero part is then not multiplied.
 int gemm_tf32x3(bool b_is_nk, int shape, int M, int N, int K, float alpha, const float* A, int64_t lda,
                 const float* B, int64_t ldb, float beta, float* C, int64_t ldc, unsigned* status,
-                cudaStream_t st) {
+                cudaStream_t st, const GemmSelfTest* selftest) {
     if (M <= 0 || N <= 0) return CRB_OK;
     const bool lower_only = (shape & GEMM_LOWER_ONLY) != 0;
     if ((shape & GEMM_B_LOWER) && (b_is_nk || N > K)) return CRB_ERR_BAD_ARG;
@@ -444,40 +406,27 @@ int gemm_tf32x3(bool b_is_nk, int shape, int M, int N, int K, float alpha, const
     g.tri = ((shape & GEMM_B_LOWER) ? 1 : 0) | ((shape & GEMM_A_LOWER) ? 2 : 0);
     g.m_tiles = (M + GT_M - 1) / GT_M; g.n_tiles = (N + GT_N - 1) / GT_N;
     g.status = status;
-    static bool attr_set = false;
-    if (!attr_set) {
+    g.wait_ns = selftest ? selftest->wait_ns : kWaitLimitNs;
+    g.withhold_loads = selftest ? selftest->withhold_loads : 0;
+    static PerDeviceSetup once;
+    int sms = 148;
+    const int rc_setup = once.run([] {
         if (cudaFuncSetAttribute(k_gemm_tf32x3, cudaFuncAttributeMaxDynamicSharedMemorySize, GT_SMEM) != cudaSuccess)
-            return CRB_ERR_LAUNCH;
+            return (int)CRB_ERR_LAUNCH;
         // The register reallocation inside the kernel can only hand out what the CTA was launched
         // with: refuse to launch a build whose register file share is smaller than the plan needs
         // (an epilogue warpgroup would wait for registers that never become free).
         cudaFuncAttributes fa;
-        if (cudaFuncGetAttributes(&fa, k_gemm_tf32x3) != cudaSuccess) return CRB_ERR_LAUNCH;
-        if (fa.numRegs * GT_THREADS < (GT_REGS_IO + GT_REGS_SPLIT + 2 * GT_REGS_EPI) * 128) return CRB_ERR_UNSUPPORTED;
-        attr_set = true;
-    }
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms <= 0) sms = 148;
-    }
+        if (cudaFuncGetAttributes(&fa, k_gemm_tf32x3) != cudaSuccess) return (int)CRB_ERR_LAUNCH;
+        if (fa.numRegs * GT_THREADS < (GT_REGS_IO + GT_REGS_SPLIT + 2 * GT_REGS_EPI) * 128) return (int)CRB_ERR_UNSUPPORTED;
+        return (int)CRB_OK;
+    }, &sms);
+    if (rc_setup != CRB_OK) return rc_setup;
     const int total = g.m_tiles * g.n_tiles;
     k_gemm_tf32x3<<<total < sms ? total : sms, GT_THREADS, GT_SMEM, st>>>(map_a, map_b, g);
     CRB_LAUNCHED();
     return CRB_OK;
 }
 
-#ifdef CRB_GEMM_PROFILE
-extern "C" void crb_gemm_profile_read(unsigned long long* out16, int reset) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out16, g_gemm_prof, sizeof(unsigned long long) * 16);
-    if (reset) {
-        unsigned long long z[16] = {0};
-        cudaMemcpyToSymbol(g_gemm_prof, z, sizeof(z));
-    }
-}
-#endif
 
 }  // namespace crb

@@ -402,18 +402,8 @@ static int make_map(CUtensorMap* map, const void* base, int dtype, int64_t T, in
 static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 // Tokens accumulated on the tensor cores before the running sum is folded into S by float32
-// adds (multiple of the 64-token stage).  CRB_HESSIAN_CHUNK overrides it for experiments.
-static int hessian_chunk_tokens() {
-    static int v = 0;
-    if (!v) {
-        v = 2048;
-        if (const char* e = getenv("CRB_HESSIAN_CHUNK")) {
-            const int x = atoi(e);
-            if (x >= HT_K && x % HT_K == 0) v = x;
-        }
-    }
-    return v;
-}
+// adds (a multiple of the 64-token stage).
+constexpr int kHessianChunkTokens = 2048;
 
 size_t hessian_workspace_bytes(int C, int64_t T, int dtype) {
     size_t b = 256;                                           // amax + inv_scale2 + status
@@ -438,7 +428,7 @@ int hessian_accumulate_launch(const void* X, int dtype, int64_t T, int C, int64_
     CUtensorMap map0, map1;
     HessArgs a;
     a.S = S; a.status = status; a.C = C; a.T = T;
-    a.chunk_tokens = hessian_chunk_tokens();
+    a.chunk_tokens = kHessianChunkTokens;
     a.n_col_tiles = (C + H2_TILE - 1) / H2_TILE;
     a.n_tiles = a.n_col_tiles * (a.n_col_tiles + 1) / 2;
     if (dtype == CRB_F32) {
@@ -461,15 +451,13 @@ int hessian_accumulate_launch(const void* X, int dtype, int64_t T, int C, int64_
         map1 = map0;
         a.n_pass = 1; a.ab_format = (dtype == CRB_BF16) ? 1 : 0; a.inv_scale2 = nullptr;
     }
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(k_hessian_umma_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, H2_SMEM) != cudaSuccess)
-            return CRB_ERR_LAUNCH;
-        attr_set = true;
-    }
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    static PerDeviceSetup once;
+    int sms = 148;
+    const int rc_setup = once.run([] {
+        return cudaFuncSetAttribute(k_hessian_umma_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, H2_SMEM) == cudaSuccess
+                   ? (int)CRB_OK : (int)CRB_ERR_LAUNCH;
+    }, &sms);
+    if (rc_setup != CRB_OK) return rc_setup;
     // clusters of two CTAs over the 256 x 256 upper-triangle tiles
     const int pairs = a.n_tiles < sms / 2 ? a.n_tiles : sms / 2;
     cudaLaunchConfig_t cfg = {};

@@ -30,7 +30,7 @@ namespace crb {
 
 size_t block_workspace_bytes(int R);
 int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu, int block,
-                      int technique, float lam, float corr_damp, int metric, float* Err, int64_t ld_err,
+                      int technique, int orders, float lam, float corr_damp, int metric, float* Err, int64_t ld_err,
                       float* Losses, unsigned char* codes, int64_t ld_codes, float* scales,
                       double* trace, void* workspace, size_t workspace_bytes, cudaStream_t st, bool reset_tickets = true);
 
@@ -43,7 +43,6 @@ constexpr size_t kStaticScratchBytes = (size_t(1) << 20) + size_t(kStaticMaxRows
 // address: the address used at launch comes from cudaGetSymbolAddress below.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-constexpr int kMaxDevices = 64;
 static std::mutex g_setup_mutex;
 static void* g_scratch_addr[kMaxDevices] = {nullptr};
 
@@ -70,7 +69,7 @@ extern "C" {
 int crb_block_step_static_max_rows(void) { return kStaticMaxRows; }
 
 int crb_block_step_static(float* W, int R, int64_t ldw, const float* U, int64_t ldu, int block,
-                          int technique, float lam, float corr_damp, int metric, float* Err,
+                          int technique, int orders, float lam, float corr_damp, int metric, float* Err,
                           float* Losses, uint8_t* codes, float* scales, double* trace,
                           unsigned* flags_out, void* stream) {
     if (R <= 0) return CRB_ERR_BAD_ARG;
@@ -82,7 +81,7 @@ int crb_block_step_static(float* W, int R, int64_t ldw, const float* U, int64_t 
     // the status word is the first thing in the scratch; it must describe this call only
     if (cudaMemsetAsync(scratch, 0, 64, st) != cudaSuccess) return CRB_ERR_LAUNCH;
     uint8_t* codes_base = codes ? codes - (int64_t)block * kBlock : nullptr;   // codes is [R, 128]
-    rc = block_step_launch(W, R, ldw, U, ldu, block, technique, lam, corr_damp, metric, Err, kBlock, Losses,
+    rc = block_step_launch(W, R, ldw, U, ldu, block, technique, orders, lam, corr_damp, metric, Err, kBlock, Losses,
                            codes_base, kBlock, scales, trace, scratch, kStaticScratchBytes, st);
     if (rc != CRB_OK) return rc;
     if (flags_out &&

@@ -37,7 +37,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
@@ -45,7 +46,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         for (int it = 0; it < 256; ++it)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (global_ns() - t0 > kWaitLimitNs) break;
+        if (global_ns() - t0 > limit_ns) break;
     }
     *abort_flag = 1;
     return false;

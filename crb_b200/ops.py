@@ -47,8 +47,11 @@ def _dtype_code(t: torch.Tensor) -> int:
 
 
 # ------------------------------------------------------------------------------------------
-def hessian_accumulate(S: torch.Tensor, X: torch.Tensor) -> None:
-    """S += X^T X.  S [C, C] float32 (upper-triangle tiles are maintained), X [T, C]."""
+def hessian_accumulate(S: torch.Tensor, X: torch.Tensor) -> torch.Tensor:
+    """S += X^T X.  S [C, C] float32 (upper-triangle tiles are maintained), X [T, C].
+
+    Returns the workspace of the call; its first word collects the kernel's status flags
+    (CRB_FLAG_WAIT_LIMIT if a bounded wait ran out), see `read_status`."""
     _need_cuda(S, X)
     if X.dim() != 2 or S.shape != (X.shape[1], X.shape[1]) or S.dtype != torch.float32:
         raise CrbError("hessian_accumulate: X must be [T, C] and S [C, C] float32")
@@ -63,6 +66,7 @@ def hessian_accumulate(S: torch.Tensor, X: torch.Tensor) -> None:
     ws = _workspace("hessian", nbytes, S.device)
     check(L.crb_hessian_accumulate(ptr(X), code, T, Cc, X.stride(0), ptr(S), ptr(ws), ws.numel(),
                                    stream_ptr()), "crb_hessian_accumulate")
+    return ws
 
 
 def hessian_finalize(S: torch.Tensor, scale: float) -> None:
@@ -122,7 +126,7 @@ def hinv_upper_factor(H: torch.Tensor, W: Optional[torch.Tensor], percdamp: floa
     status = torch.zeros(4, dtype=torch.int32, device=H.device)
     saved = H.clone() if restore is None else None
     diag0 = torch.diagonal(H).clone()
-    for attempt in range(max_retries + 1):
+    for attempt in range(max_retries):          # extra damping steps 0 .. 9, like bigptq.py:115-123
         if attempt > 0:
             if restore is None:
                 H.copy_(saved)
@@ -130,15 +134,21 @@ def hinv_upper_factor(H: torch.Tensor, W: Optional[torch.Tensor], percdamp: floa
                 restore(H)
             status.zero_()
         factor_enqueue(H, W, percdamp, attempt, status)
-        if not (int(status[0].item()) & _lib.FLAG_BAD_PIVOT):
+        flags = int(status[0].item())
+        if flags & _lib.FLAG_WAIT_LIMIT:
+            raise CrbError("factorisation: a bounded wait inside a kernel ran out (CRB_FLAG_WAIT_LIMIT)")
+        if not (flags & _lib.FLAG_BAD_PIVOT):
             return H
     return diagonal_fallback(H, diag0, percdamp, max_retries)
 
 
 def block_step(W: torch.Tensor, U: torch.Tensor, block: int, technique: str = "crb",
                lam: float = 1e-5, corr_damp: float = 0.1, metric: str = "hessian",
-               losses: Optional[torch.Tensor] = None, want_codes: bool = True) -> dict:
-    """One 128-column block in place on W; returns Err, losses, codes, scales, trace."""
+               losses: Optional[torch.Tensor] = None, want_codes: bool = True,
+               orders=(1, 1, 2)) -> dict:
+    """One 128-column block in place on W; returns Err, losses, codes, scales, trace.
+
+    `scales` are produced for the default orders (1, 1, 2) only (None otherwise)."""
     _need_cuda(W, U)
     R = W.shape[0]
     L = lib()
@@ -147,11 +157,13 @@ def block_step(W: torch.Tensor, U: torch.Tensor, block: int, technique: str = "c
     Err = torch.empty(R, BLOCK, dtype=torch.float32, device=dev)
     if losses is None:
         losses = torch.zeros(R, dtype=torch.float32, device=dev)
+    ocode = _lib.orders_code(orders)
     codes = torch.zeros(R, BLOCK, dtype=torch.uint8, device=dev) if want_codes else None
-    scales = torch.zeros(R, 8, dtype=torch.float32, device=dev) if want_codes else None
+    scales = torch.zeros(R, 8, dtype=torch.float32, device=dev) \
+        if want_codes and ocode == _lib.ORDERS_DEFAULT else None
     trace = torch.zeros(TRACE_DOUBLES, dtype=torch.float64, device=dev)
     check(L.crb_block_step(ptr(W), R, W.stride(0), ptr(U), U.stride(0), block,
-                           _lib.TECHNIQUES[technique], lam, corr_damp, _lib.METRICS[metric],
+                           _lib.TECHNIQUES[technique], ocode, lam, corr_damp, _lib.METRICS[metric],
                            ptr(Err), ptr(losses), ptr(codes), ptr(scales), ptr(trace), ptr(ws),
                            ws.numel(), stream_ptr()), "crb_block_step")
     return dict(Err=Err, losses=losses, codes=codes, scales=scales, trace=trace, workspace=ws)
@@ -161,7 +173,7 @@ def block_step_static(W: torch.Tensor, U: torch.Tensor, block: int, technique: s
                       lam: float = 1e-5, corr_damp: float = 0.1, metric: str = "hessian", *,
                       Err: torch.Tensor, losses: torch.Tensor, codes: Optional[torch.Tensor] = None,
                       scales: Optional[torch.Tensor] = None, trace: Optional[torch.Tensor] = None,
-                      flags: Optional[torch.Tensor] = None) -> None:
+                      flags: Optional[torch.Tensor] = None, orders=(1, 1, 2)) -> None:
     """`block_step` for callers that may not allocate: every buffer, outputs included, is passed
     in, and the scratch memory is the library's built-in array (at most
     `crb_block_step_static_max_rows()` rows; calls on one device must not overlap)."""
@@ -172,7 +184,8 @@ def block_step_static(W: torch.Tensor, U: torch.Tensor, block: int, technique: s
     if R > limit:
         raise CrbError(f"block_step_static serves at most {limit} rows per call, got {R}")
     check(L.crb_block_step_static(ptr(W), R, W.stride(0), ptr(U), U.stride(0), block,
-                                  _lib.TECHNIQUES[technique], lam, corr_damp, _lib.METRICS[metric],
+                                  _lib.TECHNIQUES[technique], _lib.orders_code(orders), lam, corr_damp,
+                                  _lib.METRICS[metric],
                                   ptr(Err), ptr(losses), ptr(codes), ptr(scales), ptr(trace), ptr(flags),
                                   stream_ptr()), "crb_block_step_static")
 
@@ -217,7 +230,7 @@ def gemm_f32(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, alpha: float = 1
 
 def quantize_linear(W: torch.Tensor, U: torch.Tensor, technique: str = "crb", lam: float = 1e-5,
                     corr_damp: float = 0.1, metric: str = "hessian", want_codes: bool = False,
-                    want_trace: bool = True) -> dict:
+                    want_trace: bool = True, orders=(1, 1, 2)) -> dict:
     """The whole block loop of fasterquant on W [R, C] float32 in place, given U."""
     _need_cuda(W, U)
     R, Cc = W.shape
@@ -232,11 +245,14 @@ def quantize_linear(W: torch.Tensor, U: torch.Tensor, technique: str = "crb", la
     ws = _workspace("linear", L.crb_linear_workspace_bytes(R), dev)
     nblk = Cc // BLOCK
     losses = torch.zeros(R, dtype=torch.float32, device=dev)
+    ocode = _lib.orders_code(orders)
+    if want_codes and ocode != _lib.ORDERS_DEFAULT:
+        raise NotImplementedError("codes / scales (the packed form) exist for orders (1, 1, 2) only")
     codes = torch.zeros(R, Cc, dtype=torch.uint8, device=dev) if want_codes else None
     scales = torch.zeros(nblk, R, 8, dtype=torch.float32, device=dev) if want_codes else None
     trace = torch.zeros(nblk, TRACE_DOUBLES, dtype=torch.float64, device=dev) if want_trace else None
     check(L.crb_quantize_linear(ptr(W), R, Cc, W.stride(0), ptr(U), U.stride(0),
-                                _lib.TECHNIQUES[technique], lam, corr_damp, _lib.METRICS[metric],
+                                _lib.TECHNIQUES[technique], ocode, lam, corr_damp, _lib.METRICS[metric],
                                 ptr(losses), ptr(codes), ptr(scales), ptr(trace), ptr(ws), ws.numel(),
                                 stream_ptr()), "crb_quantize_linear")
     return dict(losses=losses, codes=codes, scales=scales, trace=trace, workspace=ws)
@@ -247,6 +263,16 @@ def read_status(workspace: torch.Tensor) -> int:
     if rc < 0:
         check(rc, "crb_read_status")
     return rc
+
+
+def selftest_wait_limit(device, limit_us: int = 1000) -> int:
+    """Makes a bounded wait of the tensor-core GEMM run out on purpose (its producer withholds the
+    loads) and returns the status flags the kernel left: CRB_FLAG_WAIT_LIMIT must be among them."""
+    scratch = torch.empty(256 * 1024, dtype=torch.uint8, device=device)
+    status = torch.zeros(4, dtype=torch.int32, device=device)
+    check(lib().crb_selftest_wait_limit(ptr(scratch), scratch.numel(), int(limit_us), ptr(status), stream_ptr()),
+          "crb_selftest_wait_limit")
+    return int(status[0].item())
 
 
 def launch_count() -> int:

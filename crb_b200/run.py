@@ -36,7 +36,7 @@ from .bigptq import BRAGPTQ
 from .binary import Binarization
 from .synth import build_synthetic_model, resolve_shape, synthetic_calibration
 
-TECHNIQUES = ("braq", "crbog", "crb")
+TECHNIQUES = ("braq", "crbog", "crb", "crb_norefine", "crb_symdamp", "crb_symdamp_norefine")
 
 
 def find_layers(module, layers=(nn.Conv2d, nn.Linear), name=""):
@@ -55,8 +55,8 @@ def default_args(**overrides) -> SimpleNamespace:
                         nsamples=128, seed=0, percdamp=0.01, blocksize=128, salient_metric="hessian",
                         partition=3, global_scale=False, disable_gptq=False, minlayer=-1, maxlayer=1000,
                         quant_only="", invert=False, corr_damp=0.1, lam=1e-5, coupling=0.5,
-                        device="cuda:0", seqlen=None, forward_batch=8, act_offload_gib=64.0, verbose=True,
-                        save_packed=None)
+                        device="cuda:0", seqlen=None, forward_batch=8, act_offload_gib=64.0, act_stage_gib=16.0,
+                        verbose=True, save_packed=None)
     for k, v in overrides.items():
         setattr(a, k, v)
     return a
@@ -189,41 +189,62 @@ class _Resident:
 class _Feeder:
     """Hands the layer its calibration batches.  Device-resident activations are sliced; activations
     kept in pinned host memory (the reference offloads them above 8 GiB, run.py:166-172) are
-    copied one batch ahead on a side stream into two device buffers, so that the copy of batch
-    j + 1 overlaps the layer forward of batch j."""
+    copied one batch ahead on a side stream, so that the copy of batch j + 1 overlaps the layer
+    forward of batch j.  When this rank's shard fits `keep_gib`, the copies land in a device buffer
+    that holds the whole shard and the re-propagation pass (`second_pass`) reads that buffer
+    instead of copying everything in again; larger shards go through two batch-sized buffers."""
 
     _buffers: Dict[tuple, list] = {}        # per shape: [device buffers, events "slot no longer read"]
 
-    def __init__(self, inps: torch.Tensor, fb: int, dev):
+    def __init__(self, inps: torch.Tensor, fb: int, dev, keep_gib: float = 0.0, _resident=None):
         self.inps, self.fb, self.dev = inps, fb, torch.device(dev)
         self.n = inps.shape[0]
         self.staged = inps.device.type == "cpu" and self.dev.type == "cuda"
+        self.whole = False
+        if _resident is not None:           # second pass over a shard that pass 1 left on the device
+            self.staged, self.whole = False, True
+            self.buf, self.free = _resident
+            self.main = torch.cuda.current_stream(self.dev)
+            return
         if not self.staged:
             return
-        key = (self.dev.index or 0, fb, tuple(inps.shape[1:]), inps.dtype)
+        nb = len(self)
+        nbytes = inps.numel() * inps.element_size()
+        self.whole = nbytes <= keep_gib * (1024 ** 3)
+        slots = nb if self.whole else 2
+        rows = self.n if self.whole else 2 * fb
+        key = (self.dev.index or 0, fb, rows, tuple(inps.shape[1:]), inps.dtype)
         if key not in _Feeder._buffers:
-            buf = torch.empty((2, fb) + tuple(inps.shape[1:]), dtype=inps.dtype, device=self.dev)
+            buf = torch.empty((rows,) + tuple(inps.shape[1:]), dtype=inps.dtype, device=self.dev)
             first = torch.cuda.Event()
             first.record(torch.cuda.current_stream(self.dev))       # the buffers exist from here on
-            _Feeder._buffers[key] = [buf, [first, first]]
+            _Feeder._buffers[key] = [buf, [first] * slots]
         self.buf, self.free = _Feeder._buffers[key]    # `free` is shared: the next feeder continues it
         self.h2d = _copy_streams(self.dev)[0]
         self.main = torch.cuda.current_stream(self.dev)
-        self.ready = [None, None]
+        self.ready = [None] * slots
         self._stage(0)
 
-    def _stage(self, idx):
+    def _slot(self, idx):
+        return idx if self.whole else idx & 1
+
+    def _rows(self, idx):
         j = idx * self.fb
+        m = min(self.fb, self.n - j)
+        first = j if self.whole else (idx & 1) * self.fb
+        return j, m, self.buf[first:first + m]
+
+    def _stage(self, idx):
+        j, m, dst = self._rows(idx)
         if j >= self.n:
             return
-        slot = idx & 1
+        slot = self._slot(idx)
         self.h2d.wait_event(self.free[slot])           # the slot's previous batch has been consumed
         written = _WRITTEN.get((self.inps.data_ptr(), j))
         if written is not None:
             self.h2d.wait_event(written)               # these rows were an output on its way to the host
         with torch.cuda.stream(self.h2d):
-            m = min(self.fb, self.n - j)
-            self.buf[slot, :m].copy_(self.inps[j:j + m], non_blocking=True)
+            dst.copy_(self.inps[j:j + m], non_blocking=True)
             self.ready[slot] = torch.cuda.Event()
             self.ready[slot].record(self.h2d)
 
@@ -232,19 +253,26 @@ class _Feeder:
 
     def batch(self, idx):
         """Batch `idx` on the device; call in increasing order, `done(idx)` after its last use."""
-        j = idx * self.fb
-        m = min(self.fb, self.n - j)
-        if not self.staged:
-            return self.inps[j:j + m].to(self.dev, non_blocking=True)
-        self._stage(idx + 1)
-        self.main.wait_event(self.ready[idx & 1])
-        return self.buf[idx & 1, :m]
+        if not self.staged and not self.whole:
+            j = idx * self.fb
+            return self.inps[j:j + min(self.fb, self.n - j)].to(self.dev, non_blocking=True)
+        view = self._rows(idx)[2]
+        if self.staged:
+            self._stage(idx + 1)
+            self.main.wait_event(self.ready[self._slot(idx)])
+        return view
 
     def done(self, idx):
-        if self.staged:
+        if self.staged or self.whole:
             ev = torch.cuda.Event()
             ev.record(self.main)
-            self.free[idx & 1] = ev
+            self.free[self._slot(idx)] = ev
+
+    def second_pass(self):
+        """The feeder of the re-propagation pass over the same rows."""
+        if self.staged and self.whole:
+            return _Feeder(self.inps, self.fb, self.dev, _resident=(self.buf, self.free))
+        return _Feeder(self.inps, self.fb, self.dev)
 
 
 # (host buffer address, first row) -> event "these rows have arrived in host memory"; a feeder that
@@ -423,7 +451,7 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
     n_local = inps.shape[0]
     fb = max(1, int(args.forward_batch))
     with timer.span("forward_hessian"):
-        feed = _Feeder(inps, fb, dev)
+        feed = _Feeder(inps, fb, dev, keep_gib=float(getattr(args, "act_stage_gib", 16.0)))
         for b in range(len(feed)):
             x = feed.batch(b)
             seen.clear()
@@ -439,7 +467,9 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
         seen.clear()
     for h in handles:
         h.remove()
-    feed2 = _Feeder(inps, fb, dev)            # the first batch of pass 2 travels while the linears are quantized
+    # pass 2 re-reads the shard pass 1 left on the device; a shard too large for that starts
+    # travelling again now, while the linears are quantized
+    feed2 = feed.second_pass()
     leaders = [n for n in gptq if n not in alias]
     with timer.span("hessian_allreduce"):
         if ws > 1:
@@ -625,7 +655,11 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--coupling", type=float, default=0.5)
     p.add_argument("--layers", type=int, default=None, help="synthetic models only: number of decoder layers")
     p.add_argument("--forward_batch", type=int, default=8, help="sequences per layer forward")
-    p.add_argument("--act_offload_gib", type=float, default=64.0)
+    p.add_argument("--act_offload_gib", type=float, default=64.0,
+                   help="activations of all sequences stay in pinned host memory above this size (run.py:166-172 uses 8)")
+    p.add_argument("--act_stage_gib", type=float, default=16.0,
+                   help="host-resident activations: a shard up to this size is copied in once per layer and kept "
+                        "on the device for both passes")
     p.add_argument("--save_packed", type=str, default=None,
                    help="directory that receives the packed form (bit planes + scales) of every binarized linear")
     p.add_argument("--quiet", action="store_true")

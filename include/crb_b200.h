@@ -29,7 +29,7 @@ extern "C" {
 #define CRB_BLOCK 128          /* columns per block step                       */
 #define CRB_SALIENT_LIMIT 50   /* utils/structure.py:16 (up_lim)               */
 #define CRB_N_SPLITS 81        /* utils/autosearch.py:65                       */
-#define CRB_TRACE_DOUBLES 192  /* doubles per block in the search trace        */
+#define CRB_TRACE_DOUBLES 272  /* doubles per block in the search trace        */
 
 typedef enum {
     CRB_OK = 0,
@@ -40,7 +40,19 @@ typedef enum {
     CRB_ERR_STATIC_LIMIT = -5  /* more rows than the built-in scratch can serve */
 } crbStatus;
 
-typedef enum { CRB_TECH_BRAQ = 0, CRB_TECH_CRBOG = 1, CRB_TECH_CRB = 2 } crbTechnique;
+/* Binarization.quantize dispatch (binary.py:2875-2890): braq, crbog, crb (v7) and the three flag
+ * variants of v7: no sign refinement (skip_refinement), symmetric correlation damping. */
+typedef enum {
+    CRB_TECH_BRAQ = 0,
+    CRB_TECH_CRBOG = 1,
+    CRB_TECH_CRB = 2,
+    CRB_TECH_CRB_NOREFINE = 3,
+    CRB_TECH_CRB_SYMDAMP = 4,
+    CRB_TECH_CRB_SYMDAMP_NOREFINE = 5
+} crbTechnique;
+/* `orders` arguments: expansions of the (low, mid, salient) groups as decimal digits, each 1 or 2;
+ * 112 is the reference's default orders=(1, 1, 2) (bigptq.py:56, :246-247). */
+#define CRB_ORDERS_DEFAULT 112
 typedef enum { CRB_METRIC_HESSIAN = 0, CRB_METRIC_MAGNITUDE = 1 } crbMetric;
 typedef enum { CRB_F32 = 0, CRB_F16 = 1, CRB_BF16 = 2 } crbDtype;
 
@@ -56,6 +68,7 @@ typedef enum { CRB_F32 = 0, CRB_F16 = 1, CRB_BF16 = 2 } crbDtype;
  *   [6..55]   the 50 highest-score columns, best first
  *   [56..104] mean squared error of salient candidates i = 1..49
  *   [105..185] mean squared error of split candidates k = 0..80
+ *   [186..266] the 81 split candidates (quantiles 0.10 .. 0.90 of the non-salient metric)
  */
 
 int crb_version(void);
@@ -95,11 +108,11 @@ int crb_hinv_upper_factor(float *H_dev, int C, float *W_dev, int R, int64_t ldw,
  *   Err   [R, 128]  out: (w - q) / d
  *   Losses[R]       in/out: += sum_j (w - q)^2 / d^2 / 2
  *   codes [R, 128]  optional (NULL): bits 0-1 B1+1, bits 2-3 B2+1, bits 4-5 group
- *   scales[R, 8]    optional (NULL): per-row scales, see the Python docs
- *   trace [192]     optional (NULL): doubles, layout above                       */
+ *   scales[R, 8]    optional (NULL): per-row scales, see the Python docs; only with orders 112
+ *   trace [272]     optional (NULL): doubles, layout above                       */
 size_t crb_block_workspace_bytes(int R);
 int crb_block_step(float *W_dev, int R, int64_t ldw, const float *U_dev, int64_t ldu, int block,
-                   int technique, float lam, float corr_damp, int metric, float *Err_dev,
+                   int technique, int orders, float lam, float corr_damp, int metric, float *Err_dev,
                    float *Losses_dev, uint8_t *codes_dev, float *scales_dev, double *trace_dev,
                    void *workspace_dev, size_t workspace_bytes, void *stream);
 
@@ -120,7 +133,7 @@ int crb_block_step(float *W_dev, int R, int64_t ldw, const float *U_dev, int64_t
 #define CRB_STATIC_MAX_ROWS 16384
 int crb_block_step_static_max_rows(void);
 int crb_block_step_static(float *W_dev, int R, int64_t ldw, const float *U_dev, int64_t ldu, int block,
-                          int technique, float lam, float corr_damp, int metric, float *Err_dev,
+                          int technique, int orders, float lam, float corr_damp, int metric, float *Err_dev,
                           float *Losses_dev, uint8_t *codes_dev, float *scales_dev, double *trace_dev,
                           unsigned *flags_out_dev, void *stream);
 
@@ -176,11 +189,11 @@ int crb_dequantize(float *W_dev, int R, int C, int64_t ldw, int technique, const
  * block step + trailing update, no host synchronisation.  The updates are grouped: a block's
  * error reaches the rest of its group of 8 blocks at once and the columns right of the group
  * in one product per group (same sums as bigptq.py:264, associated differently).  Buffers as above;
- * codes [R, C], scales [C/128, R, 8], trace [C/128, 192] are optional.
+ * codes [R, C], scales [C/128, R, 8], trace [C/128, 272] are optional.
  * Workspace: crb_linear_workspace_bytes(R).                                       */
 size_t crb_linear_workspace_bytes(int R);
 int crb_quantize_linear(float *W_dev, int R, int C, int64_t ldw, const float *U_dev, int64_t ldu,
-                        int technique, float lam, float corr_damp, int metric,
+                        int technique, int orders, float lam, float corr_damp, int metric,
                         float *Losses_dev, uint8_t *codes_dev, float *scales_dev,
                         double *trace_dev, void *workspace_dev, size_t workspace_bytes,
                         void *stream);
@@ -191,6 +204,18 @@ int crb_read_status(const void *workspace_dev, void *stream);
 
 /* Number of kernels this library has launched since load (for launch accounting). */
 unsigned long long crb_launch_count(void);
+
+/* ---- self-test of the bounded waits -----------------------------------------------
+ * Every wait inside the tensor-core kernels gives up after a time limit, raises
+ * CRB_FLAG_WAIT_LIMIT in the status word, drains its copies, frees its tensor memory and
+ * returns (the counterpart of the reference's only failure handling, the retry / fallback
+ * around torch.linalg.cholesky, bigptq.py:115-126, for a failure that cannot occur in eager
+ * PyTorch: a stalled producer).  This call exercises that path without faulting anything:
+ * it launches one GEMM tile whose producer warp withholds its loads and whose waits are
+ * limited to `limit_us` microseconds; afterwards *status_dev has CRB_FLAG_WAIT_LIMIT set and
+ * the context is intact.  scratch_dev: at least 256 KiB of device memory, 256-byte aligned. */
+int crb_selftest_wait_limit(void *scratch_dev, size_t scratch_bytes, unsigned limit_us,
+                            unsigned *status_dev, void *stream);
 
 #ifdef __cplusplus
 }

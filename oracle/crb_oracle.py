@@ -23,6 +23,9 @@ import numpy as np
 import torch
 
 TECHNIQUES = ("braq", "crbog", "crb")
+# the same v7 function with skip_refinement / symmetric_damp set (binary.py:2885-2890)
+CRB_VARIANTS = {"crb": (False, False), "crb_norefine": (True, False), "crb_symdamp": (False, True),
+                "crb_symdamp_norefine": (True, True)}
 SALIENT_LIMIT = 50          # utils/structure.py:16 passes up_lim=50 (bigptq.py:142)
 N_SPLITS = 81               # utils/autosearch.py:65
 
@@ -123,10 +126,13 @@ def braq_residual(x: torch.Tensor, mask: torch.Tensor, order: int,
     return total
 
 
-def _crb_solve(B1, B2, c1w, c2w, d, maskf, lam, corr_damp):
+def _crb_solve(B1, B2, c1w, c2w, d, maskf, lam, corr_damp, symmetric_damp=False):
     """Damped, Tikhonov-regularised 2x2 solve of CRB v7 (binary.py:1582-1596)."""
     c12 = (B1 * B2 * maskf).sum(dim=1)
-    c12 = torch.where(c12 > 0, c12 * (1.0 - corr_damp), c12)
+    if symmetric_damp:                                    # binary.py:1584-1585
+        c12 = c12 * (1.0 - corr_damp)
+    else:
+        c12 = torch.where(c12 > 0, c12 * (1.0 - corr_damp), c12)
     A = d + lam
     den = A * A - c12 * c12
     ok = den.abs() > 1e-12
@@ -138,7 +144,8 @@ def _crb_solve(B1, B2, c1w, c2w, d, maskf, lam, corr_damp):
 
 
 def crb_binarize(x: torch.Tensor, mask: torch.Tensor, order: int, lam: float = 1e-5,
-                 corr_damp: float = 0.1, parts: Optional[list] = None) -> torch.Tensor:
+                 corr_damp: float = 0.1, parts: Optional[list] = None, skip_refinement: bool = False,
+                 symmetric_damp: bool = False) -> torch.Tensor:
     """`coupled_residual_binarization_stable_v7` (binary.py:1544-1638).
 
     order 1: mean + alpha*sign (binary.py:1570-1576); order 2: two coupled
@@ -165,13 +172,14 @@ def crb_binarize(x: torch.Tensor, mask: torch.Tensor, order: int, lam: float = 1
     B2 = centred_sign((c - a_init[:, None] * B1) * mf)
     c1w = (c * B1).sum(dim=1)
     c2w = (c * B2).sum(dim=1)
-    a1, a2 = _crb_solve(B1, B2, c1w, c2w, d, mf, lam, corr_damp)
-    B2 = centred_sign((c - a1[:, None] * B1) * mf)                 # step 5
-    c2w = (c * B2).sum(dim=1)
-    a1, a2 = _crb_solve(B1, B2, c1w, c2w, d, mf, lam, corr_damp)
-    B1 = centred_sign((c - a2[:, None] * B2) * mf)                 # step 6
-    c1w = (c * B1).sum(dim=1)
-    a1, a2 = _crb_solve(B1, B2, c1w, c2w, d, mf, lam, corr_damp)
+    a1, a2 = _crb_solve(B1, B2, c1w, c2w, d, mf, lam, corr_damp, symmetric_damp)
+    if not skip_refinement:                                            # binary.py:1617
+        B2 = centred_sign((c - a1[:, None] * B1) * mf)                 # step 5
+        c2w = (c * B2).sum(dim=1)
+        a1, a2 = _crb_solve(B1, B2, c1w, c2w, d, mf, lam, corr_damp, symmetric_damp)
+        B1 = centred_sign((c - a2[:, None] * B2) * mf)                 # step 6
+        c1w = (c * B1).sum(dim=1)
+        a1, a2 = _crb_solve(B1, B2, c1w, c2w, d, mf, lam, corr_damp, symmetric_damp)
     approx = (a1[:, None] * B1 + a2[:, None] * B2) * mf            # step 7
     resid = (c - approx) * mf
     mu_fix = (resid * mf).sum(dim=1) / dsafe
@@ -239,8 +247,9 @@ def binarize(technique: str, x, mask, order, lam=1e-5, corr_damp=0.1, parts=None
         return braq_residual(x, mask, order, parts)
     if technique == "crbog":
         return crbog_binarize(x, mask, order, parts)
-    if technique == "crb":
-        return crb_binarize(x, mask, order, lam, corr_damp, parts)
+    if technique in CRB_VARIANTS:
+        skip, sym = CRB_VARIANTS[technique]
+        return crb_binarize(x, mask, order, lam, corr_damp, parts, skip, sym)
     raise NotImplementedError(technique)
 
 
@@ -407,15 +416,28 @@ def block_step(W_blk: torch.Tensor, u_diag: torch.Tensor, technique: str = "crb"
         Q += qg * mask
         s1 = torch.zeros(R, B)
         s2 = torch.zeros(R, B)
-        if g < 2 or order == 1:
+        if order == 1:
             mu, al, s = parts[0]
             scales[:, 2 * g], scales[:, 2 * g + 1] = mu, al
             s1 = s
+        elif g < 2:
+            # two expansions on the low / mid group (orders other than (1, 1, 2)): sign planes
+            # only, the 8 scale slots are laid out for the default orders
+            if technique == "braq":
+                s1, s2 = parts[0][2], parts[1][2]
+            elif technique in CRB_VARIANTS:
+                s1, s2 = parts[0][4], parts[0][5]
+            else:
+                b1_, b2_, cols_ = parts[0][3], parts[0][4], parts[0][5]
+                if cols_ is None:
+                    s1, s2 = b1_, b2_
+                else:
+                    s1[:, cols_], s2[:, cols_] = b1_, b2_
         elif technique == "braq":
             (mu1, al1, sa), (mu2, al2, sb) = parts
             scales[:, 4], scales[:, 5], scales[:, 6], scales[:, 7] = mu1, al1, mu2, al2
             s1, s2 = sa, sb
-        elif technique == "crb":
+        elif technique in CRB_VARIANTS:
             mu, mu_fix, a1, a2, b1, b2 = parts[0]
             scales[:, 4], scales[:, 5], scales[:, 6] = mu + mu_fix, a1, a2
             s1, s2 = b1, b2
@@ -445,7 +467,8 @@ class LinearResult:
 def quantize_linear(W: torch.Tensor, H: torch.Tensor, technique: str = "crb",
                     blocksize: int = 128, percdamp: float = 0.01, lam: float = 1e-5,
                     corr_damp: float = 0.1, metric: str = "hessian",
-                    keep_blocks: bool = True, U: Optional[torch.Tensor] = None) -> LinearResult:
+                    keep_blocks: bool = True, U: Optional[torch.Tensor] = None,
+                    orders: Sequence[int] = (1, 1, 2)) -> LinearResult:
     """`BRAGPTQ.fasterquant` for crb/crbog/braq with partition=3 (bigptq.py:56-291).
 
     W [R, C] float32 (cloned), H [C, C] float32 (consumed).  If `U` is given the
@@ -461,7 +484,7 @@ def quantize_linear(W: torch.Tensor, H: torch.Tensor, technique: str = "crb",
     for st in range(0, C, blocksize):
         ed = min(st + blocksize, C)
         blk = block_step(W[:, st:ed], torch.diag(U[st:ed, st:ed]), technique, lam,
-                         corr_damp, metric)
+                         corr_damp, metric, orders)
         W[:, st:ed] = blk.Q
         losses += blk.loss_rows / 2
         W[:, ed:] -= blk.Err.matmul(U[st:ed, ed:])

@@ -17,6 +17,10 @@ Outputs (numpy .npz, float32 unless noted):
   blocks.npz    single-block cases: metric search + the three binarizers
   linear.npz    a 96x256 linear: Hessian from 6 add_batch calls, fasterquant x 3 techniques
   config1.npz   (only with --config1) the 2048x2048 / 262144-token case, compact outputs
+  layers.npz    the reference's own layer loop (run.py quant_sequential) on a 2-layer random-init
+                OPT-shaped model: per-linear errors, quantized weights, final hidden states
+  variants.npz  group outputs of the crb_norefine / crb_symdamp / crb_symdamp_norefine quantizers
+                and of a linear run with orders other than (1, 1, 2)
 """
 from __future__ import annotations
 
@@ -172,7 +176,7 @@ def gen_linear(bigptq, binary, autosearch, out):
 
 
 def gen_config1(bigptq, binary, autosearch, out, keep_blocks=(0, 9)):
-    """BASELINE config 1: W 2048x2048 N(0,0.02^2); X 128x2048x2048 N(0,1), 1% channels x20; crb."""
+    """The single-linear workload: W 2048x2048 N(0,0.02^2); X 128x2048x2048 N(0,1), 1% channels x20; crb."""
     R = C = 2048
     nseq, seqlen = 128, 2048
     g = torch.Generator().manual_seed(1)
@@ -209,15 +213,142 @@ def gen_config1(bigptq, binary, autosearch, out, keep_blocks=(0, 9)):
     print("wrote", out, "error", err, "out_err", out_err)
 
 
+# ---------------------------------------------------------------- variants of the same kernels
+VARIANTS = ("crb_norefine", "crb_symdamp", "crb_symdamp_norefine")       # binary.py:2885-2890
+
+
+def run_reference_linear_orders(bigptq, binary, autosearch, W, H, nsamples, tech, orders):
+    R, C = W.shape
+    lin = nn.Linear(C, R, bias=False)
+    lin.weight.data = W.clone()
+    qz = binary.Binarization(lin.weight, method=tech, groupsize=128, corr_damp=0.1, lam=1e-5)
+    g = bigptq.BRAGPTQ(lin, qz, salient_metric="hessian")
+    g.H = H.clone()
+    g.nsamples = nsamples
+    with Capture(bigptq, autosearch) as cap, contextlib.redirect_stdout(io.StringIO()):
+        info = g.fasterquant(blocksize=128, percdamp=0.01, partition=3, orders=orders)
+    return lin.weight.data.clone(), info["error"], cap.blocks
+
+
+def gen_variants(bigptq, binary, autosearch, out):
+    """(a) the three flag variants of the v7 binarizer on the masks of two block cases, order 1 and 2,
+    plus an element-structured mask with empty rows; (b) whole-linear runs with `orders` other than
+    (1, 1, 2) (bigptq.py:246-247 passes orders[i] to the quantizer) and with a flag variant."""
+    data = {}
+    blocks = np.load(os.path.join(HERE, "blocks.npz"))
+    for ci in (0, 3):
+        W = torch.from_numpy(blocks[f"c{ci}_W"])
+        n = W.numel()
+        masks = [torch.from_numpy(np.unpackbits(blocks[f"c{ci}_{k}"])[:n].reshape(W.shape).astype(bool))
+                 for k in ("m1", "m2", "m3")]
+        ragged = masks[0].clone()
+        ragged[::7] = False
+        for tech in VARIANTS:
+            qz = binary.Binarization(W, method=tech, groupsize=128, corr_damp=0.1, lam=1e-5)
+            for g, m in enumerate(masks):
+                for order in (1, 2):
+                    data[f"c{ci}_{tech}_g{g}_o{order}"] = qz.quantize(W, m, order=order).numpy()
+            data[f"c{ci}_{tech}_ragged_o2"] = qz.quantize(W, ragged, order=2).numpy()
+    lin = np.load(os.path.join(HERE, "linear.npz"))
+    W, H, nseq = torch.from_numpy(lin["W"]), torch.from_numpy(lin["H"]), int(lin["nseq"])
+    for tech, orders in (("braq", (2, 2, 2)), ("crb", (2, 2, 2)), ("crb", (2, 1, 1)), ("crb_symdamp_norefine", (1, 1, 2))):
+        tag = f"{tech}_{''.join(map(str, orders))}"
+        Wq, err, blks = run_reference_linear_orders(bigptq, binary, autosearch, W, H, nseq, tech, orders)
+        data[f"{tag}_Wq"] = Wq.numpy()
+        data[f"{tag}_error"] = np.float64(err)
+        for bi, blk in enumerate(blks):
+            data[f"{tag}_b{bi}_errs"] = np.asarray(blk["errs"], dtype=np.float64)
+    np.savez_compressed(out, **data)
+    print("wrote", out)
+
+
+# ---------------------------------------------------------------- the reference's layer loop
+LAYER_CASES = {
+    # name: (synthetic shape, technique, float32 model?, nsamples, seqlen, percdamp)
+    "opt_f32_crb": ("opt-tiny", "crb", True, 16, 256, 0.01),
+    "opt_f16_braq": ("opt-tiny", "braq", False, 16, 256, 0.01),
+}
+
+
+def layer_case_inputs(case):
+    """Model and calibration batches of a LAYER_CASES entry (seeded, CPU generators)."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from crb_b200.synth import build_synthetic_model, synthetic_calibration
+    shape, tech, f32, nsamples, seqlen, percdamp = LAYER_CASES[case]
+    model = build_synthetic_model(shape, n_layers=2, seed=3, attn="eager")
+    if f32:
+        model = model.float()
+    model.seqlen = seqlen
+    loader = synthetic_calibration(model.config.vocab_size, nsamples=nsamples, seqlen=seqlen, seed=1)
+    return model, loader
+
+
+def gen_layers(reference_path, out):
+    """run.quant_sequential (run.py:122-387) as the reference runs it, on CPU, with the module
+    globals `args` / `groupsize` it reads set from outside.  Per-linear errors are recorded by
+    a subclass of BRAGPTQ bound to run.BRAGPTQ, the final hidden states by a forward hook on the
+    last decoder layer (the last `nsamples` calls are the re-propagation pass)."""
+    import run as refrun
+    from argparse import Namespace
+    data = {}
+    for case, (shape, tech, f32, nsamples, seqlen, percdamp) in LAYER_CASES.items():
+        model, loader = layer_case_inputs(case)
+        refrun.args = Namespace(model="facebook/" + shape, nsamples=nsamples, low_quant_method=tech, minlayer=-1,
+                                maxlayer=1000, quant_only="", invert=False, corr_damp=0.1, lam=1e-5, coupling=0.5,
+                                salient_metric="hessian", disable_gptq=False, percdamp=percdamp, blocksize=128,
+                                partition=3, global_scale=False)
+        refrun.groupsize = 128
+        errors = []
+        base = refrun.BRAGPTQ
+
+        class Recorder(base):
+            def fasterquant(self, *a, **k):
+                info = base.fasterquant(self, *a, **k)
+                errors.append(float(info["error"]))
+                return info
+
+        hidden = []
+        last = model.model.decoder.layers[-1]
+        handle = last.register_forward_hook(
+            lambda mod, inp, outp: hidden.append((outp[0] if isinstance(outp, (tuple, list)) else outp).detach().clone()))
+        refrun.BRAGPTQ = Recorder
+        try:
+            with contextlib.redirect_stdout(io.StringIO()):
+                refrun.quant_sequential(model, loader, "cpu")
+        finally:
+            refrun.BRAGPTQ = base
+            handle.remove()
+        final = torch.stack([h.reshape(seqlen, -1) for h in hidden[-nsamples:]])
+        data[f"{case}_errors"] = np.asarray(errors, dtype=np.float64)
+        data[f"{case}_hidden"] = final.float().numpy().astype(np.float32 if f32 else np.float16)
+        names = []
+        for li, layer in enumerate(model.model.decoder.layers):
+            for name, mod in refrun.find_layers(layer).items():
+                names.append(f"{li}.{name}")
+                data[f"{case}_w_{li}.{name}"] = mod.weight.data.float().numpy().astype(np.float32 if f32 else np.float16)
+        data[f"{case}_names"] = np.asarray(names)
+        print(case, "errors", errors)
+    np.savez_compressed(out, **data)
+    print("wrote", out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of an unmodified checkout of the reference project")
     ap.add_argument("--config1", action="store_true")
+    ap.add_argument("--only", default="", help="comma list of fixtures to (re)generate: blocks,linear,layers,variants")
     args = ap.parse_args()
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     mods = load_reference(args.reference)
-    gen_blocks(*mods, os.path.join(HERE, "blocks.npz"))
-    gen_linear(*mods, os.path.join(HERE, "linear.npz"))
+    only = set(filter(None, args.only.split(",")))
+    if not only or "blocks" in only:
+        gen_blocks(*mods, os.path.join(HERE, "blocks.npz"))
+    if not only or "linear" in only:
+        gen_linear(*mods, os.path.join(HERE, "linear.npz"))
+    if not only or "layers" in only:
+        gen_layers(args.reference, os.path.join(HERE, "layers.npz"))
+    if not only or "variants" in only:
+        gen_variants(*mods, os.path.join(HERE, "variants.npz"))
     if args.config1:
         gen_config1(*mods, os.path.join(HERE, "config1.npz"))
 

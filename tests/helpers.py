@@ -33,7 +33,8 @@ def trace_fields(trace: torch.Tensor) -> dict:
     t = trace.detach().cpu().double().numpy()
     return dict(n_salient=int(t[0]), split_index=int(t[1]), split_value=float(t[2]),
                 salient_gap=float(t[3]), split_gap=float(t[4]), e3=float(t[5]),
-                top_cols=t[6:56].astype(np.int64), salient_err=t[56:105], split_err=t[105:186])
+                top_cols=t[6:56].astype(np.int64), salient_err=t[56:105], split_err=t[105:186],
+                split_values=t[186:267].astype(np.float32))
 
 
 def gaps_of(errs: np.ndarray):
@@ -43,7 +44,7 @@ def gaps_of(errs: np.ndarray):
     return best, float((others.min() - errs[best]) / max(errs[best], 1e-300))
 
 
-def check_search_against_reference(tf: dict, ref_errs: np.ndarray, what: str = ""):
+def check_search_against_reference(tf: dict, ref_errs: np.ndarray, what: str = "", rtol: float = 2e-5):
     """Compares a device search trace with the reference's 130 candidate errors.
 
     Returns "exact" when both decisions agree, "tie" when a decision differs but the
@@ -56,13 +57,13 @@ def check_search_against_reference(tf: dict, ref_errs: np.ndarray, what: str = "
         gap = abs(ref_sal[tf["n_salient"] - 1] - ref_sal[ri]) / ref_sal[ri]
         assert gap <= TIE_GAP, f"{what}: salient count {tf['n_salient']} vs {ri + 1}, gap {gap:.3e}"
         return "tie"
-    np.testing.assert_allclose(tf["salient_err"], ref_sal, rtol=2e-5, err_msg=f"{what}: salient errors")
+    np.testing.assert_allclose(tf["salient_err"], ref_sal, rtol=rtol, err_msg=f"{what}: salient errors")
     rk, _ = gaps_of(ref_split)
     if tf["split_index"] != rk:
         gap = abs(ref_split[tf["split_index"]] - ref_split[rk]) / ref_split[rk]
         assert gap <= TIE_GAP, f"{what}: split index {tf['split_index']} vs {rk}, gap {gap:.3e}"
         outcome = "tie"
-    np.testing.assert_allclose(tf["split_err"], ref_split, rtol=2e-5, err_msg=f"{what}: split errors")
+    np.testing.assert_allclose(tf["split_err"], ref_split, rtol=rtol, err_msg=f"{what}: split errors")
     return outcome
 
 

@@ -1,12 +1,18 @@
-"""The layer loop on a GPU: overlapped linears (own streams, shared q/k/v factor) against
-one-at-a-time quantization of the same synthetic model."""
+"""The layer loop on a GPU: against the reference's own layer loop (golden outputs of its
+run.quant_sequential on the same seeded two-layer model), and overlapped linears (own streams,
+shared q/k/v factor) against one-at-a-time quantization of the same synthetic model."""
+import os
+
+import numpy as np
 import pytest
 import torch
+
+from tests import helpers as Hh
 
 pytestmark = pytest.mark.gpu
 
 
-def _run(concurrent: bool, arch: str, tech: str, offload: bool = False):
+def _run(concurrent: bool, arch: str, tech: str, offload: bool = False, stage_gib: float = 16.0):
     from crb_b200 import run as crun
     from crb_b200.synth import build_synthetic_model, synthetic_calibration
     model = build_synthetic_model(arch, n_layers=2, seed=3)
@@ -17,6 +23,7 @@ def _run(concurrent: bool, arch: str, tech: str, offload: bool = False):
     args.concurrent_linears = concurrent
     if offload:
         args.act_offload_gib = 0.0          # activations live in pinned host memory and stream through the device
+        args.act_stage_gib = stage_gib      # 0: two batch-sized buffers, every batch copied in for both passes
     out = crun.quant_sequential(model, loader, "cuda:0", args)
     layers, _ = crun._decoder_parts(model)
     weights = {f"{i}.{n}": m.weight.data.float().cpu().clone()
@@ -39,13 +46,53 @@ def test_overlapped_linears_equal_sequential(arch, tech):
     assert out_c["error_sum"] > 0
 
 
-def test_host_resident_activations_equal_device_resident():
-    """Activations offloaded to pinned host memory (prefetched batch by batch, written back on a side
-    stream) and weights streamed one layer ahead give the very same result."""
-    out_h, w_h = _run(True, "opt-tiny", "crb", offload=True)
+@pytest.mark.parametrize("stage_gib", (16.0, 0.0))
+def test_host_resident_activations_equal_device_resident(stage_gib):
+    """Activations offloaded to pinned host memory (prefetched batch by batch, kept on the device for
+    the second pass when the shard fits, written back on a side stream) and weights streamed one
+    layer ahead give the very same result."""
+    out_h, w_h = _run(True, "opt-tiny", "crb", offload=True, stage_gib=stage_gib)
     out_d, w_d = _run(True, "opt-tiny", "crb", offload=False)
     assert out_h["final_hidden"].device.type == "cpu" and out_d["final_hidden"].device.type == "cuda"
     for name in w_d:
         assert torch.equal(w_h[name], w_d[name]), name
     assert torch.equal(out_h["final_hidden"], out_d["final_hidden"].cpu())
     assert out_h["errors"] == out_d["errors"]
+
+
+@pytest.mark.parametrize("case,forward_batch", [("opt_f32_crb", 1), ("opt_f32_crb", 4), ("opt_f16_braq", 4)])
+def test_layer_loop_matches_reference_loop(golden_dir, case, forward_batch):
+    """crb_b200.run.quant_sequential against run.quant_sequential of the reference (run.py:122-387)
+    on a two-layer random-init OPT-shaped model: per-linear errors in the reference's order, every
+    quantized weight matrix and the hidden states that leave the last layer.  forward_batch 1 is the
+    reference's one-sequence-at-a-time schedule, 4 the batched one; q/k/v share one Hessian here."""
+    from crb_b200 import run as crun
+    from tests.golden.make_golden import LAYER_CASES, layer_case_inputs
+    ref = np.load(os.path.join(golden_dir, "layers.npz"))
+    shape, tech, f32, nsamples, seqlen, percdamp = LAYER_CASES[case]
+    model, loader = layer_case_inputs(case)
+    args = crun.default_args(low_quant_method=tech, nsamples=nsamples, forward_batch=forward_batch, verbose=False,
+                             device="cuda:0", percdamp=percdamp)
+    out = crun.quant_sequential(model, loader, "cuda:0", args)
+    layers, _ = crun._decoder_parts(model)
+    names = [str(n) for n in ref[f"{case}_names"]]
+    got_names = [f"{i}.{n}" for i, layer in enumerate(layers) for n in crun.find_layers(layer)]
+    assert got_names == names                      # same linears, visited in the same order
+    errs = [out["errors"][int(n.split(".", 1)[0])][n.split(".", 1)[1]] for n in names]
+    ref_errs = ref[f"{case}_errors"]
+    # float32 model: the two runs differ by rounding only, so a linear either reproduces the
+    # reference to rounding or contains a search tie; in both cases the contract's 0.5 % holds
+    # per linear.  The fp16 model adds half-precision forward differences between CPU and GPU.
+    tol = Hh.OUTPUT_ERR_RTOL if f32 else 4 * Hh.OUTPUT_ERR_RTOL
+    for n, e, r in zip(names, errs, ref_errs):
+        assert abs(e - r) <= tol * r, (n, e, r)
+    for n in names:
+        li, ln = n.split(".", 1)
+        w = crun.find_layers(layers[int(li)])[ln].weight.data.float().cpu()
+        w_ref = torch.from_numpy(ref[f"{case}_w_{n}"].astype(np.float32))
+        rel = float((w - w_ref).norm() / w_ref.norm())
+        assert rel < (0.02 if f32 else 0.06), (n, rel)
+    hidden = out["final_hidden"].float().cpu()
+    h_ref = torch.from_numpy(ref[f"{case}_hidden"].astype(np.float32))
+    rel = float((hidden - h_ref).norm() / h_ref.norm())
+    assert rel < (0.02 if f32 else 0.06), rel

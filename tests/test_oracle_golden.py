@@ -110,3 +110,38 @@ def test_codes_and_scales_rebuild_q(blocks):
             sal = s[:, 4:5] + s[:, 5:6] * b1 + s[:, 6:7] * b2
         rebuilt = torch.where(grp == 0, low, torch.where(grp == 1, mid, sal))
         assert torch.allclose(rebuilt, blk.Q, rtol=1e-5, atol=1e-8), tech
+
+
+@pytest.fixture(scope="module")
+def variants(golden_dir):
+    return np.load(os.path.join(golden_dir, "variants.npz"))
+
+
+@pytest.mark.parametrize("tech", ("crb_norefine", "crb_symdamp", "crb_symdamp_norefine"))
+@pytest.mark.parametrize("ci", (0, 3))
+def test_crb_flag_variants_match_reference(blocks, variants, ci, tech):
+    """skip_refinement / symmetric_damp of the v7 binarizer (binary.py:2885-2890)."""
+    W = torch.from_numpy(blocks[f"c{ci}_W"])
+    masks = [unpack(blocks[f"c{ci}_{n}"], W.shape) for n in ("m1", "m2", "m3")]
+    for g, m in enumerate(masks):
+        for order in (1, 2):
+            ref = torch.from_numpy(variants[f"c{ci}_{tech}_g{g}_o{order}"])
+            assert torch.equal(O.binarize(tech, W, m, order), ref), (tech, g, order)
+    ragged = masks[0].clone()
+    ragged[::7] = False
+    assert torch.equal(O.binarize(tech, W, ragged, 2), torch.from_numpy(variants[f"c{ci}_{tech}_ragged_o2"]))
+
+
+@pytest.mark.parametrize("tech,orders", [("braq", (2, 2, 2)), ("crb", (2, 2, 2)), ("crb", (2, 1, 1)),
+                                         ("crb_symdamp_norefine", (1, 1, 2))])
+def test_linear_with_other_orders_matches_reference(linear, variants, tech, orders):
+    """`orders` reaches the quantizer per group (bigptq.py:246-247); the searches do not depend on it."""
+    tag = f"{tech}_{''.join(map(str, orders))}"
+    W = torch.from_numpy(linear["W"])
+    H = torch.from_numpy(linear["H"]).clone()
+    res = O.quantize_linear(W, H, tech, orders=orders)
+    for bi, blk in enumerate(res.blocks):
+        got = np.asarray(blk.trace.salient_err + blk.trace.split_err)
+        assert np.array_equal(got, variants[f"{tag}_b{bi}_errs"]), bi
+    assert torch.equal(res.W, torch.from_numpy(variants[f"{tag}_Wq"]))
+    assert res.error == float(variants[f"{tag}_error"])

@@ -24,11 +24,12 @@ def _inputs(R, seed):
 
 
 def _static_call(ops, W, U, block, tech):
+    from crb_b200 import _lib
     R = W.shape[0]
     out = dict(Err=torch.empty(R, 128, device=DEV), losses=torch.zeros(R, device=DEV),
                codes=torch.zeros(R, 128, dtype=torch.uint8, device=DEV),
                scales=torch.zeros(R, 8, device=DEV),
-               trace=torch.zeros(192, dtype=torch.float64, device=DEV),
+               trace=torch.zeros(_lib.TRACE_DOUBLES, dtype=torch.float64, device=DEV),
                flags=torch.full((1,), 77, dtype=torch.int32, device=DEV))
     ops.block_step_static(W, U, block, tech, **out)
     return out
@@ -68,7 +69,7 @@ def test_static_block_step_refuses_too_many_rows():
     with pytest.raises(_lib.CrbError):
         ops.block_step_static(W, U, 0, "crb", Err=Err, losses=losses)
     rc = L.crb_block_step_static(ctypes.c_void_p(W.data_ptr()), R, W.stride(0), ctypes.c_void_p(U.data_ptr()),
-                                 U.stride(0), 0, 2, 1e-5, 0.1, 0, ctypes.c_void_p(Err.data_ptr()),
+                                 U.stride(0), 0, 2, 112, 1e-5, 0.1, 0, ctypes.c_void_p(Err.data_ptr()),
                                  ctypes.c_void_p(losses.data_ptr()), None, None, None, None,
                                  ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == -5
