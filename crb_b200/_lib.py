@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "_lib", "libcrb_b200.so")
 
 BLOCK = 128
-TRACE_DOUBLES = 272
+TRACE_DOUBLES = 320
 TECHNIQUES = {"braq": 0, "crbog": 1, "crb": 2, "crb_norefine": 3, "crb_symdamp": 4,
               "crb_symdamp_norefine": 5}
 ORDERS_DEFAULT = 112

@@ -236,7 +236,7 @@ k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
             r += (o > mine) || (o == mine && c < tid);
         }
         rank_out[tid] = (unsigned char)r;
-        if (r < kSalLimit) trace[6 + r] = (double)tid;
+        if (r < kSalLimit) { trace[6 + r] = (double)tid; trace[267 + r] = mine; }
     }
 }
 

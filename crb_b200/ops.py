@@ -145,23 +145,28 @@ def hinv_upper_factor(H: torch.Tensor, W: Optional[torch.Tensor], percdamp: floa
 def block_step(W: torch.Tensor, U: torch.Tensor, block: int, technique: str = "crb",
                lam: float = 1e-5, corr_damp: float = 0.1, metric: str = "hessian",
                losses: Optional[torch.Tensor] = None, want_codes: bool = True,
-               orders=(1, 1, 2)) -> dict:
+               orders=(1, 1, 2), reuse: Optional[dict] = None) -> dict:
     """One 128-column block in place on W; returns Err, losses, codes, scales, trace.
 
-    `scales` are produced for the default orders (1, 1, 2) only (None otherwise)."""
+    `scales` are produced for the default orders (1, 1, 2) only (None otherwise).  `reuse` takes the
+    dict an earlier call on the same shape returned: its buffers are written again instead of
+    allocating new ones (losses keep accumulating)."""
     _need_cuda(W, U)
     R = W.shape[0]
     L = lib()
     ws = _workspace("block", L.crb_block_workspace_bytes(R), W.device)
     dev = W.device
-    Err = torch.empty(R, BLOCK, dtype=torch.float32, device=dev)
-    if losses is None:
-        losses = torch.zeros(R, dtype=torch.float32, device=dev)
     ocode = _lib.orders_code(orders)
-    codes = torch.zeros(R, BLOCK, dtype=torch.uint8, device=dev) if want_codes else None
-    scales = torch.zeros(R, 8, dtype=torch.float32, device=dev) \
-        if want_codes and ocode == _lib.ORDERS_DEFAULT else None
-    trace = torch.zeros(TRACE_DOUBLES, dtype=torch.float64, device=dev)
+    if reuse is not None:
+        Err, losses, codes, scales, trace = (reuse[k] for k in ("Err", "losses", "codes", "scales", "trace"))
+    else:
+        Err = torch.empty(R, BLOCK, dtype=torch.float32, device=dev)
+        if losses is None:
+            losses = torch.zeros(R, dtype=torch.float32, device=dev)
+        codes = torch.zeros(R, BLOCK, dtype=torch.uint8, device=dev) if want_codes else None
+        scales = torch.zeros(R, 8, dtype=torch.float32, device=dev) \
+            if want_codes and ocode == _lib.ORDERS_DEFAULT else None
+        trace = torch.zeros(TRACE_DOUBLES, dtype=torch.float64, device=dev)
     check(L.crb_block_step(ptr(W), R, W.stride(0), ptr(U), U.stride(0), block,
                            _lib.TECHNIQUES[technique], ocode, lam, corr_damp, _lib.METRICS[metric],
                            ptr(Err), ptr(losses), ptr(codes), ptr(scales), ptr(trace), ptr(ws),

@@ -394,11 +394,13 @@ class _Timer:
 
 @torch.no_grad()
 def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch.Tensor,
-                   layer_kwargs: dict, args, dev, timer: Optional[_Timer] = None) -> Dict[str, float]:
+                   layer_kwargs: dict, args, dev, timer: Optional[_Timer] = None,
+                   traces: Optional[dict] = None) -> Dict[str, float]:
     """One iteration of the layer loop (run.py:236-385) for a layer already on `dev`.
 
     `inps` / `outs` hold this rank's sequences [n_local, seqlen, hidden] (device or pinned host).
     Returns the per-linear `error` values (only the owner rank's are non-zero before the sum).
+    `traces` (optional dict) receives the per-block search traces of the linears this rank owns.
     """
     timer = timer or _Timer()
     rank, ws = parallel.world()
@@ -525,6 +527,8 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
                 info = gptq[name].fasterquant(percdamp=args.percdamp, blocksize=args.blocksize,
                                               partition=args.partition, global_scale=args.global_scale)
             errors[name] = info["error"]
+            if traces is not None and gptq[name].last_trace is not None:
+                traces[name] = gptq[name].last_trace.cpu()
             if getattr(gptq[name], "packed", None) is not None:
                 from . import packed as _packed
                 os.makedirs(args.save_packed, exist_ok=True)
@@ -601,6 +605,7 @@ def quant_sequential(model, dataloader, dev, args=None) -> dict:
 
     timer = _Timer()
     all_errors: List[Dict[str, float]] = []
+    all_traces: List[Optional[dict]] = []
     t0 = time.time()
     # weights stream through the device: layer i + 1 is copied in and layer i - 1 copied out while
     # layer i is being quantized
@@ -611,7 +616,9 @@ def quant_sequential(model, dataloader, dev, args=None) -> dict:
         layer = res.__enter__()
         if i + 1 < len(layers):
             nxt = _Resident(layers[i + 1], dev).prefetch()
-        errs = quantize_layer(layer, i, inps, outs, layer_kwargs, args, dev, timer)
+        layer_traces = {} if getattr(args, "keep_traces", False) else None
+        errs = quantize_layer(layer, i, inps, outs, layer_kwargs, args, dev, timer, layer_traces)
+        all_traces.append(layer_traces)
         if leaving is not None:
             leaving.finish()
         res.__exit__(defer=True)
@@ -627,7 +634,8 @@ def quant_sequential(model, dataloader, dev, args=None) -> dict:
     model.config.use_cache = use_cache
     total = sum(sum(e.values()) for e in all_errors)
     total = parallel.sum_over_ranks(total, dev)
-    return {"errors": all_errors, "error_sum": total, "timing_ms": timing, "final_hidden": inps}
+    return {"errors": all_errors, "error_sum": total, "timing_ms": timing, "final_hidden": inps,
+            "traces": all_traces}
 
 
 # ---------------------------------------------------------------------------------------------

@@ -29,7 +29,7 @@ extern "C" {
 #define CRB_BLOCK 128          /* columns per block step                       */
 #define CRB_SALIENT_LIMIT 50   /* utils/structure.py:16 (up_lim)               */
 #define CRB_N_SPLITS 81        /* utils/autosearch.py:65                       */
-#define CRB_TRACE_DOUBLES 272  /* doubles per block in the search trace        */
+#define CRB_TRACE_DOUBLES 320  /* doubles per block in the search trace        */
 
 typedef enum {
     CRB_OK = 0,
@@ -69,6 +69,7 @@ typedef enum { CRB_F32 = 0, CRB_F16 = 1, CRB_BF16 = 2 } crbDtype;
  *   [56..104] mean squared error of salient candidates i = 1..49
  *   [105..185] mean squared error of split candidates k = 0..80
  *   [186..266] the 81 split candidates (quantiles 0.10 .. 0.90 of the non-salient metric)
+ *   [267..316] the column scores (sums of the metric over the rows) of the 50 columns in [6..55]
  */
 
 int crb_version(void);
@@ -109,7 +110,7 @@ int crb_hinv_upper_factor(float *H_dev, int C, float *W_dev, int R, int64_t ldw,
  *   Losses[R]       in/out: += sum_j (w - q)^2 / d^2 / 2
  *   codes [R, 128]  optional (NULL): bits 0-1 B1+1, bits 2-3 B2+1, bits 4-5 group
  *   scales[R, 8]    optional (NULL): per-row scales, see the Python docs; only with orders 112
- *   trace [272]     optional (NULL): doubles, layout above                       */
+ *   trace [320]     optional (NULL): doubles, layout above                       */
 size_t crb_block_workspace_bytes(int R);
 int crb_block_step(float *W_dev, int R, int64_t ldw, const float *U_dev, int64_t ldu, int block,
                    int technique, int orders, float lam, float corr_damp, int metric, float *Err_dev,
@@ -189,7 +190,7 @@ int crb_dequantize(float *W_dev, int R, int C, int64_t ldw, int technique, const
  * block step + trailing update, no host synchronisation.  The updates are grouped: a block's
  * error reaches the rest of its group of 8 blocks at once and the columns right of the group
  * in one product per group (same sums as bigptq.py:264, associated differently).  Buffers as above;
- * codes [R, C], scales [C/128, R, 8], trace [C/128, 272] are optional.
+ * codes [R, C], scales [C/128, R, 8], trace [C/128, 320] are optional.
  * Workspace: crb_linear_workspace_bytes(R).                                       */
 size_t crb_linear_workspace_bytes(int R);
 int crb_quantize_linear(float *W_dev, int R, int C, int64_t ldw, const float *U_dev, int64_t ldu,

@@ -298,13 +298,17 @@ def gen_layers(reference_path, out):
                                 salient_metric="hessian", disable_gptq=False, percdamp=percdamp, blocksize=128,
                                 partition=3, global_scale=False)
         refrun.groupsize = 128
-        errors = []
+        errors, block_errs = [], []
         base = refrun.BRAGPTQ
+        import bigptq as ref_bigptq
+        import utils.autosearch as ref_autosearch
 
         class Recorder(base):
             def fasterquant(self, *a, **k):
-                info = base.fasterquant(self, *a, **k)
+                with Capture(ref_bigptq, ref_autosearch) as cap:
+                    info = base.fasterquant(self, *a, **k)
                 errors.append(float(info["error"]))
+                block_errs.append([np.asarray(b["errs"], dtype=np.float64) for b in cap.blocks])
                 return info
 
         hidden = []
@@ -327,6 +331,8 @@ def gen_layers(reference_path, out):
                 names.append(f"{li}.{name}")
                 data[f"{case}_w_{li}.{name}"] = mod.weight.data.float().numpy().astype(np.float32 if f32 else np.float16)
         data[f"{case}_names"] = np.asarray(names)
+        for name, per_block in zip(names, block_errs):       # the 130 candidate errors of every block
+            data[f"{case}_errs_{name}"] = np.stack(per_block)
         print(case, "errors", errors)
     np.savez_compressed(out, **data)
     print("wrote", out)

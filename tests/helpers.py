@@ -34,7 +34,7 @@ def trace_fields(trace: torch.Tensor) -> dict:
     return dict(n_salient=int(t[0]), split_index=int(t[1]), split_value=float(t[2]),
                 salient_gap=float(t[3]), split_gap=float(t[4]), e3=float(t[5]),
                 top_cols=t[6:56].astype(np.int64), salient_err=t[56:105], split_err=t[105:186],
-                split_values=t[186:267].astype(np.float32))
+                split_values=t[186:267].astype(np.float32), top_scores=t[267:317])
 
 
 def gaps_of(errs: np.ndarray):
@@ -44,15 +44,32 @@ def gaps_of(errs: np.ndarray):
     return best, float((others.min() - errs[best]) / max(errs[best], 1e-300))
 
 
+# Column scores are sums of the metric over all rows; the reference adds them in float32
+# (utils/autosearch.py:37), so two columns whose scores agree to about 1e-6 may be ranked
+# either way by it.  Swapping the columns at positions c and c + 1 of the score order changes
+# exactly one salient candidate (the one that takes c + 1 columns).
+SCORE_TIE = 2e-6
+
+
+def score_tied_candidates(tf: dict) -> set:
+    """Salient candidates (0-based) whose column set hinges on a near tie of two column scores."""
+    s = np.asarray(tf["top_scores"], dtype=np.float64)
+    return {c for c in range(len(s) - 1) if abs(s[c] - s[c + 1]) <= SCORE_TIE * abs(s[c])}
+
+
 def check_search_against_reference(tf: dict, ref_errs: np.ndarray, what: str = "", rtol: float = 2e-5):
     """Compares a device search trace with the reference's 130 candidate errors.
 
     Returns "exact" when both decisions agree, "tie" when a decision differs but the
-    reference's own gap between the two candidates is below TIE_GAP; raises otherwise.
+    reference's own gap between the two candidates is below TIE_GAP, or when a salient candidate
+    differs only because two column scores are tied within SCORE_TIE; raises otherwise.
     """
     ref_sal, ref_split = np.asarray(ref_errs[:49], dtype=np.float64), np.asarray(ref_errs[49:], dtype=np.float64)
     outcome = "exact"
     ri, _ = gaps_of(ref_sal)
+    bad = np.nonzero(~np.isclose(tf["salient_err"], ref_sal, rtol=rtol, atol=0))[0]
+    if len(bad) and set(bad.tolist()) <= score_tied_candidates(tf):
+        return "tie"                                   # a different (equally scored) column order
     if tf["n_salient"] != ri + 1:
         gap = abs(ref_sal[tf["n_salient"] - 1] - ref_sal[ri]) / ref_sal[ri]
         assert gap <= TIE_GAP, f"{what}: salient count {tf['n_salient']} vs {ri + 1}, gap {gap:.3e}"

@@ -63,36 +63,56 @@ def test_host_resident_activations_equal_device_resident(stage_gib):
 @pytest.mark.parametrize("case,forward_batch", [("opt_f32_crb", 1), ("opt_f32_crb", 4), ("opt_f16_braq", 4)])
 def test_layer_loop_matches_reference_loop(golden_dir, case, forward_batch):
     """crb_b200.run.quant_sequential against run.quant_sequential of the reference (run.py:122-387)
-    on a two-layer random-init OPT-shaped model: per-linear errors in the reference's order, every
-    quantized weight matrix and the hidden states that leave the last layer.  forward_batch 1 is the
-    reference's one-sequence-at-a-time schedule, 4 the batched one; q/k/v share one Hessian here."""
+    on a two-layer random-init OPT-shaped model: the linears in the reference's order, per block
+    the 130 candidate errors and both decisions, per linear the error, the quantized weights, and
+    the hidden states that leave the last layer.  forward_batch 1 is the reference's
+    one-sequence-at-a-time schedule, 4 the batched one; q/k/v share one Hessian here.
+
+    The float32 model differs from the reference by rounding only: every block must follow the
+    reference (candidate errors to 2e-4) until a decision is a tie; from the first tie on the two
+    runs quantize different numbers and only loose bounds remain.  The fp16 model adds the
+    half-precision rounding differences between a CPU and a GPU forward, so only the loose bounds
+    apply to it."""
     from crb_b200 import run as crun
     from tests.golden.make_golden import LAYER_CASES, layer_case_inputs
     ref = np.load(os.path.join(golden_dir, "layers.npz"))
     shape, tech, f32, nsamples, seqlen, percdamp = LAYER_CASES[case]
     model, loader = layer_case_inputs(case)
     args = crun.default_args(low_quant_method=tech, nsamples=nsamples, forward_batch=forward_batch, verbose=False,
-                             device="cuda:0", percdamp=percdamp)
+                             device="cuda:0", percdamp=percdamp, keep_traces=True)
     out = crun.quant_sequential(model, loader, "cuda:0", args)
     layers, _ = crun._decoder_parts(model)
     names = [str(n) for n in ref[f"{case}_names"]]
     got_names = [f"{i}.{n}" for i, layer in enumerate(layers) for n in crun.find_layers(layer)]
     assert got_names == names                      # same linears, visited in the same order
-    errs = [out["errors"][int(n.split(".", 1)[0])][n.split(".", 1)[1]] for n in names]
     ref_errs = ref[f"{case}_errors"]
-    # float32 model: the two runs differ by rounding only, so a linear either reproduces the
-    # reference to rounding or contains a search tie; in both cases the contract's 0.5 % holds
-    # per linear.  The fp16 model adds half-precision forward differences between CPU and GPU.
-    tol = Hh.OUTPUT_ERR_RTOL if f32 else 4 * Hh.OUTPUT_ERR_RTOL
-    for n, e, r in zip(names, errs, ref_errs):
-        assert abs(e - r) <= tol * r, (n, e, r)
-    for n in names:
+    tight = f32                                    # until the first tie
+    report = []
+    for n, r in zip(names, ref_errs):
         li, ln = n.split(".", 1)
+        e = out["errors"][int(li)][ln]
+        trace = out["traces"][int(li)][ln]
+        blocks = ref[f"{case}_errs_{n}"]
+        assert trace.shape[0] == blocks.shape[0]
         w = crun.find_layers(layers[int(li)])[ln].weight.data.float().cpu()
         w_ref = torch.from_numpy(ref[f"{case}_w_{n}"].astype(np.float32))
-        rel = float((w - w_ref).norm() / w_ref.norm())
-        assert rel < (0.02 if f32 else 0.06), (n, rel)
+        rel_w = float((w - w_ref).norm() / w_ref.norm())
+        if tight:
+            for bi in range(blocks.shape[0]):
+                if Hh.check_search_against_reference(Hh.trace_fields(trace[bi]), blocks[bi], f"{n} block {bi}",
+                                                     rtol=2e-4) != "exact":
+                    tight = False
+                    report.append(f"first tie: {n} block {bi}")
+                    break
+        if tight:
+            assert abs(e - r) <= 1e-3 * r, (n, e, r)
+            assert rel_w < 1e-3, (n, rel_w)
+        else:
+            assert abs(e - r) <= 0.1 * r, (n, e, r)
+            assert rel_w < 0.2, (n, rel_w)
+        report.append(f"{n}: error {e:.4f} vs {r:.4f}, weights rel {rel_w:.2e}")
     hidden = out["final_hidden"].float().cpu()
     h_ref = torch.from_numpy(ref[f"{case}_hidden"].astype(np.float32))
     rel = float((hidden - h_ref).norm() / h_ref.norm())
-    assert rel < (0.02 if f32 else 0.06), rel
+    print(case, forward_batch, "hidden rel", rel, *report, sep="\n  ")
+    assert rel < (1e-3 if tight else 0.1), rel
