@@ -50,6 +50,7 @@ SIGNATURES = {
     "crb_dequantize": (_i, [_vp, _i, _i, _i64, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "crb_read_status": (_i, [_vp, _vp]),
     "crb_launch_count": (C.c_ulonglong, []),
+    "crb_set_dependent_launch": (_i, [_i]),
     "crb_selftest_wait_limit": (_i, [_vp, _sz, C.c_uint, _vp, _vp]),
 }
 

@@ -8,7 +8,7 @@ kernels of libcrb_b200.so:
 
 Only the path of the techniques braq / crbog / crb (and the crb_norefine / crb_symdamp /
 crb_symdamp_norefine variants of crb) is implemented: partition=3, orders with one or two
-expansions per group, blocksize 128, Hessian salience metric; anything else raises
+expansions per group, blocksize 128, salience metric hessian or magnitude; anything else raises
 NotImplementedError instead of silently taking another route.
 """
 from __future__ import annotations
@@ -130,8 +130,8 @@ class BRAGPTQ:
             raise NotImplementedError(f"only blocksize {BLOCK} is implemented")
         if self.disable_gptq:
             raise NotImplementedError("disable_gptq (RTN) is not implemented")
-        if self.salient_metric != "hessian":
-            raise NotImplementedError("only salient_metric='hessian' is implemented")
+        if self.salient_metric not in ("hessian", "magnitude"):          # utils/structure.py:9-14
+            raise NotImplementedError(f"salient_metric {self.salient_metric!r}: hessian and magnitude are implemented")
         assert self.braq_quantizer.groupsize % blocksize == 0       # bigptq.py:147
         if self.columns % BLOCK:
             raise NotImplementedError(f"in_features must be a multiple of {BLOCK}")

@@ -6,6 +6,7 @@
 namespace crb {
 
 std::atomic<unsigned long long> g_launches{0};
+std::atomic<int> g_dependent_launch{1};
 
 // block_step.cu
 size_t block_workspace_bytes(int R);
@@ -52,6 +53,10 @@ const char* crb_status_string(int status) {
         case CRB_ERR_STATIC_LIMIT: return "row count exceeds the built-in scratch of crb_block_step_static";
         default: return status > 0 ? "device status flags" : "unknown error";
     }
+}
+
+int crb_set_dependent_launch(int enable) {
+    return g_dependent_launch.exchange(enable ? 1 : 0);
 }
 
 unsigned long long crb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -131,7 +131,7 @@ static size_t carve_block_ws(void* base, int R, BlockWs* ws) {
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
-                  const float* __restrict__ U, int64_t ldu, int rows_per_cta,
+                  const float* __restrict__ U, int64_t ldu, int rows_per_cta, int metric,
                   float* __restrict__ M, double* __restrict__ colpart, double* __restrict__ energy,
                   double* __restrict__ fx, unsigned* counters, unsigned char* __restrict__ rank_out,
                   double* __restrict__ trace, unsigned* status, uint4* __restrict__ zero_ptr, int zero_vecs) {
@@ -141,6 +141,7 @@ k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
     __shared__ double s_score[kBlock];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = row_in_warp(lane), l = lane_in_row(lane);
+    chain_wait();
     // histograms and accumulators of the later kernels of this block step start at zero: cleared
     // here instead of by a separate memset node in front of every block
     for (int k = blockIdx.x * blockDim.x + tid; k < zero_vecs; k += gridDim.x * blockDim.x)
@@ -164,10 +165,11 @@ k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
             float e = 0.f;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                const float m = __fdiv_rn(__fmul_rn(x[j], x[j]), d2[j]);
+                // structure.py:10-12: w^2 / diag(U)^2 (hessian) or the weight itself (magnitude)
+                const float m = (metric == CRB_METRIC_HESSIAN) ? __fdiv_rn(__fmul_rn(x[j], x[j]), d2[j]) : x[j];
                 bad |= !isfinite(m);
                 x[j] = m;
-                csum[j] += m;          // M >= 0, so |M| = M (autosearch.py:37)
+                csum[j] += fabsf(m);   // column score = sum of |M| (autosearch.py:37)
                 e = fmaf(m, m, e);
             }
             e2 += (double)e;
@@ -316,8 +318,9 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
     __shared__ unsigned s_trank[kTargets];
     __shared__ bool s_sal[kBlock];
     const int tid = threadIdx.x;
-    const int isal = sel[0];
     for (int k = tid; k < kL1Bins + kL1Bins / 32; k += blockDim.x) s_hist[k] = 0u;
+    chain_wait();
+    const int isal = sel[0];
     if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
     __syncthreads();
     const size_t n4 = (size_t)R * (kBlock / 4);
@@ -460,6 +463,7 @@ k_select_l2(const float* __restrict__ M, int R, const unsigned char* __restrict_
     __shared__ unsigned s_bin2[kTargets], s_slot1[kTargets], s_rem[kTargets], s_slot2[kTargets];
     __shared__ unsigned s_l2start[kTargets + 1], s_l2bin[kTargets];
     const int tid = threadIdx.x;
+    chain_wait();
     const int isal = sel[0];
     if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
     __syncthreads();
@@ -536,6 +540,7 @@ k_select_l3(const float* __restrict__ M, int R, const unsigned char* __restrict_
     __shared__ bool s_sal[kBlock];
     __shared__ float s_val[kTargets];
     const int tid = threadIdx.x;
+    chain_wait();
     const int isal = sel[0];
     if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
     __syncthreads();
@@ -600,6 +605,13 @@ k_select_l3(const float* __restrict__ M, int R, const unsigned char* __restrict_
 // (bitonic network, one warp per row, four elements per lane; ties keep the lower column first).
 // The sorted rows turn the candidate evaluations of the split search into prefix-sum lookups.
 // ---------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned ordered_key(float v) {
+    const unsigned b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(unsigned k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
 __device__ __forceinline__ bool key_less(unsigned ka, int ca, unsigned kb, int cb) {
     return (ka < kb) || (ka == kb && ca < cb);
 }
@@ -608,14 +620,15 @@ __global__ void __launch_bounds__(256)
 k_sort_rows(const float* __restrict__ M, int R, float* __restrict__ sv, unsigned char* __restrict__ sc) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * 8 + warp;
+    chain_wait();
     if (row >= R) return;
     unsigned k[4];
     int c[4];
     {
         const float4 v = *reinterpret_cast<const float4*>(M + (int64_t)row * kBlock + 4 * lane);
-        // the metric is >= 0, so the bit pattern orders like the value (NaN sorts last)
-        k[0] = __float_as_uint(v.x) & 0x7fffffffu; k[1] = __float_as_uint(v.y) & 0x7fffffffu;
-        k[2] = __float_as_uint(v.z) & 0x7fffffffu; k[3] = __float_as_uint(v.w) & 0x7fffffffu;
+        // keys that order like the values, negative ones included (the magnitude metric is the
+        // signed weight): flip all bits of a negative number, the sign bit of the others
+        k[0] = ordered_key(v.x); k[1] = ordered_key(v.y); k[2] = ordered_key(v.z); k[3] = ordered_key(v.w);
 #pragma unroll
         for (int q = 0; q < 4; ++q) c[q] = 4 * lane + q;
     }
@@ -654,7 +667,7 @@ k_sort_rows(const float* __restrict__ M, int R, float* __restrict__ sv, unsigned
         }
     }
     *reinterpret_cast<float4*>(sv + (int64_t)row * kBlock + 4 * lane) =
-        make_float4(__uint_as_float(k[0]), __uint_as_float(k[1]), __uint_as_float(k[2]), __uint_as_float(k[3]));
+        make_float4(key_value(k[0]), key_value(k[1]), key_value(k[2]), key_value(k[3]));
     *reinterpret_cast<uchar4*>(sc + (int64_t)row * kBlock + 4 * lane) =
         make_uchar4((unsigned char)c[0], (unsigned char)c[1], (unsigned char)c[2], (unsigned char)c[3]);
 }
@@ -699,9 +712,38 @@ __device__ __forceinline__ double range_order1_err(const float* v, const double*
     return S2 - 2.0 * mu * S1 + (double)m * mu * mu - 2.0 * alpha * A + (double)m * alpha * alpha;
 }
 
+// The same for the union of two sorted ranges [a0, b0) and [a1, b1), a0 <= b0 <= a1 <= b1: with the
+// magnitude metric the values are signed and the "mid" side |x| >= p is the two tails of the row.
+__device__ __forceinline__ double two_range_order1_err(const float* v, const double* P1, const double* P2, int n,
+                                                       int a0, int b0, int a1, int b1) {
+    const int m = (b0 - a0) + (b1 - a1);
+    if (m <= 0) return 0.0;
+    const double S1 = (P1[b0] - P1[a0]) + (P1[b1] - P1[a1]);
+    const double S2 = (P2[b0] - P2[a0]) + (P2[b1] - P2[a1]);
+    const float mu_f = __fdiv_rn((float)S1, (float)m);
+    const double mu = (double)mu_f;
+    const int cm = lower_bound_f(v, 0, n, mu_f);                  // members below mu: the part of each range in front of cm
+    const int c0 = min(max(cm, a0), b0), c1 = min(max(cm, a1), b1);
+    const double below = (P1[c0] - P1[a0]) + (P1[c1] - P1[a1]);
+    const double nb = (double)((c0 - a0) + (c1 - a1));
+    const double A = mu * nb - below + (S1 - below) - mu * ((double)m - nb);
+    const double alpha = (double)__fdiv_rn((float)A, (float)m);
+    return S2 - 2.0 * mu * S1 + (double)m * mu * mu - 2.0 * alpha * A + (double)m * alpha * alpha;
+}
+
+// first index in [0, n) with v[idx] > t
+__device__ __forceinline__ int upper_bound_f(const float* v, int n, float t) {
+    int lo = 0, len = n;
+    while (len > 0) {
+        const int half = len >> 1;
+        if (!(v[lo + half] > t)) { lo += half + 1; len -= half + 1; } else { len = half; }
+    }
+    return lo;
+}
+
 __global__ void __launch_bounds__(256)
 k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restrict__ sc, int R,
-                      int rows_per_cta, const unsigned char* __restrict__ rank,
+                      int rows_per_cta, int metric, const unsigned char* __restrict__ rank,
                       const float* __restrict__ pvals_in, unsigned long long* __restrict__ acc,
                       const double* __restrict__ fx, unsigned* counters, int* __restrict__ sel,
                       float* __restrict__ pvals_out, double* __restrict__ trace, unsigned* status) {
@@ -714,11 +756,12 @@ k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restr
     __shared__ unsigned char s_rank[kBlock];
     __shared__ double s_tot[kSplits + 1];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int k = tid; k < (kSplits + 1) * kSplitRows; k += blockDim.x) s_acc[k] = 0.0;
+    chain_wait();
     const int isal = sel[0];
     const int n = kBlock - isal;                                             // non-salient values per row
     if (tid < kSplits) s_p[tid] = pvals_in[tid];
     if (tid < kBlock) s_rank[tid] = rank[tid];
-    for (int k = tid; k < (kSplits + 1) * kSplitRows; k += blockDim.x) s_acc[k] = 0.0;
     __syncthreads();
 
     const int row_base = blockIdx.x * rows_per_cta;
@@ -816,8 +859,16 @@ k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restr
             const float* v = s_v + r * kRowPitch;
             const double* P1 = s_P1 + r * kRowPitch;
             const double* P2 = s_P2 + r * kRowPitch;
-            const int c = lower_bound_f(v, 0, n, s_p[k]);                   // low side: x < p (mask.py:11-13)
-            const double e = range_order1_err(v, P1, P2, 0, c) + range_order1_err(v, P1, P2, c, n);
+            double e;
+            if (metric == CRB_METRIC_HESSIAN) {
+                const int c = lower_bound_f(v, 0, n, s_p[k]);               // low side: x < p (mask.py:11-13), x >= 0
+                e = range_order1_err(v, P1, P2, 0, c) + range_order1_err(v, P1, P2, c, n);
+            } else {
+                // signed values: low side |x| < p is the middle of the sorted row, mid side its two tails
+                const int b = lower_bound_f(v, 0, n, s_p[k]);
+                const int a = min(upper_bound_f(v, n, -s_p[k]), b);         // p = 0: nothing is below it
+                e = range_order1_err(v, P1, P2, a, b) + two_range_order1_err(v, P1, P2, n, 0, a, b, n);
+            }
             s_acc[k * kSplitRows + r] += e;
         }
         __syncthreads();
@@ -989,8 +1040,9 @@ k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __res
     __shared__ unsigned char s_rank[kBlock];
     __shared__ double s_tot[kSalCand];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid < kBlock) s_rank[tid] = rank[tid];
     for (int k = tid; k < kSalCand * kSalRows; k += blockDim.x) s_acc[k] = 0.0;
+    chain_wait();
+    if (tid < kBlock) s_rank[tid] = rank[tid];
     __syncthreads();
     const int row_base = blockIdx.x * rows_per_cta;
     for (int p0 = 0; p0 < rows_per_cta; p0 += kSalRows) {
@@ -1274,12 +1326,13 @@ __device__ __forceinline__ void group_order2(const float (&w)[16], const bool (&
 __global__ void __launch_bounds__(256)
 k_finalize(float* __restrict__ W, int R, int64_t ldw, int col0, const float* __restrict__ U,
            int64_t ldu, const unsigned char* __restrict__ rank, const int* __restrict__ sel,
-           const float* __restrict__ pvals, int technique, int orders, float lam, float corr_damp,
+           const float* __restrict__ pvals, int technique, int orders, int metric, float lam, float corr_damp,
            float* __restrict__ Err, int64_t ld_err, float* __restrict__ Losses,
            unsigned char* __restrict__ codes, int64_t ld_codes, float* __restrict__ scales) {
     __shared__ float s_d[kBlock];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = row_in_warp(lane), l = lane_in_row(lane);
+    chain_wait();
     if (tid < kBlock) s_d[tid] = U[(int64_t)(col0 + tid) * ldu + col0 + tid];
     __syncthreads();
     const int isal = sel[0];
@@ -1300,7 +1353,8 @@ k_finalize(float* __restrict__ W, int R, int64_t ldw, int col0, const float* __r
     int grp[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
-        const float m = __fdiv_rn(__fmul_rn(w[j], w[j]), __fmul_rn(dd[j], dd[j]));
+        const float m = (metric == CRB_METRIC_HESSIAN) ? __fdiv_rn(__fmul_rn(w[j], w[j]), __fmul_rn(dd[j], dd[j]))
+                                                       : fabsf(w[j]);
         grp[j] = ((int)rank[col_of(l, j)] < isal) ? 2 : ((m < psplit) ? 0 : ((m >= psplit) ? 1 : 3));
     }
     float q[16], sc[8];
@@ -1423,7 +1477,7 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
     if (technique < CRB_TECH_BRAQ || technique > CRB_TECH_CRB_SYMDAMP_NOREFINE) return CRB_ERR_BAD_ARG;
     if (!orders_valid(orders)) return CRB_ERR_BAD_ARG;
     if (orders != CRB_ORDERS_DEFAULT && scales) return CRB_ERR_UNSUPPORTED;   // the 8 scale slots hold (1, 1, 2) only
-    if (metric != CRB_METRIC_HESSIAN) return CRB_ERR_UNSUPPORTED;
+    if (metric != CRB_METRIC_HESSIAN && metric != CRB_METRIC_MAGNITUDE) return CRB_ERR_BAD_ARG;
     if ((ldw & 3) || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(Err) & 15))
         return CRB_ERR_BAD_ARG;
     if ((long long)R * kBlock >= (1ll << 31)) return CRB_ERR_UNSUPPORTED;
@@ -1450,36 +1504,35 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
 
     // K1
     const int rows1 = 32 * ceil_div(R, 32 * kMaxCtas1);
-    k_metric_colscore<<<ceil_div(R, rows1), 256, 0, st>>>(W, R, ldw, col0, U, ldu, rows1, ws.M, ws.colpart,
-                                                          ws.energy, ws.fx, ws.counters, ws.rank, tr, ws.status,
-                                                          reinterpret_cast<uint4*>(ws.zero_begin + 64),
-                                                          (int)((ws.zero_bytes - 64) / 16));
+    launch_chained(k_metric_colscore, ceil_div(R, rows1), 256, 0, st, W, R, ldw, col0, U, ldu, rows1, metric, ws.M, ws.colpart,
+                   ws.energy, ws.fx, ws.counters, ws.rank, tr, ws.status,
+                   reinterpret_cast<uint4*>(ws.zero_begin + 64), (int)((ws.zero_bytes - 64) / 16));
     CRB_LAUNCHED();
-    k_sort_rows<<<ceil_div(R, 8), 256, 0, st>>>(ws.M, R, ws.sv, ws.sc);
+    launch_chained(k_sort_rows, ceil_div(R, 8), 256, 0, st, ws.M, R, ws.sv, ws.sc);
     CRB_LAUNCHED();
     // K2: salient-count search on the sorted rows (<= kMaxTiles CTAs)
     const int rows_sal = kSalRows * ceil_div(R, kSalRows * kMaxTiles);
-    k_salient_search_sorted<<<ceil_div(R, rows_sal), 256, kSalSmem, st>>>(
-        ws.sv, ws.sc, R, rows_sal, ws.rank, ws.acc, ws.fx, ws.counters, ws.sel, tr, ws.status);
+    launch_chained(k_salient_search_sorted, ceil_div(R, rows_sal), 256, kSalSmem, st,
+                   ws.sv, ws.sc, R, rows_sal, ws.rank, ws.acc, ws.fx, ws.counters, ws.sel, tr, ws.status);
     CRB_LAUNCHED();
     // K3-K5
     const int n4 = R * (kBlock / 4);
     const int g1 = min(148, ceil_div(n4, 1024 * 4));
-    k_select_l1<<<g1, 1024, kL1Smem, st>>>(ws.M, R, ws.rank, ws.sel, ws);
+    launch_chained(k_select_l1, g1, 1024, kL1Smem, st, ws.M, R, ws.rank, ws.sel, ws);
     CRB_LAUNCHED();
     const int g2 = min(148, ceil_div(n4, 1024));
-    k_select_l2<<<g2, 1024, 0, st>>>(ws.M, R, ws.rank, ws.sel, ws);
+    launch_chained(k_select_l2, g2, 1024, 0, st, ws.M, R, ws.rank, ws.sel, ws);
     CRB_LAUNCHED();
-    k_select_l3<<<g2, 1024, 0, st>>>(ws.M, R, ws.rank, ws.sel, ws);
+    launch_chained(k_select_l3, g2, 1024, 0, st, ws.M, R, ws.rank, ws.sel, ws);
     CRB_LAUNCHED();
     // K6: split search on the sorted rows
     const int rows_sp = kSplitRows * ceil_div(R, kSplitRows * kMaxTiles);
-    k_split_search_sorted<<<ceil_div(R, rows_sp), 256, kSplitSmem, st>>>(
-        ws.sv, ws.sc, R, rows_sp, ws.rank, ws.pvals, ws.acc, ws.fx, ws.counters, ws.sel, ws.pvals, tr, ws.status);
+    launch_chained(k_split_search_sorted, ceil_div(R, rows_sp), 256, kSplitSmem, st,
+                   ws.sv, ws.sc, R, rows_sp, metric, ws.rank, ws.pvals, ws.acc, ws.fx, ws.counters, ws.sel, ws.pvals, tr, ws.status);
     CRB_LAUNCHED();
     // K7
-    k_finalize<<<ceil_div(R, 32), 256, 0, st>>>(W, R, ldw, col0, U, ldu, ws.rank, ws.sel, ws.pvals, technique,
-                                               orders, lam, corr_damp, Err, ld_err, Losses, codes, ld_codes, scales);
+    launch_chained(k_finalize, ceil_div(R, 32), 256, 0, st, W, R, ldw, col0, U, ldu, ws.rank, ws.sel, ws.pvals, technique,
+                   orders, metric, lam, corr_damp, Err, ld_err, Losses, codes, ld_codes, scales);
     CRB_LAUNCHED();
     return CRB_OK;
 }

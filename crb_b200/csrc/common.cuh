@@ -21,6 +21,42 @@ extern std::atomic<unsigned long long> g_launches;
         if (cudaGetLastError() != cudaSuccess) return CRB_ERR_LAUNCH; \
     } while (0)
 
+// ---- programmatic dependent launch ------------------------------------------------------
+// The path is a long chain of short, stream-ordered kernels (one block step is eight of them,
+// one factorisation step three): the gap between two dependent launches is a visible share of
+// the chain.  Kernels launched through launch_chained() may be placed on free SMs while their
+// predecessor in the stream still runs; each of them calls chain_wait() before it reads or
+// writes global memory, which returns only when the predecessor has completed and its writes
+// are visible, so stream order is kept for the data.  What overlaps is the launch itself and
+// the part of a kernel in front of chain_wait() (shared-memory set-up, barrier and tensor-memory
+// allocation).  chain_wait() is a no-op for a kernel launched the ordinary way.
+extern std::atomic<int> g_dependent_launch;   // 1: use it (default); crb_set_dependent_launch()
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void chain_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // from here on the next kernel of the stream may be scheduled next to this one; it blocks in
+    // its own chain_wait() until this grid has completed
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_dependent_launch.load(std::memory_order_relaxed) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // Per-device one-time set-up.  Function attributes (the dynamic shared-memory limit of a kernel)
 // and device properties belong to a DEVICE, not to the process: a host that drives several GPUs
 // has to set them once on each.  `run(setup)` calls `setup()` (returning a crbStatus) the first

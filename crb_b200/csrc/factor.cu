@@ -139,6 +139,7 @@ k_chol_diag(float* __restrict__ Akk, int64_t ld, unsigned* status) {
     __shared__ int s_bad;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) s_bad = 0;
+    chain_wait();
     for (int e = tid; e < FB * FB; e += kDiagThreads) {
         a[(e >> 7) * kDiagPitch + (e & 127)] = Akk[(int64_t)(e >> 7) * ld + (e & 127)];
         x[(e >> 7) * kDiagPitch + (e & 127)] = 0.f;
@@ -341,7 +342,7 @@ int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
         const int k1 = k0 + kOuter < nb ? k0 + kOuter : nb;
         for (int k = k0; k < k1; ++k) {
             float* Akk = A + (int64_t)k * FB * (C + 1);
-            k_chol_diag<<<1, kDiagThreads, kDiagSmem, st>>>(Akk, C, status);
+            launch_chained(k_chol_diag, 1, kDiagThreads, kDiagSmem, st, Akk, (int64_t)C, status);
             CRB_LAUNCHED();
             const int rem = C - (k + 1) * FB;
             if (rem <= 0) break;

@@ -145,6 +145,7 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    chain_wait();          // operands and C belong to the kernels in front of this one in the stream
     const uint32_t tmem_base = *tmem_slot;
     const int total = g.m_tiles * g.n_tiles;
     // Each warpgroup first hands over / takes registers (uniform per warpgroup), then runs its role.
@@ -423,7 +424,7 @@ int gemm_tf32x3(bool b_is_nk, int shape, int M, int N, int K, float alpha, const
     }, &sms);
     if (rc_setup != CRB_OK) return rc_setup;
     const int total = g.m_tiles * g.n_tiles;
-    k_gemm_tf32x3<<<total < sms ? total : sms, GT_THREADS, GT_SMEM, st>>>(map_a, map_b, g);
+    launch_chained(k_gemm_tf32x3, total < sms ? total : sms, GT_THREADS, GT_SMEM, st, map_a, map_b, g);
     CRB_LAUNCHED();
     return CRB_OK;
 }

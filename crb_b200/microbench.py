@@ -60,10 +60,14 @@ def main(argv=None):
     ap.add_argument("--technique", default="crb", choices=["crb", "crbog", "braq"])
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--no_dependent_launch", action="store_true",
+                    help="plain stream-ordered launches instead of programmatic dependent launch")
     a = ap.parse_args(argv)
+    if a.no_dependent_launch:
+        ops.set_dependent_launch(False)
     dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator(device=dev).manual_seed(1)
-    out = {"what": a.what, "R": a.R, "C": a.C, "T": a.T}
+    out = {"what": a.what, "R": a.R, "C": a.C, "T": a.T, "dependent_launch": not a.no_dependent_launch}
     launches0 = ops.launch_count()
 
     if a.what == "hessian":

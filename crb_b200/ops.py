@@ -280,5 +280,10 @@ def selftest_wait_limit(device, limit_us: int = 1000) -> int:
     return int(status[0].item())
 
 
+def set_dependent_launch(enable: bool) -> bool:
+    """Switches programmatic dependent launch of the kernel chains on or off; returns the old setting."""
+    return bool(lib().crb_set_dependent_launch(int(bool(enable))))
+
+
 def launch_count() -> int:
     return int(lib().crb_launch_count())

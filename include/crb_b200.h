@@ -206,6 +206,13 @@ int crb_read_status(const void *workspace_dev, void *stream);
 /* Number of kernels this library has launched since load (for launch accounting). */
 unsigned long long crb_launch_count(void);
 
+/* Programmatic dependent launch for the chains of short kernels (block step, factorisation,
+ * trailing updates): a kernel may be scheduled while its predecessor in the stream still runs and
+ * waits on the device for its completion before it touches global memory.  Results are the same
+ * with and without; the switch exists to measure the effect.  Returns the previous setting
+ * (default 1 = on).  No counterpart in the reference (eager PyTorch launches).               */
+int crb_set_dependent_launch(int enable);
+
 /* ---- self-test of the bounded waits -----------------------------------------------
  * Every wait inside the tensor-core kernels gives up after a time limit, raises
  * CRB_FLAG_WAIT_LIMIT in the status word, drains its copies, frees its tensor memory and

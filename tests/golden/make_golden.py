@@ -251,6 +251,7 @@ def gen_variants(bigptq, binary, autosearch, out):
             data[f"c{ci}_{tech}_ragged_o2"] = qz.quantize(W, ragged, order=2).numpy()
     lin = np.load(os.path.join(HERE, "linear.npz"))
     W, H, nseq = torch.from_numpy(lin["W"]), torch.from_numpy(lin["H"]), int(lin["nseq"])
+    W_lin, H_lin = W, H
     for tech, orders in (("braq", (2, 2, 2)), ("crb", (2, 2, 2)), ("crb", (2, 1, 1)), ("crb_symdamp_norefine", (1, 1, 2))):
         tag = f"{tech}_{''.join(map(str, orders))}"
         Wq, err, blks = run_reference_linear_orders(bigptq, binary, autosearch, W, H, nseq, tech, orders)
@@ -258,6 +259,37 @@ def gen_variants(bigptq, binary, autosearch, out):
         data[f"{tag}_error"] = np.float64(err)
         for bi, blk in enumerate(blks):
             data[f"{tag}_b{bi}_errs"] = np.asarray(blk["errs"], dtype=np.float64)
+    # (c) the magnitude salience metric (utils/structure.py:11-12): the searches run on the signed
+    # weights themselves; single blocks and a whole linear
+    for ci in (0, 1, 3):
+        W = torch.from_numpy(blocks[f"c{ci}_W"])
+        d = torch.from_numpy(blocks[f"c{ci}_d"])
+        with Capture(bigptq, autosearch) as cap:
+            m1, m2, m3 = bigptq.structural_guassian_distribution(W, torch.diag(d), "magnitude", 50)
+        data[f"mag_c{ci}_errs"] = np.asarray(cap.blocks[0]["errs"], dtype=np.float64)
+        for name, m in (("m1", m1), ("m2", m2), ("m3", m3)):
+            data[f"mag_c{ci}_{name}"] = pack(m)
+        qz = binary.Binarization(W, method="crb", groupsize=128, corr_damp=0.1, lam=1e-5)
+        Q = torch.zeros_like(W)
+        for m, order in zip((m1, m2, m3), (1, 1, 2)):
+            Q += qz.quantize(W, m, order=order) * m
+        data[f"mag_c{ci}_crb_Q"] = Q.numpy()
+    for tech in ("braq", "crb"):
+        R, C = W_lin.shape
+        layer = nn.Linear(C, R, bias=False)
+        layer.weight.data = W_lin.clone()
+        qz = binary.Binarization(layer.weight, method=tech, groupsize=128, corr_damp=0.1, lam=1e-5)
+        g = bigptq.BRAGPTQ(layer, qz, salient_metric="magnitude")
+        g.H = H_lin.clone()
+        g.nsamples = nseq
+        with Capture(bigptq, autosearch) as cap, contextlib.redirect_stdout(io.StringIO()):
+            info = g.fasterquant(blocksize=128, percdamp=0.01, partition=3)
+        data[f"mag_{tech}_Wq"] = layer.weight.data.clone().numpy()
+        data[f"mag_{tech}_error"] = np.float64(info["error"])
+        for bi, blk in enumerate(cap.blocks):
+            data[f"mag_{tech}_b{bi}_errs"] = np.asarray(blk["errs"], dtype=np.float64)
+            data[f"mag_{tech}_b{bi}_m1"] = pack(blk["m1"])
+            data[f"mag_{tech}_b{bi}_m3"] = pack(blk["m3"])
     np.savez_compressed(out, **data)
     print("wrote", out)
 

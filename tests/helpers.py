@@ -51,36 +51,51 @@ def gaps_of(errs: np.ndarray):
 SCORE_TIE = 2e-6
 
 
-def score_tied_candidates(tf: dict) -> set:
+def score_tied_candidates(tf: dict, tol: float = SCORE_TIE) -> set:
     """Salient candidates (0-based) whose column set hinges on a near tie of two column scores."""
     s = np.asarray(tf["top_scores"], dtype=np.float64)
-    return {c for c in range(len(s) - 1) if abs(s[c] - s[c + 1]) <= SCORE_TIE * abs(s[c])}
+    return {c for c in range(len(s) - 1) if abs(s[c] - s[c + 1]) <= tol * abs(s[c])}
 
 
-def check_search_against_reference(tf: dict, ref_errs: np.ndarray, what: str = "", rtol: float = 2e-5):
+def check_search_against_reference(tf: dict, ref_errs: np.ndarray, what: str = "", rtol: float = 2e-5,
+                                   noise_ok: bool = False):
     """Compares a device search trace with the reference's 130 candidate errors.
 
     Returns "exact" when both decisions agree, "tie" when a decision differs but the
     reference's own gap between the two candidates is below TIE_GAP, or when a salient candidate
     differs only because two column scores are tied within SCORE_TIE; raises otherwise.
+
+    `noise_ok` is for comparisons in which the INPUTS of the block already differ from the
+    reference's by rounding noise (an end-to-end run on another machine: Hessian, factor and earlier
+    blocks were computed in another summation order).  The candidate errors then differ by some
+    relative amount `dev` <= rtol, measured here on the 130 values themselves, and a decision whose
+    margin in the reference is below 2 * dev cannot be expected to survive: it is reported as
+    "noise" instead of failing.
     """
     ref_sal, ref_split = np.asarray(ref_errs[:49], dtype=np.float64), np.asarray(ref_errs[49:], dtype=np.float64)
     outcome = "exact"
     ri, _ = gaps_of(ref_sal)
     bad = np.nonzero(~np.isclose(tf["salient_err"], ref_sal, rtol=rtol, atol=0))[0]
-    if len(bad) and set(bad.tolist()) <= score_tied_candidates(tf):
+    # with noisy inputs the column scores carry the same relative noise as the candidate errors
+    if len(bad) and set(bad.tolist()) <= score_tied_candidates(tf, max(SCORE_TIE, rtol) if noise_ok else SCORE_TIE):
         return "tie"                                   # a different (equally scored) column order
+    np.testing.assert_allclose(tf["salient_err"], ref_sal, rtol=rtol, err_msg=f"{what}: salient errors")
+    dev = float(np.max(np.abs(tf["salient_err"] - ref_sal) / ref_sal))
     if tf["n_salient"] != ri + 1:
         gap = abs(ref_sal[tf["n_salient"] - 1] - ref_sal[ri]) / ref_sal[ri]
-        assert gap <= TIE_GAP, f"{what}: salient count {tf['n_salient']} vs {ri + 1}, gap {gap:.3e}"
+        if noise_ok and gap <= 2.0 * dev:
+            return "noise"
+        assert gap <= TIE_GAP, f"{what}: salient count {tf['n_salient']} vs {ri + 1}, gap {gap:.3e}, noise {dev:.3e}"
         return "tie"
-    np.testing.assert_allclose(tf["salient_err"], ref_sal, rtol=rtol, err_msg=f"{what}: salient errors")
     rk, _ = gaps_of(ref_split)
+    np.testing.assert_allclose(tf["split_err"], ref_split, rtol=rtol, err_msg=f"{what}: split errors")
+    dev = float(np.max(np.abs(tf["split_err"] - ref_split) / ref_split))
     if tf["split_index"] != rk:
         gap = abs(ref_split[tf["split_index"]] - ref_split[rk]) / ref_split[rk]
-        assert gap <= TIE_GAP, f"{what}: split index {tf['split_index']} vs {rk}, gap {gap:.3e}"
+        if noise_ok and gap <= 2.0 * dev:
+            return "noise"
+        assert gap <= TIE_GAP, f"{what}: split index {tf['split_index']} vs {rk}, gap {gap:.3e}, noise {dev:.3e}"
         outcome = "tie"
-    np.testing.assert_allclose(tf["split_err"], ref_split, rtol=rtol, err_msg=f"{what}: split errors")
     return outcome
 
 

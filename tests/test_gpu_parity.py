@@ -507,3 +507,55 @@ def test_bragptq_other_orders_and_variants(linear, variants, tech, orders):
     e_dev, e_ref = O.output_error(W, Wq, X), O.output_error(W, ref_W, X)
     assert abs(e_dev - e_ref) <= Hh.OUTPUT_ERR_RTOL * e_ref, (tag, e_dev, e_ref)
     assert abs(info["error"] - float(variants[f"{tag}_error"])) <= Hh.OUTPUT_ERR_RTOL * info["error"]
+
+
+@pytest.mark.parametrize("ci", (0, 1, 3))
+def test_magnitude_metric_block_matches_reference(ops, blocks, variants, ci):
+    """salient_metric="magnitude" (utils/structure.py:11-12): signed metric values through the sort,
+    the hole-based salient search and the two-tailed mid group of the split search."""
+    W = torch.from_numpy(blocks[f"c{ci}_W"])
+    d = torch.from_numpy(blocks[f"c{ci}_d"])
+    Wd = W.to(DEV).clone()
+    out = ops.block_step(Wd, torch.diag(d).to(DEV), 0, "crb", metric="magnitude")
+    torch.cuda.synchronize()
+    tf = Hh.trace_fields(out["trace"])
+    outcome = Hh.check_search_against_reference(tf, variants[f"mag_c{ci}_errs"], f"magnitude case {ci}")
+    g1, g2, g3 = Hh.masks_from_codes(out["codes"].cpu())
+    assert bool(((g1.int() + g2.int() + g3.int()) == 1).all())
+    if outcome == "exact":
+        for got, name in ((g1, "m1"), (g2, "m2"), (g3, "m3")):
+            assert torch.equal(got, Hh.unpack(variants[f"mag_c{ci}_{name}"], W.shape)), name
+        ref_Q = torch.from_numpy(variants[f"mag_c{ci}_crb_Q"])
+        assert torch.allclose(Wd.cpu(), ref_Q, rtol=2e-5, atol=1e-7), (Wd.cpu() - ref_Q).abs().max()
+
+
+@pytest.mark.parametrize("tech", ("braq", "crb"))
+def test_magnitude_metric_linear_matches_reference(linear, variants, tech):
+    import torch.nn as nn
+    from crb_b200 import BRAGPTQ, Binarization
+    W = torch.from_numpy(linear["W"])
+    lin = nn.Linear(W.shape[1], W.shape[0], bias=False)
+    lin.weight.data = W.clone()
+    lin = lin.to(DEV)
+    g = BRAGPTQ(lin, Binarization(lin.weight, method=tech, groupsize=128), salient_metric="magnitude")
+    g.verbose = False
+    g.H = torch.from_numpy(linear["H"]).to(DEV)
+    g.nsamples = int(linear["nseq"])
+    info = g.fasterquant(blocksize=128, percdamp=0.01)
+    Wq = lin.weight.data.cpu()
+    ref_W = torch.from_numpy(variants[f"mag_{tech}_Wq"])
+    nblk = W.shape[1] // 128
+    agree = nblk
+    for bi in range(nblk):
+        tf = Hh.trace_fields(g.last_trace[bi])
+        if Hh.check_search_against_reference(tf, variants[f"mag_{tech}_b{bi}_errs"], f"magnitude {tech} block {bi}",
+                                             rtol=1e-4) != "exact":
+            agree = bi
+            break
+    if agree:
+        close = torch.isclose(Wq[:, :agree * 128], ref_W[:, :agree * 128], rtol=1e-3, atol=1e-6).float().mean().item()
+        assert close >= Hh.SIGN_AGREEMENT, (tech, close)
+    X = torch.from_numpy(linear["X"])
+    e_dev, e_ref = O.output_error(W, Wq, X), O.output_error(W, ref_W, X)
+    assert abs(e_dev - e_ref) <= Hh.OUTPUT_ERR_RTOL * e_ref, (tech, e_dev, e_ref)
+    assert abs(info["error"] - float(variants[f"mag_{tech}_error"])) <= Hh.OUTPUT_ERR_RTOL * info["error"]

@@ -122,15 +122,21 @@ def test_tall_block_matches_oracle(ops, R):
         assert torch.allclose(out["Err"].cpu(), Err, rtol=2e-5, atol=1e-7)
 
 
-def test_summation_order_of_partial_hessians_only_moves_ties(ops):
+@pytest.mark.parametrize("inputs", ("gaussian", "relu_features"))
+def test_summation_order_of_partial_hessians_only_moves_ties(ops, inputs):
     """Several GPUs sum their partial Hessians in an order that depends on the GPU count.  Quantize
-    one 4096 x 4096 linear from the same four partial sums added in two different orders: the two
+    one 4096 x 4096 linear from the same four partial sums added in three different orders: the
     runs may only part ways at a block whose decision is a near tie, and the layer's output error
-    must agree far inside the 0.5 % contract either way."""
+    must agree far inside the 0.5 % contract either way.  `relu_features` mimics the input of an
+    MLP's second linear (rectified, strongly correlated features: a badly conditioned Hessian)."""
     C = R = 4096
     g = torch.Generator(device=DEV).manual_seed(31)
-    X = torch.randn(4 * 4096, C, generator=g, device=DEV)
-    X[:, torch.randperm(C, generator=g, device=DEV)[:40]] *= 20
+    if inputs == "gaussian":
+        X = torch.randn(4 * 4096, C, generator=g, device=DEV)
+        X[:, torch.randperm(C, generator=g, device=DEV)[:40]] *= 20
+    else:
+        Z = torch.randn(4 * 4096, 1024, generator=g, device=DEV)
+        X = torch.relu(Z @ (torch.randn(1024, C, generator=g, device=DEV) / 32.0) - 0.5)
     X = X.half()
     W = (torch.randn(R, C, generator=g, device=DEV) * 0.02)
     parts = []
@@ -192,7 +198,7 @@ def test_summation_order_of_partial_hessians_only_moves_ties(ops):
             report.append((None, 0.0, 0.0))
         assert abs(other["out_err"] - base["out_err"]) <= 0.2 * Hh.OUTPUT_ERR_RTOL * base["out_err"], \
             (other["out_err"], base["out_err"])
-    print("summation order: first differing block, its gap, movement of its candidate errors:", report,
+    print(f"summation order ({inputs}): first differing block, its gap, movement of its candidate errors:", report,
           "block-error sums", [r["error"] for r in runs], "output errors", [r["out_err"] for r in runs])
 
 

@@ -145,3 +145,29 @@ def test_linear_with_other_orders_matches_reference(linear, variants, tech, orde
         assert np.array_equal(got, variants[f"{tag}_b{bi}_errs"]), bi
     assert torch.equal(res.W, torch.from_numpy(variants[f"{tag}_Wq"]))
     assert res.error == float(variants[f"{tag}_error"])
+
+
+@pytest.mark.parametrize("ci", (0, 1, 3))
+def test_magnitude_metric_block_search_matches_reference(blocks, variants, ci):
+    """salient_metric="magnitude": the searches run on the signed weights (utils/structure.py:11-12)."""
+    W = torch.from_numpy(blocks[f"c{ci}_W"])
+    d = torch.from_numpy(blocks[f"c{ci}_d"])
+    m1, m2, m3, tr = O.partition_block(W, d, "magnitude")
+    for name, m in (("m1", m1), ("m2", m2), ("m3", m3)):
+        assert torch.equal(m, unpack(variants[f"mag_c{ci}_{name}"], W.shape)), name
+    assert np.array_equal(np.asarray(tr.salient_err + tr.split_err), variants[f"mag_c{ci}_errs"])
+    assert torch.equal(O.block_step(W, d, "crb", metric="magnitude").Q, torch.from_numpy(variants[f"mag_c{ci}_crb_Q"]))
+
+
+@pytest.mark.parametrize("tech", ("braq", "crb"))
+def test_magnitude_metric_linear_matches_reference(linear, variants, tech):
+    W = torch.from_numpy(linear["W"])
+    H = torch.from_numpy(linear["H"]).clone()
+    res = O.quantize_linear(W, H, tech, metric="magnitude")
+    for bi, blk in enumerate(res.blocks):
+        got = np.asarray(blk.trace.salient_err + blk.trace.split_err)
+        assert np.array_equal(got, variants[f"mag_{tech}_b{bi}_errs"]), bi
+        assert torch.equal(blk.masks[0], unpack(variants[f"mag_{tech}_b{bi}_m1"], blk.Q.shape))
+        assert torch.equal(blk.masks[2], unpack(variants[f"mag_{tech}_b{bi}_m3"], blk.Q.shape))
+    assert torch.equal(res.W, torch.from_numpy(variants[f"mag_{tech}_Wq"]))
+    assert res.error == float(variants[f"mag_{tech}_error"])
