@@ -370,6 +370,17 @@ def run_ours(args):
     barrier()
     e2e_ms = e0.elapsed_time(e1)
 
+    # per-rank step time and phases (device time on each rank's own stream), to see which rank and
+    # which phase the maximum comes from
+    keys = ["forward_hessian", "hessian_allreduce", "fasterquant", "weight_broadcast", "forward_repropagate"]
+    mine_vec = torch.tensor([dev_ms] + [phases.get(k, 0.0) for k in keys], dtype=torch.float64, device=dev)
+    if world > 1:
+        gathered = [torch.zeros_like(mine_vec) for _ in range(world)]
+        dist.all_gather(gathered, mine_vec)
+    else:
+        gathered = [mine_vec]
+    per_rank = [{"step": round(float(v[0]) / args.steps, 2),
+                 **{k: round(float(v[1 + j]) / args.steps, 2) for j, k in enumerate(keys)}} for v in gathered]
     dev_ms = parallel.max_over_ranks(dev_ms, dev)
     e2e_ms = parallel.max_over_ranks(e2e_ms, dev)
     launches = int(parallel.sum_over_ranks(float(launches), dev))
@@ -404,6 +415,7 @@ def run_ours(args):
                 "gpu_launches": launches, "clocks": clocks, "roofline": roof, "roofline_extra": roof_extra,
                 "cpu_baseline": cpu,
                 "phases_ms_per_step": {k: v / args.steps for k, v in phases.items()},
+                "per_rank_ms_per_step": per_rank,
                 "block_error_sum_per_layer": err_sum / args.steps, "wall_clock_s_timed_region": wall,
                 "peaks": peaks["source"]}
         print(json.dumps(line))

@@ -33,6 +33,9 @@ SIGNATURES = {
     "crb_hessian_workspace_bytes": (_sz, [_i, _i64, _i]),
     "crb_hessian_accumulate": (_i, [_vp, _i, _i64, _i, _i64, _vp, _vp, _sz, _vp]),
     "crb_hessian_finalize": (_i, [_vp, _i, _f, _vp]),
+    "crb_hessian_packed_floats": (_sz, [_i]),
+    "crb_hessian_pack": (_i, [_vp, _i, _vp, _vp]),
+    "crb_hessian_unpack": (_i, [_vp, _i, _vp, _vp]),
     "crb_factor_workspace_bytes": (_sz, [_i]),
     "crb_hinv_upper_factor": (_i, [_vp, _i, _vp, _i, _i64, _f, _i, _vp, _sz, _vp, _vp]),
     "crb_block_workspace_bytes": (_sz, [_i]),

@@ -26,6 +26,8 @@ size_t hessian_workspace_bytes(int C, int64_t T, int dtype);
 int hessian_accumulate_launch(const void* X, int dtype, int64_t T, int C, int64_t ldx, float* S,
                               void* workspace, size_t workspace_bytes, cudaStream_t st);
 int hessian_finalize_launch(float* S, int C, float scale, cudaStream_t st);
+long long hessian_packed_floats(int C);
+int hessian_pack_launch(float* S, int C, float* packed, int unpack, cudaStream_t st);
 // factor.cu
 size_t factor_workspace_bytes(int C);
 int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp, int extra_steps,
@@ -71,6 +73,16 @@ int crb_hessian_accumulate(const void* X, int dtype, int64_t T, int C, int64_t l
 
 int crb_hessian_finalize(float* S, int C, float scale, void* stream) {
     return hessian_finalize_launch(S, C, scale, static_cast<cudaStream_t>(stream));
+}
+
+size_t crb_hessian_packed_floats(int C) { return (size_t)hessian_packed_floats(C); }
+
+int crb_hessian_pack(const float* S, int C, float* packed, void* stream) {
+    return hessian_pack_launch(const_cast<float*>(S), C, packed, 0, static_cast<cudaStream_t>(stream));
+}
+
+int crb_hessian_unpack(const float* packed, int C, float* S, void* stream) {
+    return hessian_pack_launch(S, C, const_cast<float*>(packed), 1, static_cast<cudaStream_t>(stream));
 }
 
 size_t crb_factor_workspace_bytes(int C) { return factor_workspace_bytes(C); }

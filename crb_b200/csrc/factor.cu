@@ -16,6 +16,10 @@
 // recursively: [[A,0],[B,D]]^-1 = [[A^-1,0],[-D^-1 B A^-1, D^-1]], skipping the zero halves.
 // A non-positive pivot sets CRB_FLAG_BAD_PIVOT (the host re-damps and calls again, like the
 // retry loop at bigptq.py:115-123) and is replaced by 1 so that nothing non-finite spreads.
+#include <map>
+#include <utility>
+#include <vector>
+
 #include "common.cuh"
 
 namespace crb {
@@ -289,12 +293,20 @@ size_t factor_workspace_bytes(int C) {
     return align256(sizeof(float) * (size_t)C * C) + 256 + align256((size_t)C);
 }
 
-static int invert_range(float* A, int C, int lo, int hi, float* tmp, unsigned* status, cudaStream_t st) {
+// A range of diagonal blocks that lies inside one outer panel of the factorisation.
+static bool within_one_panel(int lo, int hi) { return lo / kOuter == (hi - 1) / kOuter; }
+
+// Inverse of the lower-triangular factor on the diagonal blocks [lo, hi), in place, by recursive
+// merges.  `skip_panel_local`: sub-ranges inside one outer panel are already inverted (the side
+// stream did them while the factorisation went on) and are left alone.
+static int invert_range(float* A, int C, int lo, int hi, float* tmp, unsigned* status, cudaStream_t st,
+                        bool skip_panel_local) {
     if (hi - lo <= 1) return CRB_OK;
+    if (skip_panel_local && within_one_panel(lo, hi)) return CRB_OK;
     const int mid = lo + (hi - lo) / 2;
-    int rc = invert_range(A, C, lo, mid, tmp, status, st);
+    int rc = invert_range(A, C, lo, mid, tmp, status, st, skip_panel_local);
     if (rc != CRB_OK) return rc;
-    rc = invert_range(A, C, mid, hi, tmp, status, st);
+    rc = invert_range(A, C, mid, hi, tmp, status, st, skip_panel_local);
     if (rc != CRB_OK) return rc;
     const int s1 = (mid - lo) * FB, s2 = (hi - mid) * FB;
     float* B = A + (int64_t)mid * FB * C + (int64_t)lo * FB;
@@ -304,6 +316,42 @@ static int invert_range(float* A, int C, int lo, int hi, float* tmp, unsigned* s
     rc = gemm_tf32x3(false, GEMM_B_LOWER, s2, s1, s1, 1.0f, B, C, Ainv, C, 0.0f, tmp, s1, status, st);      // T = B A^-1
     if (rc != CRB_OK) return rc;
     return gemm_tf32x3(false, GEMM_A_LOWER, s2, s1, s2, -1.0f, Dinv, C, tmp, s1, 0.0f, B, C, status, st);   // B = -D^-1 T
+}
+
+// The merges of the recursion tree over [lo, hi) that lie inside outer panel `panel`: the largest
+// such sub-ranges are inverted completely (their inputs are final once that panel is factored).
+static int invert_panel_local(float* A, int C, int lo, int hi, int panel, float* tmp, unsigned* status,
+                              cudaStream_t st) {
+    if (hi - lo <= 1 || panel < lo / kOuter || panel > (hi - 1) / kOuter) return CRB_OK;
+    if (within_one_panel(lo, hi)) return invert_range(A, C, lo, hi, tmp, status, st, false);
+    const int mid = lo + (hi - lo) / 2;
+    const int rc = invert_panel_local(A, C, lo, mid, panel, tmp, status, st);
+    if (rc != CRB_OK) return rc;
+    return invert_panel_local(A, C, mid, hi, panel, tmp, status, st);
+}
+
+// A second stream per caller stream, and events to fork to it and join it again.  The merges inside
+// an outer panel are chains of small, latency-bound products: they run there while the caller's
+// stream goes on with the next panels of the factorisation.
+struct SideContext {
+    cudaStream_t side = nullptr;
+    std::vector<cudaEvent_t> events;
+};
+static std::mutex g_side_lock;
+static std::map<std::pair<int, cudaStream_t>, SideContext> g_side;
+
+static SideContext* side_context(cudaStream_t main, size_t n_events) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    std::lock_guard<std::mutex> guard(g_side_lock);
+    SideContext& ctx = g_side[std::make_pair(dev, main)];
+    if (!ctx.side && cudaStreamCreateWithFlags(&ctx.side, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    while (ctx.events.size() < n_events) {
+        cudaEvent_t e;
+        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        ctx.events.push_back(e);
+    }
+    return &ctx;
 }
 
 int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp, int extra_steps,
@@ -338,6 +386,12 @@ int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
     // touch the panel's own columns only; everything right of the panel gets one update with
     // K = 8 * 128 afterwards, which is compute bound instead of re-reading the whole trailing
     // matrix once per diagonal block.
+    const int n_panels = (nb + kOuter - 1) / kOuter;
+    SideContext* sc = nb > kOuter ? side_context(st, (size_t)n_panels + 1) : nullptr;
+    // scratch of the merges: H is free once it has been copied (the side stream's merges and the
+    // final ones never run at the same time: each uses the start of its own half)
+    float* tmp_side = H;
+    float* tmp_main = H + (size_t)C * C / 2;
     for (int k0 = 0; k0 < nb; k0 += kOuter) {
         const int k1 = k0 + kOuter < nb ? k0 + kOuter : nb;
         for (int k = k0; k < k1; ++k) {
@@ -354,6 +408,16 @@ int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
                              status, st);                                                                   // A22[:, :inside] -= P P^T
             if (rc != CRB_OK) return rc;
         }
+        if (sc) {
+            // the panel's diagonal blocks and the factor entries between them are final: invert the
+            // panel's part of the factor on the side stream while this stream carries on
+            const int p = k0 / kOuter;
+            if (cudaEventRecord(sc->events[p], st) != cudaSuccess ||
+                cudaStreamWaitEvent(sc->side, sc->events[p], 0) != cudaSuccess)
+                return CRB_ERR_LAUNCH;
+            const int rc = invert_panel_local(A, C, 0, nb, p, tmp_side, status, sc->side);
+            if (rc != CRB_OK) return rc;
+        }
         const int rem = C - k1 * FB;
         if (rem <= 0) break;
         const float* P = A + (int64_t)k1 * FB * C + (int64_t)k0 * FB;     // rows below the panel, the panel's columns
@@ -361,7 +425,12 @@ int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
                              A + (int64_t)k1 * FB * (C + 1), C, status, st);
         if (rc != CRB_OK) return rc;
     }
-    int rc = invert_range(A, C, 0, nb, H, status, st);          // H is free to serve as scratch now
+    if (sc) {
+        if (cudaEventRecord(sc->events[n_panels], sc->side) != cudaSuccess ||
+            cudaStreamWaitEvent(st, sc->events[n_panels], 0) != cudaSuccess)
+            return CRB_ERR_LAUNCH;
+    }
+    int rc = invert_range(A, C, 0, nb, tmp_main, status, st, sc != nullptr);   // the merges across panels
     if (rc != CRB_OK) return rc;
     k_reverse_upper<<<dim3((C + 255) / 256, C), 256, 0, st>>>(A, C, H);
     CRB_LAUNCHED();

@@ -393,6 +393,30 @@ __global__ void k_hessian_finalize(float* __restrict__ S, int C, float scale) {
     }
 }
 
+// Number of floats in front of row r in the packed form: rows of band b = r / 256 keep their
+// columns from 256 b on (the accumulation kernel only maintains those tiles).
+__host__ __device__ inline long long packed_row_offset(int r, int C) {
+    const long long b = r / H2_TILE, in_band = r % H2_TILE;
+    // full bands in front: sum_{k < b} 256 * (C - 256 k)
+    return (long long)H2_TILE * (b * C - (long long)H2_TILE * b * (b - 1) / 2) + in_band * ((long long)C - H2_TILE * b);
+}
+
+// Copies the maintained part of S (its upper-triangle 256 x 256 tiles) into a contiguous buffer or
+// back, so that a sum over ranks moves half the bytes.  One CTA per row.
+__global__ void __launch_bounds__(256)
+k_hessian_pack(float* __restrict__ S, int C, float* __restrict__ packed, int unpack) {
+    const int r = blockIdx.x;
+    const int c0 = r / H2_TILE * H2_TILE;
+    float* row = S + (int64_t)r * C + c0;
+    float* dst = packed + packed_row_offset(r, C);
+    const int n4 = (C - c0) >> 2;                               // C and c0 are multiples of 128
+    float4* a = reinterpret_cast<float4*>(row);
+    float4* b = reinterpret_cast<float4*>(dst);
+    for (int k = threadIdx.x; k < n4; k += blockDim.x) {
+        if (unpack) a[k] = b[k]; else b[k] = a[k];
+    }
+}
+
 // ---- host side ----------------------------------------------------------------------------------
 static int make_map(CUtensorMap* map, const void* base, int dtype, int64_t T, int C, int64_t ld) {
     const CUtensorMapDataType dt = (dtype == CRB_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -471,6 +495,16 @@ int hessian_accumulate_launch(const void* X, int dtype, int64_t T, int C, int64_
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (cudaLaunchKernelEx(&cfg, k_hessian_umma_pair, map0, map1, a) != cudaSuccess) return CRB_ERR_LAUNCH;
+    CRB_LAUNCHED();
+    return CRB_OK;
+}
+
+long long hessian_packed_floats(int C) { return C > 0 ? packed_row_offset(C, C) : 0; }
+
+int hessian_pack_launch(float* S, int C, float* packed, int unpack, cudaStream_t st) {
+    if (!S || !packed || C <= 0 || (C % kBlock)) return CRB_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(S) | reinterpret_cast<uintptr_t>(packed)) & 15) return CRB_ERR_BAD_ARG;
+    k_hessian_pack<<<C, 256, 0, st>>>(S, C, packed, unpack);
     CRB_LAUNCHED();
     return CRB_OK;
 }

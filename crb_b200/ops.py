@@ -75,6 +75,21 @@ def hessian_finalize(S: torch.Tensor, scale: float) -> None:
     check(lib().crb_hessian_finalize(ptr(S), S.shape[0], float(scale), stream_ptr()), "crb_hessian_finalize")
 
 
+def hessian_packed_floats(C: int) -> int:
+    return int(lib().crb_hessian_packed_floats(int(C)))
+
+
+def hessian_pack(S: torch.Tensor, packed: torch.Tensor) -> None:
+    """The maintained (upper-triangle tile) part of S [C, C] -> packed [hessian_packed_floats(C)]."""
+    _need_cuda(S, packed)
+    check(lib().crb_hessian_pack(ptr(S), S.shape[0], ptr(packed), stream_ptr()), "crb_hessian_pack")
+
+
+def hessian_unpack(packed: torch.Tensor, S: torch.Tensor) -> None:
+    _need_cuda(S, packed)
+    check(lib().crb_hessian_unpack(ptr(packed), S.shape[0], ptr(S), stream_ptr()), "crb_hessian_unpack")
+
+
 def hessian_status(device) -> int:
     ws = _workspaces.get(("hessian", torch.device(device).index, torch.cuda.current_stream(device).cuda_stream))
     return 0 if ws is None else lib().crb_read_status(ptr(ws), stream_ptr())

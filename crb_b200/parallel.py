@@ -60,6 +60,33 @@ def allreduce_sum_(tensors: Sequence[torch.Tensor]) -> None:
         h.wait()
 
 
+def allreduce_hessians_(sums: Sequence[torch.Tensor]) -> None:
+    """In-place sum over ranks of partial Hessian sums S [C, C] as `ops.hessian_accumulate` keeps them.
+
+    On CUDA only the maintained part of each S (its 256 x 256 tiles on and above the diagonal) is
+    summed: all of them are packed into one buffer, reduced with a single all-reduce and unpacked,
+    which moves about half the bytes of the full matrices.  CPU tensors (the gloo tests) take the
+    plain route."""
+    _, ws = world()
+    if ws == 1 or not sums:
+        return
+    if not all(t.is_cuda and t.dim() == 2 and t.shape[0] == t.shape[1] and t.is_contiguous() for t in sums):
+        allreduce_sum_(sums)
+        return
+    from . import ops
+    sizes = [ops.hessian_packed_floats(t.shape[0]) for t in sums]
+    buf = torch.empty(sum(sizes), dtype=torch.float32, device=sums[0].device)
+    off = 0
+    for t, n in zip(sums, sizes):
+        ops.hessian_pack(t, buf[off:off + n])
+        off += n
+    dist.all_reduce(buf, op=dist.ReduceOp.SUM)
+    off = 0
+    for t, n in zip(sums, sizes):
+        ops.hessian_unpack(buf[off:off + n], t)
+        off += n
+
+
 def broadcast_(tensor: torch.Tensor, src: int) -> None:
     _, ws = world()
     if ws > 1:

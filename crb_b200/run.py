@@ -475,7 +475,7 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
     leaders = [n for n in gptq if n not in alias]
     with timer.span("hessian_allreduce"):
         if ws > 1:
-            parallel.allreduce_sum_([gptq[n]._S for n in leaders])
+            parallel.allreduce_hessians_([gptq[n]._S for n in leaders])
             total = int(parallel.sum_over_ranks(float(n_local), dev))
             for n in leaders:
                 gptq[n].nsamples = total

@@ -89,6 +89,15 @@ int crb_hessian_accumulate(const void *X_dev, int dtype, int64_t T, int C, int64
 /* H = scale * S, both triangles written (S holds the upper-triangle tiles). */
 int crb_hessian_finalize(float *S_dev, int C, float scale, void *stream);
 
+/* The part of S that crb_hessian_accumulate maintains (the 256 x 256 tiles on and above the
+ * diagonal) as one contiguous buffer of crb_hessian_packed_floats(C) floats and back: what a sum of
+ * partial Hessians over several GPUs has to move (about half of C * C).  No counterpart in the
+ * single-device reference; the sum itself stands for the accumulation over all sequences in
+ * bigptq.py:50-53.  The packed buffer must be 16-byte aligned.                                  */
+size_t crb_hessian_packed_floats(int C);
+int crb_hessian_pack(const float *S_dev, int C, float *packed_dev, void *stream);
+int crb_hessian_unpack(const float *packed_dev, int C, float *S_dev, void *stream);
+
 /* ---- (2) damping + inverse factor ----------------------------------------------
  * Replaces bigptq.py:101-129: dead columns (diag == 0 -> H[d,d] = 1, W[:,d] = 0),
  * H += percdamp * mean(diag) * I, then U = chol(inv(H), upper) written over H.

@@ -559,3 +559,25 @@ def test_magnitude_metric_linear_matches_reference(linear, variants, tech):
     e_dev, e_ref = O.output_error(W, Wq, X), O.output_error(W, ref_W, X)
     assert abs(e_dev - e_ref) <= Hh.OUTPUT_ERR_RTOL * e_ref, (tech, e_dev, e_ref)
     assert abs(info["error"] - float(variants[f"mag_{tech}_error"])) <= Hh.OUTPUT_ERR_RTOL * info["error"]
+
+
+@pytest.mark.parametrize("C", (128, 384, 1024))
+def test_hessian_pack_round_trip(ops, C):
+    """The packed form holds exactly the tiles the accumulation maintains; summing packed partial
+    sums and unpacking equals summing the matrices."""
+    g = torch.Generator().manual_seed(C)
+    parts = [torch.randn(C, C, generator=g).to(DEV) for _ in range(3)]
+    n = ops.hessian_packed_floats(C)
+    bands = torch.arange(C) // 256 * 256
+    keep = (torch.arange(C)[None, :] >= bands[:, None]).to(DEV)             # row r keeps columns from its band on
+    assert n == int(keep.sum())
+    total = torch.zeros(n, device=DEV)
+    for p in parts:
+        buf = torch.empty(n, device=DEV)
+        ops.hessian_pack(p, buf)
+        assert torch.equal(buf, p[keep])
+        total += buf
+    out = torch.full((C, C), -7.0, device=DEV)
+    ops.hessian_unpack(total, out)
+    expect = torch.where(keep, parts[0] + parts[1] + parts[2], torch.full_like(out, -7.0))
+    assert torch.equal(out, expect)
