@@ -299,6 +299,7 @@ def run_ours(args):
     errors = []
 
     def barrier():
+        torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
@@ -308,6 +309,10 @@ def run_ours(args):
         nonlocal dev_in, dev_out
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
         with crun._Resident(layers[i], dev) as layer:
+            # this arm times a step whose weights and activations are resident: all ranks start it
+            # together, so that one rank's slower weight copy between two steps (untimed) does not
+            # show up as waiting time inside the next step's collectives on the other ranks
+            barrier()
             ev[0].record()
             with torch.no_grad():
                 errs = crun.quantize_layer(layer, i, dev_in, dev_out, layer_kwargs, qargs, dev,

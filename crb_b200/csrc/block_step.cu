@@ -11,10 +11,10 @@
 // Kernel sequence per block (stream ordered, no host synchronisation, no kernel waits on
 // another CTA: grid-wide decisions are taken by whichever CTA finishes last):
 //   k_metric_colscore  M, column scores, top-50 columns
+//   k_sort_rows        every metric row sorted (bitonic network) with its column ids
 //   k_salient_search_sorted  49 candidates x rows from prefix sums of the sorted rows, first strict minimum
 //   k_select_l1/l2/l3  exact radix selection (15+9+7 bits) of the 162 order statistics that
 //                      numpy.quantile(method="linear") interpolates between
-//   k_sort_rows        every metric row sorted (bitonic network), for the split search
 //   k_split_search_sorted  81 candidates x rows from prefix sums of the sorted rows
 //   k_finalize         masks, the technique's binarizer per group, Q, Err, Losses
 #include <math.h>
@@ -127,6 +127,85 @@ static size_t carve_block_ws(void* base, int R, BlockWs* ws) {
 }
 
 // ---------------------------------------------------------------------------------------
+// Row sort: every row of the metric sorted ascending together with the column of each value
+// (bitonic network, one warp per row, four elements per lane; ties keep the lower column first).
+// The sorted rows turn the candidate evaluations of both searches into prefix-sum lookups.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned ordered_key(float v) {
+    const unsigned b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(unsigned k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+__device__ __forceinline__ bool key_less(unsigned ka, int ca, unsigned kb, int cb) {
+    return (ka < kb) || (ka == kb && ca < cb);
+}
+
+__device__ __forceinline__ void sort_metric_row(const float* __restrict__ M, int row, float* __restrict__ sv,
+                                                unsigned char* __restrict__ sc, int lane) {
+    unsigned k[4];
+    int c[4];
+    {
+        const float4 v = *reinterpret_cast<const float4*>(M + (int64_t)row * kBlock + 4 * lane);
+        // keys that order like the values, negative ones included (the magnitude metric is the
+        // signed weight): flip all bits of a negative number, the sign bit of the others
+        k[0] = ordered_key(v.x); k[1] = ordered_key(v.y); k[2] = ordered_key(v.z); k[3] = ordered_key(v.w);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) c[q] = 4 * lane + q;
+    }
+#pragma unroll
+    for (int size = 2; size <= kBlock; size <<= 1) {
+#pragma unroll
+        for (int j = size >> 1; j >= 1; j >>= 1) {
+            if (j >= 4) {
+                const int lj = j >> 2;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int e = 4 * lane + q;
+                    const unsigned ok = __shfl_xor_sync(0xffffffffu, k[q], lj);
+                    const int oc = __shfl_xor_sync(0xffffffffu, c[q], lj);
+                    const bool up = (e & size) == 0;            // ascending segment
+                    const bool lower_half = (e & j) == 0;       // this element keeps the smaller key
+                    const bool mine_less = key_less(k[q], c[q], ok, oc);
+                    const bool keep = (lower_half == up) ? mine_less : !mine_less;
+                    if (!keep) { k[q] = ok; c[q] = oc; }
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int qq = q ^ j;
+                    if (qq > q) {
+                        const int e = 4 * lane + q;
+                        const bool up = (e & size) == 0;
+                        const bool in_order = key_less(k[q], c[q], k[qq], c[qq]);
+                        if (in_order != up) {
+                            const unsigned tk = k[q]; k[q] = k[qq]; k[qq] = tk;
+                            const int tc = c[q]; c[q] = c[qq]; c[qq] = tc;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    *reinterpret_cast<float4*>(sv + (int64_t)row * kBlock + 4 * lane) =
+        make_float4(key_value(k[0]), key_value(k[1]), key_value(k[2]), key_value(k[3]));
+    *reinterpret_cast<uchar4*>(sc + (int64_t)row * kBlock + 4 * lane) =
+        make_uchar4((unsigned char)c[0], (unsigned char)c[1], (unsigned char)c[2], (unsigned char)c[3]);
+}
+
+// One warp per row, eight rows per CTA: many small CTAs, because a single row's network is a
+// chain of dependent shuffles (fused into the metric kernel, whose grid is at most one CTA per SM,
+// the sort took 10 us longer per block at 4096 rows and 70 us longer at 16384).
+__global__ void __launch_bounds__(256)
+k_sort_rows(const float* __restrict__ M, int R, float* __restrict__ sv, unsigned char* __restrict__ sc) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + warp;
+    chain_wait();
+    if (row < R) sort_metric_row(M, row, sv, sc, lane);
+}
+
+// ---------------------------------------------------------------------------------------
 // K1: metric, column scores, top-50 columns                     (structure.py:10, autosearch.py:37-42)
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
@@ -179,6 +258,7 @@ k_metric_colscore(const float* __restrict__ W, int R, int64_t ldw, int col0,
     e2 = warp_sum_d(e2);
     if (lane == 0) s_e[warp] = e2;
     if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(status, CRB_FLAG_NONFINITE);
+
     // sum the 4 rows of the warp, then the 8 warps, in double
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
@@ -601,78 +681,6 @@ k_select_l3(const float* __restrict__ M, int R, const unsigned char* __restrict_
 }
 
 // ---------------------------------------------------------------------------------------
-// Row sort: every row of the metric sorted ascending together with the column of each value
-// (bitonic network, one warp per row, four elements per lane; ties keep the lower column first).
-// The sorted rows turn the candidate evaluations of the split search into prefix-sum lookups.
-// ---------------------------------------------------------------------------------------
-__device__ __forceinline__ unsigned ordered_key(float v) {
-    const unsigned b = __float_as_uint(v);
-    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-}
-__device__ __forceinline__ float key_value(unsigned k) {
-    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
-}
-__device__ __forceinline__ bool key_less(unsigned ka, int ca, unsigned kb, int cb) {
-    return (ka < kb) || (ka == kb && ca < cb);
-}
-
-__global__ void __launch_bounds__(256)
-k_sort_rows(const float* __restrict__ M, int R, float* __restrict__ sv, unsigned char* __restrict__ sc) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * 8 + warp;
-    chain_wait();
-    if (row >= R) return;
-    unsigned k[4];
-    int c[4];
-    {
-        const float4 v = *reinterpret_cast<const float4*>(M + (int64_t)row * kBlock + 4 * lane);
-        // keys that order like the values, negative ones included (the magnitude metric is the
-        // signed weight): flip all bits of a negative number, the sign bit of the others
-        k[0] = ordered_key(v.x); k[1] = ordered_key(v.y); k[2] = ordered_key(v.z); k[3] = ordered_key(v.w);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) c[q] = 4 * lane + q;
-    }
-#pragma unroll
-    for (int size = 2; size <= kBlock; size <<= 1) {
-#pragma unroll
-        for (int j = size >> 1; j >= 1; j >>= 1) {
-            if (j >= 4) {
-                const int lj = j >> 2;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int e = 4 * lane + q;
-                    const unsigned ok = __shfl_xor_sync(0xffffffffu, k[q], lj);
-                    const int oc = __shfl_xor_sync(0xffffffffu, c[q], lj);
-                    const bool up = (e & size) == 0;            // ascending segment
-                    const bool lower_half = (e & j) == 0;       // this element keeps the smaller key
-                    const bool mine_less = key_less(k[q], c[q], ok, oc);
-                    const bool keep = (lower_half == up) ? mine_less : !mine_less;
-                    if (!keep) { k[q] = ok; c[q] = oc; }
-                }
-            } else {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int qq = q ^ j;
-                    if (qq > q) {
-                        const int e = 4 * lane + q;
-                        const bool up = (e & size) == 0;
-                        const bool in_order = key_less(k[q], c[q], k[qq], c[qq]);
-                        if (in_order != up) {
-                            const unsigned tk = k[q]; k[q] = k[qq]; k[qq] = tk;
-                            const int tc = c[q]; c[q] = c[qq]; c[qq] = tc;
-                        }
-                    }
-                }
-            }
-        }
-    }
-    *reinterpret_cast<float4*>(sv + (int64_t)row * kBlock + 4 * lane) =
-        make_float4(key_value(k[0]), key_value(k[1]), key_value(k[2]), key_value(k[3]));
-    *reinterpret_cast<uchar4*>(sc + (int64_t)row * kBlock + 4 * lane) =
-        make_uchar4((unsigned char)c[0], (unsigned char)c[1], (unsigned char)c[2], (unsigned char)c[3]);
-}
-
-// ---------------------------------------------------------------------------------------
 // K6: split search on sorted rows                                      (autosearch.py:72-81)
 //
 // Per row the non-salient values are kept sorted with float64 prefix sums of x and x^2.  A split
@@ -1015,14 +1023,31 @@ __device__ __forceinline__ double salient_candidate_err(const float* v, const do
 
 // Which candidates (salient counts) a thread evaluates: thread t works on row t % 16 of the tile
 // with schedule slot t / 16.  A candidate costs about i + 8 units; the slots are balanced
-// (longest-processing-time order), 94..108 units each instead of 177 for a plain round robin.
+// (longest-processing-time order).  With 32 slots (512 threads, at most two candidates per
+// thread: 51..57 units) a CTA has twice the warps to hide the latency of the dependent
+// shared-memory searches than with 16 slots (256 threads, 94..108 units per thread).
+#ifndef CRB_SAL_SLOTS
+#define CRB_SAL_SLOTS 32
+#endif
+constexpr int kSalSlots = CRB_SAL_SLOTS;
+constexpr int kSalThreads = kSalRows * kSalSlots;
+#if CRB_SAL_SLOTS == 16
 __constant__ unsigned char c_sal_sched[16][4] = {
     {49, 18, 17, 0}, {48, 19, 16, 0}, {47, 20, 15, 0}, {46, 21, 14, 0}, {45, 22, 13, 0}, {44, 23, 12, 0},
     {43, 24, 11, 0}, {42, 25, 10, 0}, {41, 26, 9, 0}, {40, 27, 8, 0}, {39, 28, 7, 0}, {38, 29, 6, 0},
     {37, 30, 5, 0}, {36, 31, 4, 0}, {35, 32, 3, 0}, {34, 33, 2, 1}};
-static_assert(kSalRows == 16 && kSalCand == 49, "c_sal_sched is laid out for 16 rows x 16 slots and 49 candidates");
+#else
+__constant__ unsigned char c_sal_sched[32][4] = {
+    {49, 0, 0, 0}, {48, 0, 0, 0}, {47, 0, 0, 0}, {46, 0, 0, 0}, {45, 0, 0, 0}, {44, 0, 0, 0}, {43, 0, 0, 0},
+    {42, 0, 0, 0}, {41, 0, 0, 0}, {40, 0, 0, 0}, {39, 0, 0, 0}, {38, 0, 0, 0}, {37, 0, 0, 0}, {36, 0, 0, 0},
+    {35, 0, 0, 0}, {34, 1, 0, 0}, {33, 2, 0, 0}, {32, 3, 0, 0}, {31, 4, 0, 0}, {30, 5, 0, 0}, {29, 6, 0, 0},
+    {28, 7, 0, 0}, {27, 8, 0, 0}, {26, 9, 0, 0}, {25, 10, 0, 0}, {24, 11, 0, 0}, {23, 12, 0, 0}, {22, 13, 0, 0},
+    {21, 14, 0, 0}, {20, 15, 0, 0}, {19, 16, 0, 0}, {18, 17, 0, 0}};
+#endif
+static_assert(kSalRows == 16 && kSalCand == 49 && (kSalSlots == 16 || kSalSlots == 32),
+              "c_sal_sched is laid out for 16 rows x 16 or 32 slots and 49 candidates");
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kSalThreads)
 k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __restrict__ sc, int R,
                         int rows_per_cta, const unsigned char* __restrict__ rank,
                         unsigned long long* __restrict__ acc, const double* __restrict__ fx,
@@ -1047,7 +1072,7 @@ k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __res
     const int row_base = blockIdx.x * rows_per_cta;
     for (int p0 = 0; p0 < rows_per_cta; p0 += kSalRows) {
         // ---- phase A: one warp per row: sorted values, float64 prefix sums, top-column values ----
-        for (int r = warp; r < kSalRows; r += 8) {
+        for (int r = warp; r < kSalRows; r += kSalThreads / 32) {
             const int row = row_base + p0 + r;
             float x[4] = {0.f, 0.f, 0.f, 0.f};
             uchar4 c = make_uchar4(0, 0, 0, 0);
@@ -1512,7 +1537,7 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
     CRB_LAUNCHED();
     // K2: salient-count search on the sorted rows (<= kMaxTiles CTAs)
     const int rows_sal = kSalRows * ceil_div(R, kSalRows * kMaxTiles);
-    launch_chained(k_salient_search_sorted, ceil_div(R, rows_sal), 256, kSalSmem, st,
+    launch_chained(k_salient_search_sorted, ceil_div(R, rows_sal), kSalThreads, kSalSmem, st,
                    ws.sv, ws.sc, R, rows_sal, ws.rank, ws.acc, ws.fx, ws.counters, ws.sel, tr, ws.status);
     CRB_LAUNCHED();
     // K3-K5

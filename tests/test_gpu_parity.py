@@ -212,7 +212,7 @@ def test_trailing_update_matches_fp32_matmul(ops):
         assert torch.equal(Wd.cpu()[:, :ed], W[:, :ed])
 
 
-@pytest.mark.parametrize("C", (128, 384, 1024))
+@pytest.mark.parametrize("C", (128, 384, 1024, 4096))      # 4096: four outer panels, two levels of merges across them
 def test_factor_matches_reference_chain(ops, C):
     g = torch.Generator().manual_seed(C)
     X = torch.randn(4 * C, C, generator=g)
