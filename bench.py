@@ -400,6 +400,12 @@ def run_ours(args):
     roof = hessian_roofline(dev, d, f, args, peaks)
     roof_extra = extra_rooflines(dev, d, f, args.technique, peaks) if rank == 0 else None
 
+    ref_gpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            ref_gpu = reference_eager_on_gpu(dev, args.technique)
+        except Exception as exc:            # a baseline, not the product: report and go on
+            ref_gpu = {"unavailable": f"{type(exc).__name__}: {exc}"}
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         info = cpu_reference_sample(args.technique)
@@ -418,7 +424,7 @@ def run_ours(args):
                                 "re-propagation pass) and the quantized weights and the layer outputs are copied "
                                 "out; copies overlap compute"},
                 "gpu_launches": launches, "clocks": clocks, "roofline": roof, "roofline_extra": roof_extra,
-                "cpu_baseline": cpu,
+                "cpu_baseline": cpu, "reference_eager_gpu": ref_gpu,
                 "phases_ms_per_step": {k: v / args.steps for k, v in phases.items()},
                 "per_rank_ms_per_step": per_rank,
                 "block_error_sum_per_layer": err_sum / args.steps, "wall_clock_s_timed_region": wall,
@@ -464,6 +470,52 @@ def hessian_roofline(dev, d, f, args, peaks):
             "work": f"T={T} tokens x C={f}: {issued:.3e} flop issued on upper-triangle tiles "
                     f"({algorithmic:.3e} for the full product the reference computes)",
             "peak_source": f"{peaks['source']} cuBLAS bf16 burst"}
+
+
+def reference_eager_on_gpu(dev, technique):
+    """The reference's own eager-PyTorch path on this GPU, as the stronger baseline for the block
+    loop: `BRAGPTQ.fasterquant` of the reference (oracle/_ref) on one 4096 x 4096 linear with an
+    injected Hessian, next to this library on the very same inputs.  Rank 0, one GPU, bounded (the
+    reference launches several thousand small kernels and synchronises some hundred times per block).
+    """
+    from oracle import build_ref
+    if not build_ref.available():
+        return None
+    import contextlib
+    import io
+    from crb_b200 import BRAGPTQ, Binarization
+    bigptq, binary, _ = build_ref.load()
+    rows = cols = 4096
+    g = torch.Generator(device=dev).manual_seed(5)
+    W = torch.randn(rows, cols, generator=g, device=dev) * 0.02
+    X = torch.randn(4 * SEQLEN, cols, generator=g, device=dev)
+    H = (X.t() @ X) * (2.0 / 4)
+    out = {"linear": f"{rows}x{cols}", "technique": technique}
+    for name in ("ours", "reference"):
+        lin = torch.nn.Linear(cols, rows, bias=False, device=dev, dtype=torch.float16)
+        lin.weight.data = W.half()
+        if name == "ours":
+            q = BRAGPTQ(lin, Binarization(lin.weight, method=technique, groupsize=128), salient_metric="hessian")
+            q.verbose = False
+        else:
+            q = bigptq.BRAGPTQ(lin, binary.Binarization(lin.weight, method=technique, groupsize=128), "hessian")
+        reps = 3 if name == "ours" else 1
+        best = None
+        for _ in range(reps):
+            lin.weight.data = W.half()
+            q.H = H.clone()
+            q.nsamples = 4
+            torch.cuda.synchronize()
+            t0 = time.time()
+            with contextlib.redirect_stdout(io.StringIO()):
+                info = q.fasterquant(blocksize=128, percdamp=0.01)
+            torch.cuda.synchronize()
+            dt = time.time() - t0
+            best = dt if best is None else min(best, dt)
+        out[f"{name}_fasterquant_s"] = best
+        out[f"{name}_error"] = float(info["error"])
+    out["speedup"] = out["reference_fasterquant_s"] / out["ours_fasterquant_s"]
+    return out
 
 
 def _time_ms(fn, reps, warm=3):
