@@ -1348,7 +1348,13 @@ __device__ __forceinline__ void group_order2(const float (&w)[16], const bool (&
 // K7: final masks, the technique's binarizer on the three groups, Q / Err / Losses
 // (bigptq.py:246-263)
 // ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
+// kDefaultOrders: the reference's default orders = (1, 1, 2), compiled without the per-group
+// order dispatch (the generic form costs about a third more time in this kernel).
+// kMinCtas: 1 lets the compiler keep everything in registers (190 per thread, one CTA per SM):
+// best while the grid has at most one CTA per SM anyway (up to 4736 rows); 2 caps the registers at
+// 128 (a few spills) so that two CTAs share an SM: 3 % faster per block at 16384 rows.
+template <bool kDefaultOrders, int kMinCtas>
+__global__ void __launch_bounds__(256, kMinCtas)
 k_finalize(float* __restrict__ W, int R, int64_t ldw, int col0, const float* __restrict__ U,
            int64_t ldu, const unsigned char* __restrict__ rank, const int* __restrict__ sel,
            const float* __restrict__ pvals, int technique, int orders, int metric, float lam, float corr_damp,
@@ -1390,6 +1396,23 @@ k_finalize(float* __restrict__ W, int R, int64_t ldw, int col0, const float* __r
     // `orders`, 112 = (low 1, mid 1, salient 2), the only combination whose scales fit `sc`
 #pragma unroll
     for (int k = 0; k < 8; ++k) sc[k] = 0.f;
+    if (kDefaultOrders) {
+#pragma unroll
+        for (int gi = 0; gi < 2; ++gi) {
+            bool in[16];
+            int n = 0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { in[j] = grp[j] == gi; n += in[j]; }
+            n = red8i(n);
+            group_order1(w, in, n, q, b1, &sc[2 * gi], &sc[2 * gi + 1]);
+        }
+        bool in[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) in[j] = grp[j] == 2;
+        float s2[4];
+        group_order2(w, in, isal, technique, lam, corr_damp, q, b1, b2, s2);
+        sc[4] = s2[0]; sc[5] = s2[1]; sc[6] = s2[2]; sc[7] = s2[3];
+    } else
 #pragma unroll 1
     for (int gi = 0; gi < 3; ++gi) {
         const int order = (gi == 0) ? orders / 100 : ((gi == 1) ? (orders / 10) % 10 : orders % 10);
@@ -1556,7 +1579,11 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
                    ws.sv, ws.sc, R, rows_sp, metric, ws.rank, ws.pvals, ws.acc, ws.fx, ws.counters, ws.sel, ws.pvals, tr, ws.status);
     CRB_LAUNCHED();
     // K7
-    launch_chained(k_finalize, ceil_div(R, 32), 256, 0, st, W, R, ldw, col0, U, ldu, ws.rank, ws.sel, ws.pvals, technique,
+    const bool one_wave = ceil_div(R, 32) <= 148;
+    auto* finalize = orders == CRB_ORDERS_DEFAULT ? (one_wave ? k_finalize<true, 1> : k_finalize<true, 2>)
+                                                  : (one_wave ? k_finalize<false, 1> : k_finalize<false, 2>);
+    launch_chained(finalize, ceil_div(R, 32), 256, 0, st,
+                   W, R, ldw, col0, U, ldu, ws.rank, ws.sel, ws.pvals, technique,
                    orders, metric, lam, corr_damp, Err, ld_err, Losses, codes, ld_codes, scales);
     CRB_LAUNCHED();
     return CRB_OK;

@@ -91,6 +91,7 @@ __global__ void k_reverse_copy(const float* __restrict__ H, int C, const float* 
 constexpr int kDiagThreads = 512;
 constexpr int kDiagPitch = FB + 4;                 // 132 floats: rows 16-byte aligned, 8 rows hit 8 bank groups
 constexpr int kDiagTmpPitch = 68;
+constexpr int kLiPitch = 20;                       // rows of the 16x16 inverse: 16-byte aligned
 constexpr int kDiagSmemFloats = 2 * FB * kDiagPitch + 64 * kDiagTmpPitch;
 
 // C[i][j] (+)= sign * sum_k A[i][k] * B[k][j] for an n x n block, 4x4 outputs per thread, rows and
@@ -133,16 +134,26 @@ __device__ __forceinline__ void smem_gemm_nn(const float* A, int lda, const floa
     }
 }
 
+// Waits (bounded) until a shared-memory progress counter has reached `need`; false if it gave up.
+__device__ __forceinline__ bool wait_progress(volatile int* counter, int need) {
+    for (int it = 0; it < (1 << 22); ++it) {
+        if (*counter >= need) { __threadfence_block(); return true; }
+    }
+    return false;
+}
+
 __global__ void __launch_bounds__(kDiagThreads)
 k_chol_diag(float* __restrict__ Akk, int64_t ld, unsigned* status) {
     extern __shared__ __align__(16) float s_diag[];
     float* a = s_diag;                               // [128][132] the block, then its factor L
     float* x = s_diag + FB * kDiagPitch;             // [128][132] the inverse of L
     float* tmp = x + FB * kDiagPitch;                // [64][68]   products of phase 2
-    __shared__ float s_li[16][17];                   // inverse of the current 16x16 diagonal factor
-    __shared__ int s_bad;
+    __shared__ __align__(16) float s_li[2][16][kLiPitch];   // inverse of the 16x16 diagonal factor of step j (buffer j & 1)
+    __shared__ int s_bad, s_gave_up;
+    __shared__ volatile int s_crit;                  // steps whose diagonal block AND look-ahead row are done (warp 0)
+    __shared__ volatile int s_bulk;                  // steps whose panel + trailing update are done (warps 1..15)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid == 0) s_bad = 0;
+    if (tid == 0) { s_bad = 0; s_gave_up = 0; s_crit = 0; s_bulk = 0; }
     chain_wait();
     for (int e = tid; e < FB * FB; e += kDiagThreads) {
         a[(e >> 7) * kDiagPitch + (e & 127)] = Akk[(int64_t)(e >> 7) * ld + (e & 127)];
@@ -150,115 +161,207 @@ k_chol_diag(float* __restrict__ Akk, int64_t ld, unsigned* status) {
     }
     __syncthreads();
 
-    // ---------------- phase 1: blocked Cholesky ----------------
-    for (int c0 = 0; c0 < FB; c0 += 16) {
-        if (warp == 0) {
-            // 16x16 diagonal block: lane i (< 16) holds row i
-            const int i = lane & 15;
-            float d[16];
+    // ---------------- phase 1: blocked Cholesky, 16 columns per step ----------------
+    // The chain that cannot be parallelised is: factor and invert the 16x16 diagonal block of step
+    // j, then bring the NEXT 16 rows up to date so that step j + 1 can start.  Warp 0 does exactly
+    // that and runs ahead; warps 1..15 follow one step behind with the rest of step j's work (the
+    // panel below those 16 rows and the rank-16 update of the trailing block).  Every element still
+    // receives the same updates in the same order as in a step-by-step factorisation.
+    constexpr int kSteps = FB / 16;
+    constexpr int kBulkThreads = kDiagThreads - 32;
+    if (warp == 0) {
+        for (int j = 0; j < kSteps; ++j) {
+            const int c0 = 16 * j;
+            float (*li)[kLiPitch] = s_li[j & 1];
+            {
+                // 16x16 diagonal block: lane i (and its mirror i + 16) holds row i of the block and
+                // column i of the inverse.  This warp is the serial core of the whole factorisation
+                // (a timeline of the kernel showed 6 us per step here with IEEE sqrt and divisions
+                // in the chain against 1 us for everything else), so the pivots go through
+                // rsqrt + one Newton step and the inverse rows are produced inside the same loop:
+                // row k of the inverse only needs rows < k of it and row k of L, which is final once
+                // column k has been scaled, and its chain runs beside the update of the block.
+                const int i = lane & 15;
+                float d[16], xi[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) d[j] = a[(c0 + i) * kDiagPitch + c0 + j];
-            bool bad = false;
+                for (int jj = 0; jj < 16; jj += 4) {
+                    const float4 v = *reinterpret_cast<const float4*>(a + (c0 + i) * kDiagPitch + c0 + jj);
+                    d[jj] = v.x; d[jj + 1] = v.y; d[jj + 2] = v.z; d[jj + 3] = v.w;
+                }
+                bool bad = false;
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-                float piv = __shfl_sync(0xffffffffu, d[k], k);
-                if (!(piv > 0.f) || !isfinite(piv)) { bad = true; piv = 1.f; }
-                const float s = sqrtf(piv);
-                d[k] = (i == k) ? s : __fdiv_rn(d[k], s);            // column k of L (rows i >= k meaningful)
+                for (int k = 0; k < 16; ++k) {
+                    float piv = __shfl_sync(0xffffffffu, d[k], k);
+                    if (!(piv > 0.f) || !isfinite(piv)) { bad = true; piv = 1.f; }
+                    float rs = rsqrtf(piv);
+                    rs = rs * fmaf(-0.5f * piv * rs, rs, 1.5f);           // 1 / sqrt(piv) to float32 accuracy
+                    const float lik = (i == k) ? piv * rs : d[k] * rs;    // L[i][k] (rows i >= k meaningful)
+                    d[k] = lik;
+                    // row k of the inverse: X[k][i] = ((k == i) - sum_{m<k} L[k][m] X[m][i]) / L[k][k];
+                    // rows above the diagonal come out as exact zeros
+                    float acc = (k == i) ? 1.f : 0.f;
 #pragma unroll
-                for (int j = k + 1; j < 16; ++j) {
-                    const float ljk = __shfl_sync(0xffffffffu, d[k], j);
-                    d[j] = fmaf(-d[k], ljk, d[j]);                    // used only for i >= j
+                    for (int m = 0; m < k; ++m) acc = fmaf(-__shfl_sync(0xffffffffu, d[m], k), xi[m], acc);
+                    xi[k] = acc * rs;
+#pragma unroll
+                    for (int jj = k + 1; jj < 16; ++jj)
+                        d[jj] = fmaf(-lik, __shfl_sync(0xffffffffu, lik, jj), d[jj]);   // used only for i >= jj
+                }
+                if (bad && lane == 0) s_bad = 1;
+                if (lane < 16) {
+#pragma unroll
+                    for (int jj = 0; jj < 16; jj += 4)
+                        *reinterpret_cast<float4*>(a + (c0 + i) * kDiagPitch + c0 + jj) =
+                            make_float4(jj <= i ? d[jj] : 0.f, jj + 1 <= i ? d[jj + 1] : 0.f, jj + 2 <= i ? d[jj + 2] : 0.f,
+                                        jj + 3 <= i ? d[jj + 3] : 0.f);
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) {
+                        li[r][i] = xi[r];
+                        x[(c0 + r) * kDiagPitch + c0 + i] = xi[r];
+                    }
                 }
             }
-            if (bad && lane == 0) s_bad = 1;
-            // inverse of the 16x16 factor: lane j holds column j of the inverse
-            const int j = lane & 15;
-            float xi[16];
-#pragma unroll
-            for (int r = 0; r < 16; ++r) {
-                float acc = 0.f;
-#pragma unroll
-                for (int m = 0; m < r; ++m) {
-                    const float lrm = __shfl_sync(0xffffffffu, d[m], r);      // L[r][m]
-                    acc = fmaf(lrm, (m >= j) ? xi[m] : 0.f, acc);
-                }
-                const float lrr = __shfl_sync(0xffffffffu, d[r], r);
-                xi[r] = (r < j) ? 0.f : ((r == j) ? __fdiv_rn(1.f, lrr) : __fdiv_rn(-acc, lrr));
-            }
-            if (lane < 16) {
-#pragma unroll
-                for (int jj = 0; jj < 16; ++jj) a[(c0 + i) * kDiagPitch + c0 + jj] = (jj <= i) ? d[jj] : 0.f;
-#pragma unroll
-                for (int r = 0; r < 16; ++r) {
-                    s_li[r][j] = xi[r];
-                    x[(c0 + r) * kDiagPitch + c0 + j] = xi[r];
-                }
-            }
-        }
-        __syncthreads();
-        const int below = FB - c0 - 16;                                // rows under the diagonal block
-        if (below > 0) {
-            // panel: P[i][j] = sum_{m <= j} A[i][c0 + m] * Linv[j][m]; four lanes share a row
-            const int r = tid >> 2, jg = tid & 3;
-            float in[16];
-            const bool act = r < below;
-            float* prow = a + (c0 + 16 + (act ? r : 0)) * kDiagPitch + c0;
-#pragma unroll
-            for (int m = 0; m < 16; ++m) in[m] = prow[m];
             __syncwarp();
-            if (act) {
-#pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
-                    const int j = 4 * jg + jj;
-                    float acc = 0.f;
-#pragma unroll
-                    for (int m = 0; m < 16; ++m) acc = fmaf(in[m], (m <= j) ? s_li[j][m] : 0.f, acc);
-                    prow[j] = acc;
-                }
-            }
-            __syncthreads();
-            // trailing update: A[i][j] -= sum_m P[i][m] P[j][m] for the rows / columns below the panel
-            const int q = below >> 2;
-            const float* P = a + (c0 + 16) * kDiagPitch + c0;           // P[i][m]
-            float* T = a + (c0 + 16) * kDiagPitch + c0 + 16;            // trailing block, T[i][j]
-            for (int idx = tid; idx < q * q; idx += kDiagThreads) {
-                const int ti = idx % q, tj = idx / q;
-                if (ti + 3 * q < 4 * tj) continue;                      // tile entirely above the diagonal
-                float acc[4][4];
-#pragma unroll
-                for (int aa = 0; aa < 4; ++aa)
-#pragma unroll
-                    for (int bb = 0; bb < 4; ++bb) acc[aa][bb] = 0.f;
+            if (j + 1 < kSteps) {
+                // the next 16 rows have received every update of the steps before j once the other
+                // warps are through with step j - 1
+                if (lane == 0 && !wait_progress(&s_bulk, j)) s_gave_up = 1;
+                __syncwarp();
+                // look-ahead: P = A[next 16 rows, this step's columns] * Linv^T (two lanes per row,
+                // eight columns each; Linv[col][m] is zero for m > col), then the next diagonal
+                // block -= P P^T
+                const int r = lane >> 1, h = lane & 1;
+                float* prow = a + (c0 + 16 + r) * kDiagPitch + c0;
+                float in[16];
 #pragma unroll
                 for (int m = 0; m < 16; m += 4) {
-                    float4 pi[4], pj[4];
+                    const float4 v = *reinterpret_cast<const float4*>(prow + m);
+                    in[m] = v.x; in[m + 1] = v.y; in[m + 2] = v.z; in[m + 3] = v.w;
+                }
+                __syncwarp();
+                float pout[8];
 #pragma unroll
-                    for (int aa = 0; aa < 4; ++aa) pi[aa] = *reinterpret_cast<const float4*>(P + (ti + aa * q) * kDiagPitch + m);
+                for (int jj = 0; jj < 8; ++jj) {
+                    const float4* lrow = reinterpret_cast<const float4*>(&li[8 * h + jj][0]);
+                    float acc = 0.f;
 #pragma unroll
-                    for (int bb = 0; bb < 4; ++bb) pj[bb] = *reinterpret_cast<const float4*>(P + (4 * tj + bb) * kDiagPitch + m);
+                    for (int m4 = 0; m4 < 4; ++m4) {
+                        const float4 v = lrow[m4];
+                        acc = fmaf(in[4 * m4], v.x, acc); acc = fmaf(in[4 * m4 + 1], v.y, acc);
+                        acc = fmaf(in[4 * m4 + 2], v.z, acc); acc = fmaf(in[4 * m4 + 3], v.w, acc);
+                    }
+                    pout[jj] = acc;
+                }
+                *reinterpret_cast<float4*>(prow + 8 * h) = make_float4(pout[0], pout[1], pout[2], pout[3]);
+                *reinterpret_cast<float4*>(prow + 8 * h + 4) = make_float4(pout[4], pout[5], pout[6], pout[7]);
+                __syncwarp();
+                const float* P = a + (c0 + 16) * kDiagPitch + c0;        // P[i][m], 16 x 16
+                float* D = a + (c0 + 16) * kDiagPitch + c0 + 16;         // the next diagonal block
+                float pr[16];
+#pragma unroll
+                for (int m = 0; m < 16; m += 4) {
+                    const float4 v = *reinterpret_cast<const float4*>(P + r * kDiagPitch + m);
+                    pr[m] = v.x; pr[m + 1] = v.y; pr[m + 2] = v.z; pr[m + 3] = v.w;
+                }
+                float upd[8];
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) {
+                    const float4* crow = reinterpret_cast<const float4*>(P + (8 * h + jj) * kDiagPitch);
+                    float acc = 0.f;
+#pragma unroll
+                    for (int m4 = 0; m4 < 4; ++m4) {
+                        const float4 v = crow[m4];
+                        acc = fmaf(pr[4 * m4], v.x, acc); acc = fmaf(pr[4 * m4 + 1], v.y, acc);
+                        acc = fmaf(pr[4 * m4 + 2], v.z, acc); acc = fmaf(pr[4 * m4 + 3], v.w, acc);
+                    }
+                    upd[jj] = acc;
+                }
+                float4* dst = reinterpret_cast<float4*>(D + r * kDiagPitch + 8 * h);
+                float4 o0 = dst[0], o1 = dst[1];
+                o0.x -= upd[0]; o0.y -= upd[1]; o0.z -= upd[2]; o0.w -= upd[3];
+                o1.x -= upd[4]; o1.y -= upd[5]; o1.z -= upd[6]; o1.w -= upd[7];
+                dst[0] = o0; dst[1] = o1;
+            }
+            __threadfence_block();
+            __syncwarp();
+            if (lane == 0) s_crit = j + 1;
+        }
+    } else {
+        const int bt = tid - 32;                                       // 0 .. 479
+        for (int j = 0; j + 1 < kSteps; ++j) {
+            const int c0 = 16 * j;
+            if (lane == 0 && !wait_progress(&s_crit, j + 1)) s_gave_up = 1;
+            __syncwarp();
+            __threadfence_block();
+            const float (*li)[kLiPitch] = s_li[j & 1];
+            const int below = FB - c0 - 32;                            // rows under the look-ahead rows
+            if (below > 0) {
+                // panel: P[i][col] = sum_{m <= col} A[i][c0 + m] * Linv[col][m]; four threads share a row
+                const int r = bt >> 2, jg = bt & 3;
+                const bool act = r < below;
+                float* prow = a + (c0 + 32 + (act ? r : 0)) * kDiagPitch + c0;
+                float in[16];
+#pragma unroll
+                for (int m = 0; m < 16; ++m) in[m] = prow[m];
+                asm volatile("bar.sync 1, %0;" ::"n"(kBulkThreads) : "memory");
+                if (act) {
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) {
+                        const int col = 4 * jg + jj;
+                        float acc = 0.f;
+#pragma unroll
+                        for (int m = 0; m < 16; ++m) acc = fmaf(in[m], (m <= col) ? li[col][m] : 0.f, acc);
+                        prow[col] = acc;
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kBulkThreads) : "memory");
+                // trailing update: rows from c0 + 32 on, columns from c0 + 16 on (the first 16 of them
+                // pair with the look-ahead rows of warp 0):  A[i][c] -= sum_m P[i][m] P[c][m]
+                const int qi = below >> 2, qj = (below + 16) >> 2;
+                const float* P = a + (c0 + 16) * kDiagPitch + c0;       // P of row (c0 + 16 + k) at P[k]
+                float* T = a + (c0 + 32) * kDiagPitch + c0 + 16;        // T[i][c]: row c0 + 32 + i, column c0 + 16 + c
+                for (int idx = bt; idx < qi * qj; idx += kBulkThreads) {
+                    const int ti = idx % qi, tj = idx / qi;
+                    if (16 + ti + 3 * qi < 4 * tj) continue;            // tile entirely above the diagonal
+                    float acc[4][4];
 #pragma unroll
                     for (int aa = 0; aa < 4; ++aa)
 #pragma unroll
-                        for (int bb = 0; bb < 4; ++bb) {
-                            acc[aa][bb] = fmaf(pi[aa].x, pj[bb].x, acc[aa][bb]);
-                            acc[aa][bb] = fmaf(pi[aa].y, pj[bb].y, acc[aa][bb]);
-                            acc[aa][bb] = fmaf(pi[aa].z, pj[bb].z, acc[aa][bb]);
-                            acc[aa][bb] = fmaf(pi[aa].w, pj[bb].w, acc[aa][bb]);
-                        }
-                }
+                        for (int bb = 0; bb < 4; ++bb) acc[aa][bb] = 0.f;
 #pragma unroll
-                for (int aa = 0; aa < 4; ++aa) {
-                    float4* dst = reinterpret_cast<float4*>(T + (ti + aa * q) * kDiagPitch + 4 * tj);
-                    float4 o = *dst;
-                    o.x -= acc[aa][0]; o.y -= acc[aa][1]; o.z -= acc[aa][2]; o.w -= acc[aa][3];
-                    *dst = o;
+                    for (int m = 0; m < 16; m += 4) {
+                        float4 pi[4], pj[4];
+#pragma unroll
+                        for (int aa = 0; aa < 4; ++aa) pi[aa] = *reinterpret_cast<const float4*>(P + (16 + ti + aa * qi) * kDiagPitch + m);
+#pragma unroll
+                        for (int bb = 0; bb < 4; ++bb) pj[bb] = *reinterpret_cast<const float4*>(P + (4 * tj + bb) * kDiagPitch + m);
+#pragma unroll
+                        for (int aa = 0; aa < 4; ++aa)
+#pragma unroll
+                            for (int bb = 0; bb < 4; ++bb) {
+                                acc[aa][bb] = fmaf(pi[aa].x, pj[bb].x, acc[aa][bb]);
+                                acc[aa][bb] = fmaf(pi[aa].y, pj[bb].y, acc[aa][bb]);
+                                acc[aa][bb] = fmaf(pi[aa].z, pj[bb].z, acc[aa][bb]);
+                                acc[aa][bb] = fmaf(pi[aa].w, pj[bb].w, acc[aa][bb]);
+                            }
+                    }
+#pragma unroll
+                    for (int aa = 0; aa < 4; ++aa) {
+                        float4* dst = reinterpret_cast<float4*>(T + (ti + aa * qi) * kDiagPitch + 4 * tj);
+                        float4 o = *dst;
+                        o.x -= acc[aa][0]; o.y -= acc[aa][1]; o.z -= acc[aa][2]; o.w -= acc[aa][3];
+                        *dst = o;
+                    }
                 }
+                asm volatile("bar.sync 1, %0;" ::"n"(kBulkThreads) : "memory");
             }
-            __syncthreads();
+            __threadfence_block();
+            if (bt == 0) s_bulk = j + 1;
         }
     }
+    __syncthreads();
     if (tid == 0 && s_bad) atomicOr(status, CRB_FLAG_BAD_PIVOT);
+    if (tid == 0 && s_gave_up) atomicOr(status, CRB_FLAG_WAIT_LIMIT);
 
     // ---------------- phase 2: inverse by merging diagonal blocks of size s = 16, 32, 64 ----------------
     for (int s = 16; s < FB; s <<= 1) {
