@@ -155,9 +155,20 @@ k_chol_diag(float* __restrict__ Akk, int64_t ld, unsigned* status) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) { s_bad = 0; s_gave_up = 0; s_crit = 0; s_bulk = 0; }
     chain_wait();
-    for (int e = tid; e < FB * FB; e += kDiagThreads) {
-        a[(e >> 7) * kDiagPitch + (e & 127)] = Akk[(int64_t)(e >> 7) * ld + (e & 127)];
-        x[(e >> 7) * kDiagPitch + (e & 127)] = 0.f;
+    {
+        // 16-byte loads, all eight of a thread in flight before the first store
+        float4 v[FB * FB / 4 / kDiagThreads];
+#pragma unroll
+        for (int u = 0; u < FB * FB / 4 / kDiagThreads; ++u) {
+            const int e = 4 * (tid + u * kDiagThreads);
+            v[u] = *reinterpret_cast<const float4*>(Akk + (int64_t)(e >> 7) * ld + (e & 127));
+        }
+#pragma unroll
+        for (int u = 0; u < FB * FB / 4 / kDiagThreads; ++u) {
+            const int e = 4 * (tid + u * kDiagThreads);
+            *reinterpret_cast<float4*>(a + (e >> 7) * kDiagPitch + (e & 127)) = v[u];
+            *reinterpret_cast<float4*>(x + (e >> 7) * kDiagPitch + (e & 127)) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
     }
     __syncthreads();
 
@@ -378,7 +389,12 @@ k_chol_diag(float* __restrict__ Akk, int64_t ld, unsigned* status) {
                            x + (b0 + s) * kDiagPitch + b0, kDiagPitch, s, tg, gthreads);
         __syncthreads();
     }
-    for (int e = tid; e < FB * FB; e += kDiagThreads) Akk[(int64_t)(e >> 7) * ld + (e & 127)] = x[(e >> 7) * kDiagPitch + (e & 127)];
+#pragma unroll
+    for (int u = 0; u < FB * FB / 4 / kDiagThreads; ++u) {
+        const int e = 4 * (tid + u * kDiagThreads);
+        *reinterpret_cast<float4*>(Akk + (int64_t)(e >> 7) * ld + (e & 127)) =
+            *reinterpret_cast<const float4*>(x + (e >> 7) * kDiagPitch + (e & 127));
+    }
 }
 
 // U = index-reversed copy of the lower-triangular X (upper triangle and diagonal; zeros below).
