@@ -439,7 +439,7 @@ def run_ours(args):
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of k_hessian_umma_pair on fp16
 # X [T, C], from an ncu capture of exactly that launch (profiles/k_hessian_umma_pair_fp16.txt);
 # the algorithmic bytes of the launch are T*C*2 + 2 * 4 * C*(C+256)/2 = 1.63e9.
-HESSIAN_DRAM_BYTES = {(16384, 16384): 9099327744 + 559308544}
+HESSIAN_DRAM_BYTES = {(16384, 16384): 7966005504 + 552323840}
 
 
 def hessian_roofline(dev, d, f, args, peaks):
@@ -566,8 +566,8 @@ def extra_rooflines(dev, d, f, technique, peaks):
             W[:, :128].copy_(W0[:, :128])         # the step overwrites its block with Q: start from weights again
             ops.block_step(W, U, 0, technique, reuse=bufs)
 
-        ms_copy = _time_ms(lambda: W[:, :128].copy_(W0[:, :128]), reps=20)
-        ms = _time_ms(one_block, reps=20) - ms_copy
+        ms_copy = _time_ms(lambda: W[:, :128].copy_(W0[:, :128]), reps=50, warm=10)
+        ms = _time_ms(one_block, reps=50, warm=10) - ms_copy
         nbytes = 1536.0 * R + 65536.0
         out.append({"kernel": "block step (8 kernels)", "bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9,
                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
