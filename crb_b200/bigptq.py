@@ -114,6 +114,10 @@ class BRAGPTQ:
     #   begin  - enqueues the factorisation (attempt 0); no host synchronisation
     #   blocks - reads the factorisation status (waits for that stream only), handles the rare
     #            damping retry and enqueues the whole block loop; returns without waiting for it
+    #   commit - (optional) enqueues the write-back of the binarized weight INTO the layer's
+    #            existing weight storage on the linear's stream and returns the event that marks
+    #            it; a caller can then enqueue work that reads the weight (behind that event)
+    #            before anything has waited for the block loop on the host
     #   end    - waits for the block loop, reads the error and writes the weight back
     # A caller with several linears runs every `begin`, then every `blocks`, then every `end`.
     # `factor_from` names the state of another linear with the very same Hessian (q/k/v of one
@@ -210,6 +214,22 @@ class BRAGPTQ:
             st["ev"][2].record()
         return st
 
+    def fasterquant_commit(self, st):
+        """Enqueues `layer.weight.data.copy_(binarized W)` behind the block loop; returns its event.
+
+        The status flags of the block loop are only read by `fasterquant_end`: if that raises, the
+        layer's weight has already been overwritten with the incomplete result."""
+        self.fasterquant_blocks(st)
+        if "committed" not in st:
+            with torch.cuda.stream(st["stream"]):
+                W = st["W"]
+                if _Conv1D and isinstance(self.layer, _Conv1D):
+                    W = W.t()
+                self.layer.weight.data.copy_(W.reshape(self.layer.weight.shape))
+                st["committed"] = torch.cuda.Event()
+                st["committed"].record()
+        return st["committed"]
+
     def fasterquant_end(self, st):
         self.fasterquant_blocks(st)
         with torch.cuda.stream(st["stream"]):
@@ -228,9 +248,10 @@ class BRAGPTQ:
             if self.verbose:
                 print("time %.2f" % (time.time() - st["tick"]))
                 print("error", error)
-            if _Conv1D and isinstance(self.layer, _Conv1D):
-                W = W.t()
-            self.layer.weight.data = W.reshape(self.layer.weight.shape).to(self.layer.weight.data.dtype)
+            if "committed" not in st:                                   # bigptq.py:278-280
+                if _Conv1D and isinstance(self.layer, _Conv1D):
+                    W = W.t()
+                self.layer.weight.data = W.reshape(self.layer.weight.shape).to(self.layer.weight.data.dtype)
         return {"error": error}
 
     def free(self):

@@ -13,8 +13,10 @@
 //   k_metric_colscore  M, column scores, top-50 columns
 //   k_sort_rows        every metric row sorted (bitonic network) with its column ids
 //   k_salient_search_sorted  49 candidates x rows from prefix sums of the sorted rows, first strict minimum
-//   k_select_l1/l2/l3  exact radix selection (15+9+7 bits) of the 162 order statistics that
-//                      numpy.quantile(method="linear") interpolates between
+//   k_select_l1        histogram of the upper 15 key bits of |M|: the bins that hold the 162 order
+//                      statistics numpy.quantile(method="linear") interpolates between
+//   k_select_collect   the elements of those bins, gathered bin by bin
+//   k_select_bins      exact selection inside each bin (two 8-bit levels), the 81 interpolated values
 //   k_split_search_sorted  81 candidates x rows from prefix sums of the sorted rows
 //   k_finalize         masks, the technique's binarizer per group, Q, Err, Losses
 #include <math.h>
@@ -43,8 +45,6 @@ __constant__ unsigned c_split_probs[kSplits] = {
 constexpr int kL1Bins = 32768;   // key bits 30..16
 constexpr int kL1Smem = (kL1Bins + kL1Bins / 32) * (int)sizeof(unsigned);   // padded, see k_select_l1
 __host__ __device__ constexpr int pad1(int b) { return b + (b >> 5); }
-constexpr int kL2Bins = 512;     // key bits 15..7
-constexpr int kL3Bins = 128;     // key bits 6..0
 constexpr int kMaxCtas1 = 148;   // CTAs of the metric kernel (one per SM at most)
 constexpr int kMaxTiles = 512;   // row tiles of the search kernels
 constexpr int kAccSlots = 136;   // 0..48 salient candidates, 49..129 split candidates, 130 salient-group term
@@ -60,8 +60,7 @@ struct BlockWs {
     unsigned* counters;      // [16]   last-CTA tickets, one per kernel
     unsigned* hist1;         // [kL1Bins]
     unsigned char* slot1;    // [kL1Bins] 0 = not a target bin, else level-1 slot + 1
-    unsigned* hist2;         // [kTargets][kL2Bins]
-    unsigned* hist3;         // [kTargets][kL3Bins]
+    unsigned* cursor;        // [kTargets] fill level of each target bin's list
     unsigned long long* acc; // [kAccSlots] fixed-point candidate error sums (49 salient, 81 split, 1 salient term)
     // ---- scratch ----
     float* M;                // [R][128] metric
@@ -71,16 +70,16 @@ struct BlockWs {
     double* energy;          // [kMaxCtas1] per-CTA sum of M^2 (bounds every candidate error)
     double* fx;              // [2] fixed-point scale of the error sums and its inverse
     unsigned char* rank;     // [128] position of each column in the score order (>= 50: never salient)
-    int* sel;                // [8]   0: i*   1: k*   2: level-1 slots   3: level-2 slots
+    int* sel;                // [8]   0: i*   1: k*   2: number of target bins (lists)
     float* pvals;            // [kSplits + 1]  the 81 split candidates, [81] = chosen split
     unsigned* tgt_rank;      // [kTargets]
     unsigned* tgt_bin1;      // [kTargets]
-    unsigned* tgt_bin2;      // [kTargets]
-    unsigned* tgt_rem;       // [kTargets] rank left inside the current bin
-    unsigned* tgt_slot;      // [kTargets] slot of the target at the current level
+    unsigned* tgt_rem;       // [kTargets] rank left inside the target's level-1 bin
+    unsigned* tgt_slot;      // [kTargets] index of the target's bin among the target bins (its list)
     float* tgt_frac;         // [kSplits]  interpolation weight
-    unsigned* l2_start;      // [kTargets + 1] per level-1 slot: first level-2 slot
-    unsigned* l2_bin;        // [kTargets]     level-2 bin of each level-2 slot
+    unsigned* list_off;      // [kTargets + 1] per level-1 slot: start of its list (elements, zeros excluded)
+    unsigned* tgt_val;       // [kTargets] bit pattern of each order statistic
+    unsigned short* list;    // [R * 128] low 16 key bits of the elements that fall into a target bin, slot by slot
     double* trace_dummy;     // [CRB_TRACE_DOUBLES] sink when the caller passes no trace
 };
 
@@ -99,8 +98,7 @@ static size_t carve_block_ws(void* base, int R, BlockWs* ws) {
     w.counters = static_cast<unsigned*>(take(64));
     w.hist1 = static_cast<unsigned*>(take(sizeof(unsigned) * kL1Bins));
     w.slot1 = static_cast<unsigned char*>(take(kL1Bins));
-    w.hist2 = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets * kL2Bins));
-    w.hist3 = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets * kL3Bins));
+    w.cursor = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets));
     w.acc = static_cast<unsigned long long*>(take(sizeof(unsigned long long) * kAccSlots));
     w.zero_begin = base ? static_cast<unsigned char*>(base) + z0 : nullptr;
     w.zero_bytes = off - z0;
@@ -115,12 +113,12 @@ static size_t carve_block_ws(void* base, int R, BlockWs* ws) {
     w.pvals = static_cast<float*>(take(sizeof(float) * (kSplits + 1)));
     w.tgt_rank = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets));
     w.tgt_bin1 = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets));
-    w.tgt_bin2 = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets));
     w.tgt_rem = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets));
     w.tgt_slot = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets));
     w.tgt_frac = static_cast<float*>(take(sizeof(float) * kSplits));
-    w.l2_start = static_cast<unsigned*>(take(sizeof(unsigned) * (kTargets + 1)));
-    w.l2_bin = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets));
+    w.list_off = static_cast<unsigned*>(take(sizeof(unsigned) * (kTargets + 1)));
+    w.tgt_val = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets));
+    w.list = static_cast<unsigned short*>(take(sizeof(unsigned short) * (size_t)R * kBlock));
     w.trace_dummy = static_cast<double*>(take(sizeof(double) * CRB_TRACE_DOUBLES));
     if (ws) *ws = w;
     return off;
@@ -358,8 +356,10 @@ __device__ void warp_first_strict_min(const double* e, int n, int fallback, int*
 // ---------------------------------------------------------------------------------------
 // K3-K5: exact selection of the order statistics behind the 81 quantiles
 // (autosearch.py:62-68: numpy.quantile of |M * ~mask3| flattened, zeros at salient columns
-// included).  Keys are the float bit patterns (values are >= 0), selected by three histogram
-// levels; the salient zeros are added to bin 0 as a count.
+// included).  Keys are the float bit patterns of |M|.  A histogram of the upper 15 key bits finds
+// the bins that hold the targets; the elements of those bins (typically a fifth of the block) are
+// gathered bin by bin as 16-bit remainders and each bin is searched on its own with two 8-bit
+// histograms.  The salient zeros are added to bin 0 as a count.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ unsigned block_exclusive_scan_1024(unsigned v, unsigned* s_warp) {
     // exclusive scan of one value per thread over a 1024-thread CTA
@@ -472,7 +472,9 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
         ws.tgt_rem[tid] = r - s_hist[pad1(lo)];
     }
     __syncthreads();
-    // level-1 slots: the number of distinct bins before each target (targets are rank ordered)
+    // level-1 slots: the number of distinct bins before each target (targets are rank ordered); per
+    // slot the start of its list in the collection buffer (the bin's element count is exact: it is
+    // the difference of two prefix values, less the salient zeros that are only counted)
     if (tid < 32) {
         unsigned base = 0;
         for (int t0 = 0; t0 < kTargets; t0 += 32) {
@@ -482,197 +484,168 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
             if (t < kTargets) {
                 const unsigned slot = base + __popc(m & (0xffffffffu >> (31 - tid)));
                 ws.tgt_slot[t] = slot;
-                ws.slot1[s_tbin[t]] = (unsigned char)(slot + 1);
+                if (fresh || t == 0) {
+                    const unsigned bin = s_tbin[t];
+                    ws.slot1[bin] = (unsigned char)(slot + 1);
+                    const unsigned next = (bin + 1 < (unsigned)kL1Bins) ? s_hist[pad1(bin + 1)] : N;
+                    s_trank[slot] = next - s_hist[pad1(bin)] - (bin == 0 ? zeros : 0u);   // reused: count per slot
+                }
                 if (t == kTargets - 1) ws.sel[2] = (int)slot + 1;
             }
             base += __popc(m);
         }
+        __syncwarp();
+        // exclusive scan of the (at most 162) slot counts
+        const unsigned nslot = base + 1;
+        unsigned run = 0;
+        for (unsigned s0 = 0; s0 < nslot; s0 += 32) {
+            const unsigned sidx = s0 + tid;
+            const unsigned c = sidx < nslot ? s_trank[sidx] : 0u;
+            unsigned inc = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned v = __shfl_up_sync(0xffffffffu, inc, o);
+                if (tid >= o) inc += v;
+            }
+            if (sidx < nslot) ws.list_off[sidx] = run + inc - c;
+            run += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (tid == 0) ws.list_off[nslot] = run;
     }
 }
 
-// Warp-level search inside a histogram row of 32 * PER counters (PER a multiple of 4): `load`
-// fetches the lane's PER consecutive counters and their prefix over the warp, `pick` returns the
-// bin holding the rem-th element (0-based) and the rank left inside that bin.  Two targets in the
-// same row (the two order statistics of one quantile nearly always are) share one `load`.
-template <int PER>
-struct WarpRow {
-    unsigned c[PER];
-    unsigned exc, inc;
-    __device__ __forceinline__ void load(const unsigned* row) {
-        const int lane = threadIdx.x & 31;
-        const uint4* src = reinterpret_cast<const uint4*>(row + lane * PER);
-        unsigned tot = 0;
+// Collection: the low 16 key bits of every non-salient element that falls into a target bin, appended
+// to that bin's list (exact-size segments, order irrelevant).  A CTA first counts its elements per
+// list in shared memory, reserves one range per list with a single global atomic, then writes.
+__global__ void __launch_bounds__(1024)
+k_select_collect(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
+                 const int* __restrict__ sel, BlockWs ws) {
+    __shared__ bool s_sal[kBlock];
+    __shared__ unsigned s_cnt[kTargets], s_base[kTargets];
+    const int tid = threadIdx.x;
+    chain_wait();
+    const int isal = sel[0];
+    if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
+    if (tid < kTargets) s_cnt[tid] = 0u;
+    __syncthreads();
+    const size_t n4 = (size_t)R * (kBlock / 4);
+    const size_t first = (size_t)blockIdx.x * blockDim.x + tid, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t idx = first; idx < n4; idx += stride) {
+        const int c4 = (int)(idx & 31) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(M + idx * 4);
+        const float vv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int k = 0; k < PER / 4; ++k) {
-            const uint4 v = __ldcg(&src[k]);
-            c[4 * k] = v.x; c[4 * k + 1] = v.y; c[4 * k + 2] = v.z; c[4 * k + 3] = v.w;
-            tot += v.x + v.y + v.z + v.w;
+        for (int k = 0; k < 4; ++k) {
+            if (s_sal[c4 + k]) continue;
+            const unsigned s1 = ws.slot1[(__float_as_uint(vv[k]) & 0x7fffffffu) >> 16];
+            if (s1) atomicAdd(&s_cnt[s1 - 1], 1u);
         }
-        inc = tot;
+    }
+    __syncthreads();
+    if (tid < kTargets) {
+        const unsigned c = s_cnt[tid];
+        s_base[tid] = c ? ws.list_off[tid] + atomicAdd(&ws.cursor[tid], c) : 0u;
+        s_cnt[tid] = 0u;
+    }
+    __syncthreads();
+    for (size_t idx = first; idx < n4; idx += stride) {
+        const int c4 = (int)(idx & 31) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(M + idx * 4);
+        const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (s_sal[c4 + k]) continue;
+            const unsigned key = __float_as_uint(vv[k]) & 0x7fffffffu;
+            const unsigned s1 = ws.slot1[key >> 16];
+            if (!s1) continue;
+            const unsigned pos = atomicAdd(&s_cnt[s1 - 1], 1u);
+            ws.list[s_base[s1 - 1] + pos] = (unsigned short)(key & 0xffffu);
+        }
+    }
+}
+
+// Selection inside the target bins: one CTA per level-1 slot.  The list of the slot holds the low
+// 16 key bits of the bin's elements; every target of the slot (usually one to four) is located by
+// two 8-bit histogram levels over that list.  The histogram of the high byte is shared by all
+// targets of the slot, the one of the low byte by all targets with the same high byte.  The CTA that
+// finishes last interpolates the 81 split candidates exactly as numpy does.
+constexpr int kBinThreads = 512;
+__global__ void __launch_bounds__(kBinThreads)
+k_select_bins(int R, const int* __restrict__ sel, BlockWs ws) {
+    __shared__ unsigned s_hi[256], s_lo[256], s_scan[256], s_warp[kBinThreads / 32];
+    __shared__ int s_t0, s_t1;
+    __shared__ unsigned s_pick, s_left;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool owner = tid < 256;                            // one thread per histogram counter
+    chain_wait();
+    const int slot = blockIdx.x;
+    const int nslot = sel[2];
+    // exclusive scan over the CTA of one counter per thread (zero beyond the first 256 threads)
+    auto scan_cta = [&](unsigned v) {
+        unsigned inc = v;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const unsigned t = __shfl_up_sync(0xffffffffu, inc, o);
             if (lane >= o) inc += t;
         }
-        exc = inc - tot;
-    }
-    __device__ __forceinline__ void pick(unsigned rem, unsigned* bin_out, unsigned* rem_out) const {
-        const int lane = threadIdx.x & 31;
-        const bool mine = (exc <= rem) && (rem < inc);
-        const unsigned who = __ballot_sync(0xffffffffu, mine);
-        unsigned bin = 32 * PER - 1, left = 0;
-        if (mine) {
-            unsigned run = exc;
-#pragma unroll
-            for (int k = 0; k < PER; ++k) {
-                if (rem < run + c[k]) { bin = lane * PER + k; left = rem - run; break; }
-                run += c[k];
+        if (lane == 31) s_warp[warp] = inc;
+        __syncthreads();
+        unsigned base = 0;
+        for (int w = 0; w < warp; ++w) base += s_warp[w];
+        __syncthreads();
+        return base + inc - v;
+    };
+    if (slot < nslot) {
+        if (tid == 0) { s_t0 = kTargets; s_t1 = -1; }
+        __syncthreads();
+        if (tid < kTargets && (int)ws.tgt_slot[tid] == slot) { atomicMin(&s_t0, tid); atomicMax(&s_t1, tid); }
+        const unsigned off = ws.list_off[slot], n = ws.list_off[slot + 1] - off;
+        const unsigned short* list = ws.list + off;
+        if (owner) s_hi[tid] = 0u;
+        __syncthreads();
+        const int t0 = s_t0, t1 = s_t1;
+        const unsigned bin1 = ws.tgt_bin1[t0];
+        const unsigned zeros = bin1 == 0u ? (unsigned)R * (unsigned)sel[0] : 0u;   // salient zeros: counted, not listed
+        for (unsigned k = tid; k < n; k += kBinThreads) atomicAdd(&s_hi[list[k] >> 8], 1u);
+        __syncthreads();
+        const unsigned hi_cnt = owner ? s_hi[tid] : 0u;
+        const unsigned hi_exc = scan_cta(hi_cnt);
+        int lo_of = -1;                                      // high byte the low-byte histogram currently describes
+        for (int t = t0; t <= t1; ++t) {
+            unsigned rem = ws.tgt_rem[t];
+            if (rem < zeros) {                               // one of the counted zeros: the value is 0
+                if (tid == 0) ws.tgt_val[t] = 0u;
+                continue;
             }
-        }
-        const int src = who ? (__ffs(who) - 1) : 0;
-        *bin_out = __shfl_sync(0xffffffffu, bin, src);
-        *rem_out = __shfl_sync(0xffffffffu, left, src);
-    }
-};
-
-// Level 2: key bits 15..7 of the elements that fall in a level-1 target bin.
-__global__ void __launch_bounds__(1024)
-k_select_l2(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
-            const int* __restrict__ sel, BlockWs ws) {
-    __shared__ bool s_sal[kBlock];
-    __shared__ unsigned s_bin2[kTargets], s_slot1[kTargets], s_rem[kTargets], s_slot2[kTargets];
-    __shared__ unsigned s_l2start[kTargets + 1], s_l2bin[kTargets];
-    const int tid = threadIdx.x;
-    chain_wait();
-    const int isal = sel[0];
-    if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
-    __syncthreads();
-    const size_t n4 = (size_t)R * (kBlock / 4);
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + tid; idx < n4; idx += (size_t)gridDim.x * blockDim.x) {
-        const int c4 = (int)(idx & 31) * 4;
-        const float4 v = *reinterpret_cast<const float4*>(M + idx * 4);
-        const float vv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            if (s_sal[c4 + k]) continue;
-            const unsigned key = __float_as_uint(vv[k]) & 0x7fffffffu;
-            const unsigned s = ws.slot1[key >> 16];
-            if (s) atomicAdd(&ws.hist2[(size_t)(s - 1) * kL2Bins + ((key >> 7) & (kL2Bins - 1))], 1u);
+            rem -= zeros;
+            if (hi_exc <= rem && rem < hi_exc + hi_cnt) { s_pick = (unsigned)tid; s_left = rem - hi_exc; }
+            __syncthreads();
+            const unsigned hi = s_pick, left = s_left;
+            if ((int)hi != lo_of) {
+                if (owner) s_lo[tid] = 0u;
+                __syncthreads();
+                for (unsigned k = tid; k < n; k += kBinThreads) {
+                    const unsigned e = list[k];
+                    if ((e >> 8) == hi) atomicAdd(&s_lo[e & 255u], 1u);
+                }
+                __syncthreads();
+                const unsigned exc = scan_cta(owner ? s_lo[tid] : 0u);
+                if (owner) s_scan[tid] = exc;
+                lo_of = (int)hi;
+                __syncthreads();
+            }
+            if (owner) {
+                const unsigned lo_cnt = s_lo[tid], lo_exc = s_scan[tid];
+                if (lo_exc <= left && left < lo_exc + lo_cnt) ws.tgt_val[t] = (bin1 << 16) | (hi << 8) | (unsigned)tid;
+            }
+            __syncthreads();
         }
     }
     if (!last_cta_done(&ws.counters[3], gridDim.x)) return;
-    if (tid == 0) {
-        const unsigned s0 = ws.slot1[0];
-        if (s0) atomicAdd(&ws.hist2[(size_t)(s0 - 1) * kL2Bins], (unsigned)R * (unsigned)isal);
-    }
-    __syncthreads();
-    const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
-    if (tid < kTargets) { s_slot1[tid] = ws.tgt_slot[tid]; s_rem[tid] = ws.tgt_rem[tid]; }
-    __syncthreads();
-    for (int p = warp; p < kSplits; p += nw) {            // the two order statistics of quantile p
-        const int ta = 2 * p, tb = ta + 1;
-        WarpRow<kL2Bins / 32> row;
-        unsigned bin, left;
-        row.load(ws.hist2 + (size_t)s_slot1[ta] * kL2Bins);
-        row.pick(s_rem[ta], &bin, &left);
-        if (lane == 0) { s_bin2[ta] = bin; s_rem[ta] = left; }
-        if (s_slot1[tb] != s_slot1[ta]) row.load(ws.hist2 + (size_t)s_slot1[tb] * kL2Bins);
-        row.pick(s_rem[tb], &bin, &left);
-        if (lane == 0) { s_bin2[tb] = bin; s_rem[tb] = left; }
-    }
-    __syncthreads();
-    if (warp == 0) {
-        // level-2 slots: distinct (level-1 slot, bin2) pairs in rank order; level-1 slots are consecutive
-        unsigned base = 0;
-        for (int t0 = 0; t0 < kTargets; t0 += 32) {
-            const int t = t0 + lane;
-            const bool in = t < kTargets;
-            const unsigned s1 = in ? s_slot1[t] : 0u, b2 = in ? s_bin2[t] : 0u;
-            const bool new1 = in && (t == 0 || s1 != s_slot1[t - 1]);
-            const bool fresh = in && t > 0 && (new1 || b2 != s_bin2[t - 1]);
-            const unsigned m = __ballot_sync(0xffffffffu, fresh);
-            const unsigned slot2 = base + __popc(m & (0xffffffffu >> (31 - lane)));
-            if (in) {
-                s_slot2[t] = slot2;
-                if (fresh || t == 0) s_l2bin[slot2] = b2;
-                if (new1) s_l2start[s1] = slot2;
-                if (t == kTargets - 1) {
-                    s_l2start[s1 + 1] = slot2 + 1;
-                    ws.sel[3] = (int)slot2 + 1;
-                    ws.sel[2] = (int)s1 + 1;
-                }
-            }
-            base += __popc(m);
-        }
-    }
-    __syncthreads();
-    if (tid < kTargets) {
-        ws.tgt_bin2[tid] = s_bin2[tid]; ws.tgt_rem[tid] = s_rem[tid]; ws.tgt_slot[tid] = s_slot2[tid];
-        ws.l2_bin[tid] = s_l2bin[tid];
-    }
-    if (tid <= kTargets) ws.l2_start[tid] = s_l2start[tid];
-}
-
-// Level 3: key bits 6..0, then the 81 interpolated split candidates.
-__global__ void __launch_bounds__(1024)
-k_select_l3(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
-            const int* __restrict__ sel, BlockWs ws) {
-    __shared__ bool s_sal[kBlock];
-    __shared__ float s_val[kTargets];
-    const int tid = threadIdx.x;
-    chain_wait();
-    const int isal = sel[0];
-    if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
-    __syncthreads();
-    const size_t n4 = (size_t)R * (kBlock / 4);
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + tid; idx < n4; idx += (size_t)gridDim.x * blockDim.x) {
-        const int c4 = (int)(idx & 31) * 4;
-        const float4 v = *reinterpret_cast<const float4*>(M + idx * 4);
-        const float vv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            if (s_sal[c4 + k]) continue;
-            const unsigned key = __float_as_uint(vv[k]) & 0x7fffffffu;
-            const unsigned s = ws.slot1[key >> 16];
-            if (!s) continue;
-            const unsigned b2 = (key >> 7) & (kL2Bins - 1);
-            const unsigned j1 = ws.l2_start[s];
-            for (unsigned j = ws.l2_start[s - 1]; j < j1; ++j)
-                if (ws.l2_bin[j] == b2) { atomicAdd(&ws.hist3[(size_t)j * kL3Bins + (key & (kL3Bins - 1))], 1u); break; }
-        }
-    }
-    if (!last_cta_done(&ws.counters[4], gridDim.x)) return;
-
-    if (tid == 0) {
-        const unsigned s0 = ws.slot1[0];
-        if (s0) {
-            const unsigned j = ws.l2_start[s0 - 1];
-            if (ws.l2_bin[j] == 0u) atomicAdd(&ws.hist3[(size_t)j * kL3Bins], (unsigned)R * (unsigned)isal);
-        }
-    }
-    __syncthreads();
-    const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
-    __shared__ unsigned s_slot[kTargets], s_rem[kTargets], s_hi[kTargets];
-    if (tid < kTargets) {
-        s_slot[tid] = ws.tgt_slot[tid]; s_rem[tid] = ws.tgt_rem[tid];
-        s_hi[tid] = (ws.tgt_bin1[tid] << 16) | (ws.tgt_bin2[tid] << 7);
-    }
-    __syncthreads();
-    for (int p = warp; p < kSplits; p += nw) {
-        const int ta = 2 * p, tb = ta + 1;
-        WarpRow<kL3Bins / 32> row;
-        unsigned bin, left;
-        row.load(ws.hist3 + (size_t)s_slot[ta] * kL3Bins);
-        row.pick(s_rem[ta], &bin, &left);
-        if (lane == 0) s_val[ta] = __uint_as_float(s_hi[ta] | bin);
-        if (s_slot[tb] != s_slot[ta]) row.load(ws.hist3 + (size_t)s_slot[tb] * kL3Bins);
-        row.pick(s_rem[tb], &bin, &left);
-        if (lane == 0) s_val[tb] = __uint_as_float(s_hi[tb] | bin);
-    }
-    __syncthreads();
     if (tid < kSplits) {
         // numpy _lerp: a + (b-a)*t, replaced by b - (b-a)*(1-t) when t >= 0.5; float32, unfused
-        const float a = s_val[2 * tid], b = s_val[2 * tid + 1], t = ws.tgt_frac[tid];
+        const float a = __uint_as_float(__ldcg(&ws.tgt_val[2 * tid])), b = __uint_as_float(__ldcg(&ws.tgt_val[2 * tid + 1]));
+        const float t = ws.tgt_frac[tid];
         const float diff = __fsub_rn(b, a);
         const float v0 = __fadd_rn(a, __fmul_rn(diff, t));
         const float v1 = __fsub_rn(b, __fmul_rn(diff, __fsub_rn(1.0f, t)));
@@ -1569,9 +1542,9 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
     launch_chained(k_select_l1, g1, 1024, kL1Smem, st, ws.M, R, ws.rank, ws.sel, ws);
     CRB_LAUNCHED();
     const int g2 = min(148, ceil_div(n4, 1024));
-    launch_chained(k_select_l2, g2, 1024, 0, st, ws.M, R, ws.rank, ws.sel, ws);
+    launch_chained(k_select_collect, g2, 1024, 0, st, ws.M, R, ws.rank, ws.sel, ws);
     CRB_LAUNCHED();
-    launch_chained(k_select_l3, g2, 1024, 0, st, ws.M, R, ws.rank, ws.sel, ws);
+    launch_chained(k_select_bins, kTargets, kBinThreads, 0, st, R, ws.sel, ws);
     CRB_LAUNCHED();
     // K6: split search on the sorted rows
     const int rows_sp = kSplitRows * ceil_div(R, kSplitRows * kMaxTiles);

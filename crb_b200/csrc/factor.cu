@@ -464,7 +464,12 @@ static SideContext* side_context(cudaStream_t main, size_t n_events) {
     if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
     std::lock_guard<std::mutex> guard(g_side_lock);
     SideContext& ctx = g_side[std::make_pair(dev, main)];
-    if (!ctx.side && cudaStreamCreateWithFlags(&ctx.side, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (!ctx.side) {
+        // same priority as the caller's stream: the side work is part of the caller's critical path
+        int prio = 0;
+        if (cudaStreamGetPriority(main, &prio) != cudaSuccess) prio = 0;
+        if (cudaStreamCreateWithPriority(&ctx.side, cudaStreamNonBlocking, prio) != cudaSuccess) return nullptr;
+    }
     while (ctx.events.size() < n_events) {
         cudaEvent_t e;
         if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return nullptr;

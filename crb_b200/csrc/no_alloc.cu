@@ -12,7 +12,7 @@
 // Limits and rules
 //   * at most CRB_STATIC_MAX_ROWS (16384) rows per call; larger R is refused with
 //     CRB_ERR_STATIC_LIMIT before anything is launched;
-//   * the array costs kStaticScratchBytes (19 MiB) of device memory on every GPU that loads
+//   * the array costs kStaticScratchBytes (23 MiB) of device memory on every GPU that loads
 //     the library, whether or not this entry point is ever called;
 //   * all calls on a device share the one array.  It keeps whatever the previous call left,
 //     so each call clears the parts that must start at zero (status word, tickets,
@@ -36,8 +36,8 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
 
 constexpr int kStaticMaxRows = CRB_STATIC_MAX_ROWS;
 // fixed tables of the block step (< 1 MiB) + per row 512 bytes of metric values, 512 bytes of
-// sorted values and 128 bytes of sorted column indices
-constexpr size_t kStaticScratchBytes = (size_t(1) << 20) + size_t(kStaticMaxRows) * 1152;
+// sorted values, 128 bytes of sorted column indices and 256 bytes of selection lists
+constexpr size_t kStaticScratchBytes = (size_t(1) << 20) + size_t(kStaticMaxRows) * 1408;
 
 // The scratch itself.  In host code this name is only a handle for the runtime, not a device
 // address: the address used at launch comes from cudaGetSymbolAddress below.

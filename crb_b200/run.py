@@ -56,7 +56,7 @@ def default_args(**overrides) -> SimpleNamespace:
                         partition=3, global_scale=False, disable_gptq=False, minlayer=-1, maxlayer=1000,
                         quant_only="", invert=False, corr_damp=0.1, lam=1e-5, coupling=0.5,
                         device="cuda:0", seqlen=None, forward_batch=8, act_offload_gib=64.0, act_stage_gib=16.0,
-                        verbose=True, save_packed=None)
+                        reprop_lanes=16, reprop_overlap=True, verbose=True, save_packed=None)
     for k, v in overrides.items():
         setattr(a, k, v)
     return a
@@ -108,11 +108,19 @@ _STREAMS: Dict[object, list] = {}
 
 
 def _copy_streams(dev):
-    """(host->device, device->host) side streams of a device, created once."""
+    """(host->device, device->host, weight broadcast) side streams of a device, created once."""
     key = ("copy", torch.device(dev).index or 0)
     if key not in _STREAMS:
-        _STREAMS[key] = [torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)]
+        _STREAMS[key] = [torch.cuda.Stream(device=dev) for _ in range(3)]
     return _STREAMS[key]
+
+
+def _lane_streams(dev, n):
+    """Streams of the re-propagation pass (lowest priority), created once per device."""
+    lanes = _STREAMS.setdefault(("lanes", torch.device(dev).index or 0), [])
+    while len(lanes) < n:
+        lanes.append(torch.cuda.Stream(device=dev, priority=0))
+    return lanes[:n]
 
 
 class _Resident:
@@ -251,21 +259,22 @@ class _Feeder:
     def __len__(self):
         return (self.n + self.fb - 1) // self.fb
 
-    def batch(self, idx):
-        """Batch `idx` on the device; call in increasing order, `done(idx)` after its last use."""
+    def batch(self, idx, stream=None):
+        """Batch `idx` on the device; call in increasing order, `done(idx)` after its last use.
+        `stream` is the stream that reads the batch (default: the one current at construction)."""
         if not self.staged and not self.whole:
             j = idx * self.fb
             return self.inps[j:j + min(self.fb, self.n - j)].to(self.dev, non_blocking=True)
         view = self._rows(idx)[2]
         if self.staged:
             self._stage(idx + 1)
-            self.main.wait_event(self.ready[self._slot(idx)])
+            (stream or self.main).wait_event(self.ready[self._slot(idx)])
         return view
 
-    def done(self, idx):
+    def done(self, idx, stream=None):
         if self.staged or self.whole:
             ev = torch.cuda.Event()
-            ev.record(self.main)
+            ev.record(stream or self.main)
             self.free[self._slot(idx)] = ev
 
     def second_pass(self):
@@ -337,12 +346,12 @@ def _stream_pool(dev, n):
     """Side streams per device, created once: scratch buffers are cached per stream.
 
     Slot 0 serves the most expensive linear of a layer, whose serial chain of small kernels decides
-    when the layer is done: it gets the high priority, so that its kernels are placed first whenever
-    an SM frees up among the wide kernels of the other linears."""
+    when the layer is done: it gets the highest priority, so that its kernels are placed first
+    whenever an SM frees up among the wide kernels of the other linears; the other linears come
+    next, ahead of the forwards of the re-propagation pass that run beside them."""
     pool = _STREAMS.setdefault(torch.device(dev).index or 0, [])
     while len(pool) < n:
-        prio = -1 if (len(pool) == 0 and os.environ.get("CRB_STREAM_PRIORITY", "1") != "0") else 0
-        pool.append(torch.cuda.Stream(device=dev, priority=prio))
+        pool.append(torch.cuda.Stream(device=dev, priority=-2 if len(pool) == 0 else -1))
     return pool
 
 
@@ -487,71 +496,133 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
     shapes = {n: (gptq[n].rows, gptq[n].columns) for n in gptq}
     owners = parallel.assign_owners(shapes, ws)
     errors: Dict[str, float] = {n: 0.0 for n in gptq}        # same key order on every rank
-    with timer.span("fasterquant"):
-        mine = [n for n in gptq if owners[n] == rank]
-        # the linears are independent problems: give each its own stream so that the serial parts of
-        # one (128-wide diagonal factorisations, small block kernels) overlap the wide kernels of another
-        main = torch.cuda.current_stream(dev) if dev.type == "cuda" else None
-        concurrent = main is not None and getattr(args, "concurrent_linears", True) and len(mine) > 1
-        states = {}
-        order = sorted(mine, key=lambda n: -parallel.linear_cost(*shapes[n]))
-        if concurrent:
-            ready = torch.cuda.Event()
-            ready.record(main)
-            pool = _stream_pool(dev, len(order))
-            slot_of = {name: slot for slot, name in enumerate(order)}
-            # linears that share a Hessian on this rank share its factor: leaders first
-            lead_of = {n: alias[n] for n in order if n in alias and alias[n] in slot_of}
-            begin_order = [n for n in order if n not in lead_of] + [n for n in order if n in lead_of]
-            for name in begin_order:
-                s = pool[slot_of[name]]
-                s.wait_event(ready)
-                with torch.cuda.stream(s):
-                    states[name] = gptq[name].fasterquant_begin(
-                        percdamp=args.percdamp, blocksize=args.blocksize, partition=args.partition,
-                        global_scale=args.global_scale,
-                        factor_from=states[lead_of[name]] if name in lead_of else None)
-            # cheapest factorisations finish first: enqueue their block loops as soon as they are checked
-            for name in reversed(begin_order[:len(order) - len(lead_of)]):
-                gptq[name].fasterquant_blocks(states[name])
-                for other in (n for n in lead_of if lead_of[n] == name):
-                    gptq[other].fasterquant_blocks(states[other])
-        for name in (reversed(order) if concurrent else mine):
-            if args.verbose:
-                print(index, name)
-                print("Quantizing ...")
-            if concurrent:
-                info = gptq[name].fasterquant_end(states[name])
-                main.wait_stream(states[name]["stream"])
-            else:
-                info = gptq[name].fasterquant(percdamp=args.percdamp, blocksize=args.blocksize,
-                                              partition=args.partition, global_scale=args.global_scale)
-            errors[name] = info["error"]
-            if traces is not None and gptq[name].last_trace is not None:
-                traces[name] = gptq[name].last_trace.cpu()
-            if getattr(gptq[name], "packed", None) is not None:
-                from . import packed as _packed
-                os.makedirs(args.save_packed, exist_ok=True)
-                _packed.save(os.path.join(args.save_packed, f"layer{index}.{name}.npz"), gptq[name].packed)
-                gptq[name].packed = None
-            for k, v in gptq[name].last_timing.items():
-                timer.ms[k] = timer.ms.get(k, 0.0) + v
-        states.clear()
-        for name in gptq:
-            gptq[name].free()
-    with timer.span("weight_broadcast"):
-        if ws > 1:
-            for name in gptq:
-                parallel.broadcast_(subset[name].weight.data, owners[name])
+    mine = [n for n in gptq if owners[n] == rank]
+    order = sorted(gptq, key=lambda n: -parallel.linear_cost(*shapes[n]))     # same on every rank
+    main = torch.cuda.current_stream(dev) if dev.type == "cuda" else None
+    concurrent = main is not None and getattr(args, "concurrent_linears", True)
+    states = {}
 
-    # ---- pass 2: re-propagate with the quantized weights (run.py:376-377) ----
-    with timer.span("forward_repropagate"):
+    def finish(name, info):
+        errors[name] = info["error"]
+        if traces is not None and gptq[name].last_trace is not None:
+            traces[name] = gptq[name].last_trace.cpu()
+        if getattr(gptq[name], "packed", None) is not None:
+            from . import packed as _packed
+            os.makedirs(args.save_packed, exist_ok=True)
+            _packed.save(os.path.join(args.save_packed, f"layer{index}.{name}.npz"), gptq[name].packed)
+            gptq[name].packed = None
+        for k, v in gptq[name].last_timing.items():
+            timer.ms[k] = timer.ms.get(k, 0.0) + v
+
+    if not concurrent:
+        with timer.span("fasterquant"):
+            for name in mine:
+                if args.verbose:
+                    print(index, name)
+                    print("Quantizing ...")
+                finish(name, gptq[name].fasterquant(percdamp=args.percdamp, blocksize=args.blocksize,
+                                                    partition=args.partition, global_scale=args.global_scale))
+            for name in gptq:
+                gptq[name].free()
+        with timer.span("weight_broadcast"):
+            if ws > 1:
+                for name in gptq:
+                    parallel.broadcast_(subset[name].weight.data, owners[name])
+        # ---- pass 2: re-propagate with the quantized weights (run.py:376-377) ----
+        with timer.span("forward_repropagate"):
+            feed = feed2
+            for b in range(len(feed)):
+                x = feed.batch(b)
+                y = _layer_out(layer(x, **_replay_kwargs(layer_kwargs, x.shape[0])))
+                feed.done(b)
+                _store_outputs(outs, b * fb, y.reshape(x.shape), dev)
+        del gptq
+        return errors
+
+    # Device path.  Every linear of this rank gets its own stream, so that the serial parts of one
+    # (128-wide diagonal factorisations, small block kernels) overlap the wide kernels of another.
+    # Nothing below waits on the host for a block loop before the re-propagation pass has been
+    # enqueued: each binarized weight is written into the layer's weight storage on the linear's
+    # stream (then broadcast when there are several ranks) and an event marks it; the batches of
+    # the re-propagation pass run on side streams and wait, in front of every linear, for that
+    # linear's event.  The forward of a batch therefore runs up to the first linear that is still
+    # being quantized - for a decoder layer everything but its last, most expensive linear - while
+    # that linear's block loop is still going.
+    with timer.span("fasterquant"):
+        start = torch.cuda.Event()
+        start.record(main)
+        mine_order = [n for n in order if owners[n] == rank]
+        pool = _stream_pool(dev, len(mine_order))
+        slot_of = {name: slot for slot, name in enumerate(mine_order)}
+        # linears that share a Hessian on this rank share its factor: leaders first
+        lead_of = {n: alias[n] for n in mine_order if n in alias and alias[n] in slot_of}
+        begin_order = [n for n in mine_order if n not in lead_of] + [n for n in mine_order if n in lead_of]
+        for name in begin_order:
+            s = pool[slot_of[name]]
+            s.wait_event(start)
+            with torch.cuda.stream(s):
+                states[name] = gptq[name].fasterquant_begin(
+                    percdamp=args.percdamp, blocksize=args.blocksize, partition=args.partition,
+                    global_scale=args.global_scale,
+                    factor_from=states[lead_of[name]] if name in lead_of else None)
+        # cheapest factorisations finish first: enqueue their block loops as soon as they are checked
+        committed = {}
+        for name in reversed(begin_order[:len(mine_order) - len(lead_of)]):
+            committed[name] = gptq[name].fasterquant_commit(states[name])
+            for other in (n for n in lead_of if lead_of[n] == name):
+                committed[other] = gptq[other].fasterquant_commit(states[other])
+        # the event behind which a linear's weight may be read on this rank; with several ranks the
+        # weights travel in the order in which they get ready (cheapest first), on a stream of their own
+        ready = dict(committed)
+        if ws > 1:
+            bc = _copy_streams(dev)[2]
+            bc.wait_event(start)
+            with torch.cuda.stream(bc):
+                for name in reversed(order):
+                    if name in committed:
+                        bc.wait_event(committed[name])
+                    parallel.broadcast_(subset[name].weight.data, owners[name])
+                    ready[name] = torch.cuda.Event()
+                    ready[name].record(bc)
+
+        # ---- pass 2: re-propagate with the quantized weights (run.py:376-377) ----
+        def gate(name):
+            def hook(_, inp):
+                torch.cuda.current_stream(dev).wait_event(ready[name])
+            return hook
+
+        handles = [subset[name].register_forward_pre_hook(gate(name)) for name in gptq]
         feed = feed2
+        overlap = bool(getattr(args, "reprop_overlap", True))
+        lanes = _lane_streams(dev, min(len(feed), max(1, int(getattr(args, "reprop_lanes", 16)))))
         for b in range(len(feed)):
-            x = feed.batch(b)
-            y = _layer_out(layer(x, **_replay_kwargs(layer_kwargs, x.shape[0])))
-            feed.done(b)
-            _store_outputs(outs, b * fb, y.reshape(x.shape), dev)
+            lane = lanes[b % len(lanes)]
+            lane.wait_event(start)
+            if not overlap:
+                for name in gptq:
+                    lane.wait_event(ready[name])
+            with torch.cuda.stream(lane):
+                x = feed.batch(b, lane)
+                y = _layer_out(layer(x, **_replay_kwargs(layer_kwargs, x.shape[0])))
+                feed.done(b, lane)
+                _store_outputs(outs, b * fb, y.reshape(x.shape), dev)
+        for h in handles:
+            h.remove()
+        # the phase ends on the caller's stream when the last weight is in place ...
+        for name in gptq:
+            main.wait_event(ready[name])
+    with timer.span("forward_repropagate"):
+        # ... and what the side streams still have to do after that is the exposed part of pass 2
+        for lane in lanes:
+            main.wait_stream(lane)
+    for name in reversed(mine_order):
+        if args.verbose:
+            print(index, name)
+            print("Quantizing ...")
+        finish(name, gptq[name].fasterquant_end(states[name]))
+    states.clear()
+    for name in gptq:
+        gptq[name].free()
     del gptq
     return errors
 
@@ -668,6 +739,11 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--act_stage_gib", type=float, default=16.0,
                    help="host-resident activations: a shard up to this size is copied in once per layer and kept "
                         "on the device for both passes")
+    p.add_argument("--reprop_lanes", type=int, default=16,
+                   help="batches of the re-propagation pass that may be in flight (each on its own stream) while "
+                        "the layer's last linear is still being quantized; each holds one batch of intermediate activations")
+    p.add_argument("--no_reprop_overlap", dest="reprop_overlap", action="store_false",
+                   help="start the re-propagation pass only when every linear of the layer has been quantized")
     p.add_argument("--save_packed", type=str, default=None,
                    help="directory that receives the packed form (bit planes + scales) of every binarized linear")
     p.add_argument("--quiet", action="store_true")

@@ -132,7 +132,7 @@ int crb_block_step(float *W_dev, int R, int64_t ldw, const float *U_dev, int64_t
  * whole GPU through its own memory pool; a latency-critical loop that cannot take the
  * device-wide synchronisation of cudaMalloc / cudaFree).  Same arithmetic, arguments and
  * outputs as crb_block_step, but the scratch memory is an array inside the library image
- * (19 MiB on every GPU that loads the library) instead of a caller workspace, and the call
+ * (23 MiB on every GPU that loads the library) instead of a caller workspace, and the call
  * performs no allocation of any kind.
  *   - R <= CRB_STATIC_MAX_ROWS, otherwise CRB_ERR_STATIC_LIMIT and nothing is launched;
  *   - flags_out (optional, device): receives this call's status flags (CRB_FLAG_*);
