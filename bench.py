@@ -258,7 +258,8 @@ def run_ours(args):
     model = crun.get_model(args.model, fill_device=str(dev), n_layers=n_layers)
     model.seqlen = args.seqlen
     qargs = crun.default_args(model=args.model, low_quant_method=args.technique, nsamples=args.nsamples,
-                              device=str(dev), forward_batch=args.forward_batch, verbose=False)
+                              device=str(dev), forward_batch=args.forward_batch, verbose=False,
+                              reprop_overlap=args.reprop_overlap)
     loader = synthetic_calibration(model.config.vocab_size, args.nsamples, args.seqlen, seed=0)
 
     # ---- layer-0 inputs of this rank's sequences, kept in pinned host memory ----
@@ -591,6 +592,8 @@ def main():
     ap.add_argument("--seqlen", type=int, default=SEQLEN)
     ap.add_argument("--forward_batch", type=int, default=8)
     ap.add_argument("--no_cpu_baseline", action="store_true")
+    ap.add_argument("--reprop_overlap", action="store_true",
+                    help="forwards of the re-propagation pass on side streams, gated per linear (measured: no gain)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -7,6 +7,7 @@ namespace crb {
 
 std::atomic<unsigned long long> g_launches{0};
 std::atomic<int> g_dependent_launch{1};
+std::atomic<int> g_fused_selection{0};
 
 // block_step.cu
 size_t block_workspace_bytes(int R);
@@ -59,6 +60,10 @@ const char* crb_status_string(int status) {
 
 int crb_set_dependent_launch(int enable) {
     return g_dependent_launch.exchange(enable ? 1 : 0);
+}
+
+int crb_set_fused_selection(int enable) {
+    return g_fused_selection.exchange(enable ? 1 : 0);
 }
 
 unsigned long long crb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

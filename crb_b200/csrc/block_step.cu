@@ -61,6 +61,7 @@ struct BlockWs {
     unsigned* hist1;         // [kL1Bins]
     unsigned char* slot1;    // [kL1Bins] 0 = not a target bin, else level-1 slot + 1
     unsigned* cursor;        // [kTargets] fill level of each target bin's list
+    unsigned* barrier;       // [16]   arrival counters of the grid barriers of k_select_fused
     unsigned long long* acc; // [kAccSlots] fixed-point candidate error sums (49 salient, 81 split, 1 salient term)
     // ---- scratch ----
     float* M;                // [R][128] metric
@@ -99,6 +100,7 @@ static size_t carve_block_ws(void* base, int R, BlockWs* ws) {
     w.hist1 = static_cast<unsigned*>(take(sizeof(unsigned) * kL1Bins));
     w.slot1 = static_cast<unsigned char*>(take(kL1Bins));
     w.cursor = static_cast<unsigned*>(take(sizeof(unsigned) * kTargets));
+    w.barrier = static_cast<unsigned*>(take(64));
     w.acc = static_cast<unsigned long long*>(take(sizeof(unsigned long long) * kAccSlots));
     w.zero_begin = base ? static_cast<unsigned char*>(base) + z0 : nullptr;
     w.zero_bytes = off - z0;
@@ -386,25 +388,18 @@ __device__ __forceinline__ unsigned block_exclusive_scan_1024(unsigned v, unsign
     return base + inc - v;
 }
 
-// Level 1: histogram of key bits 30..16 over the non-salient elements.
-__global__ void __launch_bounds__(1024)
-k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
-            const int* __restrict__ sel, BlockWs ws) {
-    // bin b lives at s_hist[pad1(b)]: one spare word per 32 bins, so that the scan of the tail,
-    // in which every thread walks its own 32 consecutive bins, is free of bank conflicts
-    extern __shared__ __align__(16) unsigned s_hist[];   // kL1Smem bytes
-    __shared__ unsigned s_warp[32];
-    __shared__ unsigned s_tbin[kTargets];
-    __shared__ unsigned s_trank[kTargets];
-    __shared__ bool s_sal[kBlock];
+// The selection runs either as three kernels (k_select_l1 / k_select_collect / k_select_bins, each
+// handing over through the last CTA that finishes) or as one cooperative kernel whose CTAs meet at
+// grid barriers (k_select_fused); both are built from the phases below.
+
+// Phase 1: histogram of key bits 30..16 over the non-salient elements this CTA reads, merged into
+// the global histogram.  Bin b lives at s_hist[pad1(b)]: one spare word per 32 bins, so that the
+// scan of phase 2, in which every thread walks its own 32 consecutive bins, is free of bank conflicts.
+__device__ __forceinline__ void select_histogram(const float* __restrict__ M, int R, const bool* s_sal,
+                                                 unsigned* s_hist, const BlockWs& ws, int cta, int nctas) {
     const int tid = threadIdx.x;
-    for (int k = tid; k < kL1Bins + kL1Bins / 32; k += blockDim.x) s_hist[k] = 0u;
-    chain_wait();
-    const int isal = sel[0];
-    if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
-    __syncthreads();
     const size_t n4 = (size_t)R * (kBlock / 4);
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + tid; idx < n4; idx += (size_t)gridDim.x * blockDim.x) {
+    for (size_t idx = (size_t)cta * blockDim.x + tid; idx < n4; idx += (size_t)nctas * blockDim.x) {
         const int c4 = (int)(idx & 31) * 4;
         const float4 v = *reinterpret_cast<const float4*>(M + idx * 4);
         const float vv[4] = {v.x, v.y, v.z, v.w};
@@ -417,8 +412,15 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
         const unsigned c = s_hist[pad1(k)];
         if (c) atomicAdd(&ws.hist1[k], c);
     }
-    if (!last_cta_done(&ws.counters[2], gridDim.x)) return;
+}
 
+// Phase 2 (one CTA of 1024 threads): prefix of the global histogram, the bin of each of the 162 target
+// ranks, the target bins numbered in rank order and the start of each one's list.
+__device__ void select_locate(int R, int isal, unsigned* s_hist, const BlockWs& ws) {
+    __shared__ unsigned s_warp[32];
+    __shared__ unsigned s_tbin[kTargets];
+    __shared__ unsigned s_trank[kTargets];
+    const int tid = threadIdx.x;
     // ---- scan + locate the 162 target ranks ----
     const unsigned N = (unsigned)R * kBlock;
     const unsigned zeros = (unsigned)R * (unsigned)isal;
@@ -514,22 +516,17 @@ k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict_
     }
 }
 
-// Collection: the low 16 key bits of every non-salient element that falls into a target bin, appended
+// Phase 3: the low 16 key bits of every non-salient element that falls into a target bin, appended
 // to that bin's list (exact-size segments, order irrelevant).  A CTA first counts its elements per
 // list in shared memory, reserves one range per list with a single global atomic, then writes.
-__global__ void __launch_bounds__(1024)
-k_select_collect(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
-                 const int* __restrict__ sel, BlockWs ws) {
-    __shared__ bool s_sal[kBlock];
+__device__ __forceinline__ void select_collect(const float* __restrict__ M, int R, const bool* s_sal,
+                                               const BlockWs& ws, int cta, int nctas) {
     __shared__ unsigned s_cnt[kTargets], s_base[kTargets];
     const int tid = threadIdx.x;
-    chain_wait();
-    const int isal = sel[0];
-    if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
     if (tid < kTargets) s_cnt[tid] = 0u;
     __syncthreads();
     const size_t n4 = (size_t)R * (kBlock / 4);
-    const size_t first = (size_t)blockIdx.x * blockDim.x + tid, stride = (size_t)gridDim.x * blockDim.x;
+    const size_t first = (size_t)cta * blockDim.x + tid, stride = (size_t)nctas * blockDim.x;
     for (size_t idx = first; idx < n4; idx += stride) {
         const int c4 = (int)(idx & 31) * 4;
         const float4 v = *reinterpret_cast<const float4*>(M + idx * 4);
@@ -564,22 +561,17 @@ k_select_collect(const float* __restrict__ M, int R, const unsigned char* __rest
     }
 }
 
-// Selection inside the target bins: one CTA per level-1 slot.  The list of the slot holds the low
-// 16 key bits of the bin's elements; every target of the slot (usually one to four) is located by
-// two 8-bit histogram levels over that list.  The histogram of the high byte is shared by all
-// targets of the slot, the one of the low byte by all targets with the same high byte.  The CTA that
-// finishes last interpolates the 81 split candidates exactly as numpy does.
-constexpr int kBinThreads = 512;
-__global__ void __launch_bounds__(kBinThreads)
-k_select_bins(int R, const int* __restrict__ sel, BlockWs ws) {
-    __shared__ unsigned s_hi[256], s_lo[256], s_scan[256], s_warp[kBinThreads / 32];
+// Phase 4: selection inside one target bin.  The bin's list holds the low 16 key bits of its
+// elements; every target of the bin (usually one to four) is located by two 8-bit histogram levels
+// over that list.  The histogram of the high byte is shared by all targets of the bin, the one of
+// the low byte by all targets with the same high byte.  Any CTA size from 256 to 1024 threads.
+__device__ void select_in_bin(int R, int isal, int slot, const BlockWs& ws) {
+    __shared__ unsigned s_hi[256], s_lo[256], s_scan[256], s_warp[32];
     __shared__ int s_t0, s_t1;
     __shared__ unsigned s_pick, s_left;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const unsigned nthreads = blockDim.x;
     const bool owner = tid < 256;                            // one thread per histogram counter
-    chain_wait();
-    const int slot = blockIdx.x;
-    const int nslot = sel[2];
     // exclusive scan over the CTA of one counter per thread (zero beyond the first 256 threads)
     auto scan_cta = [&](unsigned v) {
         unsigned inc = v;
@@ -595,53 +587,56 @@ k_select_bins(int R, const int* __restrict__ sel, BlockWs ws) {
         __syncthreads();
         return base + inc - v;
     };
-    if (slot < nslot) {
-        if (tid == 0) { s_t0 = kTargets; s_t1 = -1; }
+    if (tid == 0) { s_t0 = kTargets; s_t1 = -1; }
+    __syncthreads();
+    if (tid < kTargets && (int)ws.tgt_slot[tid] == slot) { atomicMin(&s_t0, tid); atomicMax(&s_t1, tid); }
+    const unsigned off = ws.list_off[slot], n = ws.list_off[slot + 1] - off;
+    const unsigned short* list = ws.list + off;
+    if (owner) s_hi[tid] = 0u;
+    __syncthreads();
+    const int t0 = s_t0, t1 = s_t1;
+    const unsigned bin1 = ws.tgt_bin1[t0];
+    const unsigned zeros = bin1 == 0u ? (unsigned)R * (unsigned)isal : 0u;   // salient zeros: counted, not listed
+    for (unsigned k = tid; k < n; k += nthreads) atomicAdd(&s_hi[list[k] >> 8], 1u);
+    __syncthreads();
+    const unsigned hi_cnt = owner ? s_hi[tid] : 0u;
+    const unsigned hi_exc = scan_cta(hi_cnt);
+    int lo_of = -1;                                      // high byte the low-byte histogram currently describes
+    for (int t = t0; t <= t1; ++t) {
+        unsigned rem = ws.tgt_rem[t];
+        if (rem < zeros) {                               // one of the counted zeros: the value is 0
+            if (tid == 0) ws.tgt_val[t] = 0u;
+            continue;
+        }
+        rem -= zeros;
+        if (hi_exc <= rem && rem < hi_exc + hi_cnt) { s_pick = (unsigned)tid; s_left = rem - hi_exc; }
         __syncthreads();
-        if (tid < kTargets && (int)ws.tgt_slot[tid] == slot) { atomicMin(&s_t0, tid); atomicMax(&s_t1, tid); }
-        const unsigned off = ws.list_off[slot], n = ws.list_off[slot + 1] - off;
-        const unsigned short* list = ws.list + off;
-        if (owner) s_hi[tid] = 0u;
-        __syncthreads();
-        const int t0 = s_t0, t1 = s_t1;
-        const unsigned bin1 = ws.tgt_bin1[t0];
-        const unsigned zeros = bin1 == 0u ? (unsigned)R * (unsigned)sel[0] : 0u;   // salient zeros: counted, not listed
-        for (unsigned k = tid; k < n; k += kBinThreads) atomicAdd(&s_hi[list[k] >> 8], 1u);
-        __syncthreads();
-        const unsigned hi_cnt = owner ? s_hi[tid] : 0u;
-        const unsigned hi_exc = scan_cta(hi_cnt);
-        int lo_of = -1;                                      // high byte the low-byte histogram currently describes
-        for (int t = t0; t <= t1; ++t) {
-            unsigned rem = ws.tgt_rem[t];
-            if (rem < zeros) {                               // one of the counted zeros: the value is 0
-                if (tid == 0) ws.tgt_val[t] = 0u;
-                continue;
-            }
-            rem -= zeros;
-            if (hi_exc <= rem && rem < hi_exc + hi_cnt) { s_pick = (unsigned)tid; s_left = rem - hi_exc; }
+        const unsigned hi = s_pick, left = s_left;
+        if ((int)hi != lo_of) {
+            if (owner) s_lo[tid] = 0u;
             __syncthreads();
-            const unsigned hi = s_pick, left = s_left;
-            if ((int)hi != lo_of) {
-                if (owner) s_lo[tid] = 0u;
-                __syncthreads();
-                for (unsigned k = tid; k < n; k += kBinThreads) {
-                    const unsigned e = list[k];
-                    if ((e >> 8) == hi) atomicAdd(&s_lo[e & 255u], 1u);
-                }
-                __syncthreads();
-                const unsigned exc = scan_cta(owner ? s_lo[tid] : 0u);
-                if (owner) s_scan[tid] = exc;
-                lo_of = (int)hi;
-                __syncthreads();
+            for (unsigned k = tid; k < n; k += nthreads) {
+                const unsigned e = list[k];
+                if ((e >> 8) == hi) atomicAdd(&s_lo[e & 255u], 1u);
             }
-            if (owner) {
-                const unsigned lo_cnt = s_lo[tid], lo_exc = s_scan[tid];
-                if (lo_exc <= left && left < lo_exc + lo_cnt) ws.tgt_val[t] = (bin1 << 16) | (hi << 8) | (unsigned)tid;
-            }
+            __syncthreads();
+            const unsigned exc = scan_cta(owner ? s_lo[tid] : 0u);
+            if (owner) s_scan[tid] = exc;
+            lo_of = (int)hi;
             __syncthreads();
         }
+        if (owner) {
+            const unsigned lo_cnt = s_lo[tid], lo_exc = s_scan[tid];
+            if (lo_exc <= left && left < lo_exc + lo_cnt) ws.tgt_val[t] = (bin1 << 16) | (hi << 8) | (unsigned)tid;
+        }
+        __syncthreads();
     }
-    if (!last_cta_done(&ws.counters[3], gridDim.x)) return;
+    __syncthreads();
+}
+
+// The 81 split candidates from the 162 order statistics, exactly as numpy interpolates them.
+__device__ __forceinline__ void select_interpolate(const BlockWs& ws) {
+    const int tid = threadIdx.x;
     if (tid < kSplits) {
         // numpy _lerp: a + (b-a)*t, replaced by b - (b-a)*(1-t) when t >= 0.5; float32, unfused
         const float a = __uint_as_float(__ldcg(&ws.tgt_val[2 * tid])), b = __uint_as_float(__ldcg(&ws.tgt_val[2 * tid + 1]));
@@ -651,6 +646,88 @@ k_select_bins(int R, const int* __restrict__ sel, BlockWs ws) {
         const float v1 = __fsub_rn(b, __fmul_rn(diff, __fsub_rn(1.0f, t)));
         ws.pvals[tid] = (t >= 0.5f) ? v1 : v0;
     }
+}
+
+__global__ void __launch_bounds__(1024)
+k_select_l1(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
+            const int* __restrict__ sel, BlockWs ws) {
+    extern __shared__ __align__(16) unsigned s_hist[];   // kL1Smem bytes
+    __shared__ bool s_sal[kBlock];
+    const int tid = threadIdx.x;
+    for (int k = tid; k < kL1Bins + kL1Bins / 32; k += blockDim.x) s_hist[k] = 0u;
+    chain_wait();
+    const int isal = sel[0];
+    if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
+    __syncthreads();
+    select_histogram(M, R, s_sal, s_hist, ws, blockIdx.x, gridDim.x);
+    if (!last_cta_done(&ws.counters[2], gridDim.x)) return;
+    select_locate(R, isal, s_hist, ws);
+}
+
+__global__ void __launch_bounds__(1024)
+k_select_collect(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
+                 const int* __restrict__ sel, BlockWs ws) {
+    __shared__ bool s_sal[kBlock];
+    const int tid = threadIdx.x;
+    chain_wait();
+    const int isal = sel[0];
+    if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
+    __syncthreads();
+    select_collect(M, R, s_sal, ws, blockIdx.x, gridDim.x);
+}
+
+constexpr int kBinThreads = 512;
+__global__ void __launch_bounds__(kBinThreads)
+k_select_bins(int R, const int* __restrict__ sel, BlockWs ws) {
+    chain_wait();
+    if ((int)blockIdx.x < sel[2]) select_in_bin(R, sel[0], blockIdx.x, ws);
+    if (!last_cta_done(&ws.counters[3], gridDim.x)) return;
+    select_interpolate(ws);
+}
+
+// All CTAs of a cooperative launch meet here.  The wait is bounded: a CTA that gives up raises
+// CRB_FLAG_WAIT_LIMIT and the kernel returns (every CTA then runs out the same way).
+__device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned expected, unsigned* status) {
+    __shared__ int s_ok;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        atomicAdd(counter, 1u);
+        int ok = 0;
+        for (unsigned it = 0; it < (1u << 22); ++it) {       // each probe is a round trip to L2: seconds in all
+            unsigned seen;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+            if (seen >= expected) { ok = 1; break; }
+        }
+        if (!ok) atomicOr(status, CRB_FLAG_WAIT_LIMIT);
+        s_ok = ok;
+    }
+    __syncthreads();
+    return s_ok != 0;
+}
+
+// The three selection kernels as one cooperative launch (one CTA per SM at most, all resident).
+__global__ void __launch_bounds__(1024)
+k_select_fused(const float* __restrict__ M, int R, const unsigned char* __restrict__ rank,
+               const int* __restrict__ sel, BlockWs ws) {
+    extern __shared__ __align__(16) unsigned s_hist[];   // kL1Smem bytes
+    __shared__ bool s_sal[kBlock];
+    const int tid = threadIdx.x;
+    const unsigned nctas = gridDim.x;
+    for (int k = tid; k < kL1Bins + kL1Bins / 32; k += blockDim.x) s_hist[k] = 0u;
+    const int isal = sel[0];
+    if (tid < kBlock) s_sal[tid] = rank[tid] < isal;
+    __syncthreads();
+    select_histogram(M, R, s_sal, s_hist, ws, blockIdx.x, nctas);
+    if (!grid_barrier(&ws.barrier[0], nctas, ws.status)) return;
+    if (blockIdx.x == 0) select_locate(R, isal, s_hist, ws);
+    if (!grid_barrier(&ws.barrier[1], nctas, ws.status)) return;
+    select_collect(M, R, s_sal, ws, blockIdx.x, nctas);
+    if (!grid_barrier(&ws.barrier[2], nctas, ws.status)) return;
+    const int nslot = __ldcg(&ws.sel[2]);
+    for (int slot = blockIdx.x; slot < nslot; slot += nctas) select_in_bin(R, isal, slot, ws);
+    if (!last_cta_done(&ws.counters[3], nctas)) return;
+    select_interpolate(ws);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1509,15 +1586,17 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
     const int col0 = block * kBlock;
 
     static PerDeviceSetup once;
+    int sm_count = 0;
     int rc_setup = once.run([] {
         if (cudaFuncSetAttribute(k_select_l1, cudaFuncAttributeMaxDynamicSharedMemorySize, kL1Smem) != cudaSuccess ||
+            cudaFuncSetAttribute(k_select_fused, cudaFuncAttributeMaxDynamicSharedMemorySize, kL1Smem) != cudaSuccess ||
             cudaFuncSetAttribute(k_split_search_sorted, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kSplitSmem) != cudaSuccess ||
             cudaFuncSetAttribute(k_salient_search_sorted, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kSalSmem) != cudaSuccess)
             return (int)CRB_ERR_LAUNCH;
         return (int)CRB_OK;
-    });
+    }, &sm_count);
     if (rc_setup != CRB_OK) return rc_setup;
     // the last-CTA tickets reset themselves; a caller that cannot vouch for them (first use of a
     // workspace, stand-alone calls) asks for a reset
@@ -1538,14 +1617,32 @@ int block_step_launch(float* W, int R, int64_t ldw, const float* U, int64_t ldu,
     CRB_LAUNCHED();
     // K3-K5
     const int n4 = R * (kBlock / 4);
-    const int g1 = min(148, ceil_div(n4, 1024 * 4));
-    launch_chained(k_select_l1, g1, 1024, kL1Smem, st, ws.M, R, ws.rank, ws.sel, ws);
-    CRB_LAUNCHED();
     const int g2 = min(148, ceil_div(n4, 1024));
-    launch_chained(k_select_collect, g2, 1024, 0, st, ws.M, R, ws.rank, ws.sel, ws);
-    CRB_LAUNCHED();
-    launch_chained(k_select_bins, kTargets, kBinThreads, 0, st, R, ws.sel, ws);
-    CRB_LAUNCHED();
+    if (g_fused_selection.load(std::memory_order_relaxed)) {
+        // one cooperative launch: all CTAs resident (one per SM: 132 KB of shared memory each)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)min(g2, sm_count > 0 ? sm_count : 1));
+        cfg.blockDim = dim3(1024);
+        cfg.dynamicSmemBytes = kL1Smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, k_select_fused, (const float*)ws.M, R, (const unsigned char*)ws.rank,
+                               (const int*)ws.sel, ws) != cudaSuccess)
+            return CRB_ERR_LAUNCH;
+        CRB_LAUNCHED();
+    } else {
+        const int g1 = min(148, ceil_div(n4, 1024 * 4));
+        launch_chained(k_select_l1, g1, 1024, kL1Smem, st, ws.M, R, ws.rank, ws.sel, ws);
+        CRB_LAUNCHED();
+        launch_chained(k_select_collect, g2, 1024, 0, st, ws.M, R, ws.rank, ws.sel, ws);
+        CRB_LAUNCHED();
+        launch_chained(k_select_bins, kTargets, kBinThreads, 0, st, R, ws.sel, ws);
+        CRB_LAUNCHED();
+    }
     // K6: split search on the sorted rows
     const int rows_sp = kSplitRows * ceil_div(R, kSplitRows * kMaxTiles);
     launch_chained(k_split_search_sorted, ceil_div(R, rows_sp), 256, kSplitSmem, st,

@@ -30,6 +30,7 @@ extern std::atomic<unsigned long long> g_launches;
 // are visible, so stream order is kept for the data.  What overlaps is the launch itself and
 // the part of a kernel in front of chain_wait() (shared-memory set-up, barrier and tensor-memory
 // allocation).  chain_wait() is a no-op for a kernel launched the ordinary way.
+extern std::atomic<int> g_fused_selection;    // 1: quantile selection as one cooperative kernel; crb_set_fused_selection()
 extern std::atomic<int> g_dependent_launch;   // 1: use it (default); crb_set_dependent_launch()
 
 #ifdef __CUDACC__

@@ -6,6 +6,7 @@
     python -m crb_b200.microbench trailing --R 4096 --C 4096
     python -m crb_b200.microbench linear   --R 4096 --C 4096 --technique crb
     python -m crb_b200.microbench dequant  --R 4096 --C 4096 --technique crb
+    python -m crb_b200.microbench gemm     --R 4096 --C 4096 --T 1024     (C[R,C] -= A[R,T] B[C,T]^T)
 
 Each run does `--warmup` untimed and `--iters` timed calls bracketed by CUDA events on the
 launching stream and prints one JSON line with the time per call and the algorithmic
@@ -52,7 +53,7 @@ def _synthetic_factor(C, dev, seed=0):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["hessian", "factor", "block", "trailing", "linear", "dequant"])
+    ap.add_argument("what", choices=["hessian", "factor", "block", "trailing", "linear", "dequant", "gemm"])
     ap.add_argument("--R", type=int, default=4096)
     ap.add_argument("--C", type=int, default=4096)
     ap.add_argument("--T", type=int, default=16384)
@@ -62,12 +63,17 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--no_dependent_launch", action="store_true",
                     help="plain stream-ordered launches instead of programmatic dependent launch")
+    ap.add_argument("--fused_selection", action="store_true",
+                    help="quantile selection of the block step as one cooperative kernel")
     a = ap.parse_args(argv)
+    if a.fused_selection:
+        ops.set_fused_selection(True)
     if a.no_dependent_launch:
         ops.set_dependent_launch(False)
     dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator(device=dev).manual_seed(1)
-    out = {"what": a.what, "R": a.R, "C": a.C, "T": a.T, "dependent_launch": not a.no_dependent_launch}
+    out = {"what": a.what, "R": a.R, "C": a.C, "T": a.T, "dependent_launch": not a.no_dependent_launch,
+           "fused_selection": a.fused_selection}
     launches0 = ops.launch_count()
 
     if a.what == "hessian":
@@ -106,6 +112,15 @@ def main(argv=None):
         n = a.C - 128
         out.update(ms=ms, tflops=2.0 * a.R * 128 * n / ms / 1e9, gbs=(8.0 * a.R * n + 4 * a.R * 128 + 4 * 128 * n) / ms / 1e6,
                    note="first block of the loop: flop 2*R*128*(C-128); bytes read+write W[:,128:] + Err + U rows")
+    elif a.what == "gemm":
+        # the shape of the factorisation's rank-K updates: both operands row-major with K contiguous
+        A = torch.randn(a.R, a.T, generator=g, device=dev)
+        B = torch.randn(a.C, a.T, generator=g, device=dev)
+        Cm = torch.zeros(a.R, a.C, device=dev)
+        ms = _time(lambda: ops.gemm_f32(A, B, Cm, alpha=-1.0, beta=1.0, b_is_nk=True), a.warmup, a.iters)
+        out.update(ms=ms, tflops_fp32_equivalent=2.0 * a.R * a.C * a.T / ms / 1e9,
+                   tflops_tf32_issued=6.0 * a.R * a.C * a.T / ms / 1e9,
+                   note="M=R, N=C, K=T; three TF32 MMAs per float32 product term")
     elif a.what == "dequant":
         from . import packed
         W = torch.randn(a.R, a.C, generator=g, device=dev) * 0.02

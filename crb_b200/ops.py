@@ -295,6 +295,12 @@ def selftest_wait_limit(device, limit_us: int = 1000) -> int:
     return int(status[0].item())
 
 
+def set_fused_selection(enable: bool) -> bool:
+    """Quantile selection of the block step as one cooperative kernel (True) or three kernels (False,
+    the default); returns the old setting."""
+    return bool(lib().crb_set_fused_selection(int(bool(enable))))
+
+
 def set_dependent_launch(enable: bool) -> bool:
     """Switches programmatic dependent launch of the kernel chains on or off; returns the old setting."""
     return bool(lib().crb_set_dependent_launch(int(bool(enable))))

@@ -35,8 +35,15 @@ def shard_range(n: int, rank: int, world_size: int) -> range:
 
 
 def linear_cost(rows: int, cols: int) -> float:
-    """Relative cost of quantizing one linear: factorisation ~ cols^3, block loop ~ rows*cols."""
-    return (2.0 / 3.0) * cols ** 3 / 2.5e13 + rows * cols * 2.0e-9 + (cols / 128) * 6.0e-5
+    """Seconds one linear takes on a B200 (fitted to measurements, used only to balance ranks).
+
+    Factorisation: products at the split-TF32 GEMM rate (~ cols^3) plus the serial chain of diagonal
+    blocks (~ cols): 2.7 ms at 4096 columns, 25.6 ms at 16384.  Block loop: per 128-column block a
+    chain of dependent kernels (61 us + 15.4 ns per row) plus the trailing updates (~ rows * cols^2
+    at the same GEMM rate)."""
+    factor = 3.57e-15 * cols ** 3 + 6.04e-7 * cols
+    blocks = (cols / 128) * (6.1e-5 + 1.54e-8 * rows) + rows * cols ** 2 / 1.9e14
+    return factor + blocks
 
 
 def assign_owners(shapes: Dict[str, Tuple[int, int]], world_size: int) -> Dict[str, int]:

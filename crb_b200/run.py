@@ -56,7 +56,7 @@ def default_args(**overrides) -> SimpleNamespace:
                         partition=3, global_scale=False, disable_gptq=False, minlayer=-1, maxlayer=1000,
                         quant_only="", invert=False, corr_damp=0.1, lam=1e-5, coupling=0.5,
                         device="cuda:0", seqlen=None, forward_batch=8, act_offload_gib=64.0, act_stage_gib=16.0,
-                        reprop_lanes=16, reprop_overlap=True, verbose=True, save_packed=None)
+                        reprop_lanes=16, reprop_overlap=False, verbose=True, save_packed=None)
     for k, v in overrides.items():
         setattr(a, k, v)
     return a
@@ -541,13 +541,14 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
 
     # Device path.  Every linear of this rank gets its own stream, so that the serial parts of one
     # (128-wide diagonal factorisations, small block kernels) overlap the wide kernels of another.
-    # Nothing below waits on the host for a block loop before the re-propagation pass has been
-    # enqueued: each binarized weight is written into the layer's weight storage on the linear's
-    # stream (then broadcast when there are several ranks) and an event marks it; the batches of
-    # the re-propagation pass run on side streams and wait, in front of every linear, for that
-    # linear's event.  The forward of a batch therefore runs up to the first linear that is still
-    # being quantized - for a decoder layer everything but its last, most expensive linear - while
-    # that linear's block loop is still going.
+    # Each binarized weight is written into the layer's weight storage on the linear's stream (then
+    # broadcast when there are several ranks) and an event marks it; the host does not wait for a
+    # block loop before everything, the second pass included, has been enqueued.
+    # `reprop_overlap` (off by default) lets the forwards of the second pass start before the last
+    # linear is done: its batches run on side streams and wait, in front of every linear, for that
+    # linear's event, so a forward runs up to the first linear that is still being quantized.  On a
+    # B200 this moved no time: the block loops and the forwards' GEMMs both need whole SMs (shared
+    # memory), so they take turns on the SMs instead of sharing them.
     with timer.span("fasterquant"):
         start = torch.cuda.Event()
         start.record(main)
@@ -585,36 +586,43 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
                     ready[name] = torch.cuda.Event()
                     ready[name].record(bc)
 
-        # ---- pass 2: re-propagate with the quantized weights (run.py:376-377) ----
-        def gate(name):
-            def hook(_, inp):
-                torch.cuda.current_stream(dev).wait_event(ready[name])
-            return hook
-
-        handles = [subset[name].register_forward_pre_hook(gate(name)) for name in gptq]
+        overlap = bool(getattr(args, "reprop_overlap", False))
         feed = feed2
-        overlap = bool(getattr(args, "reprop_overlap", True))
-        lanes = _lane_streams(dev, min(len(feed), max(1, int(getattr(args, "reprop_lanes", 16)))))
-        for b in range(len(feed)):
-            lane = lanes[b % len(lanes)]
-            lane.wait_event(start)
-            if not overlap:
-                for name in gptq:
-                    lane.wait_event(ready[name])
-            with torch.cuda.stream(lane):
-                x = feed.batch(b, lane)
-                y = _layer_out(layer(x, **_replay_kwargs(layer_kwargs, x.shape[0])))
-                feed.done(b, lane)
-                _store_outputs(outs, b * fb, y.reshape(x.shape), dev)
-        for h in handles:
-            h.remove()
-        # the phase ends on the caller's stream when the last weight is in place ...
+        lanes = []
+        if overlap:
+            # ---- pass 2 (run.py:376-377) started early, gated per linear ----
+            def gate(name):
+                def hook(_, inp):
+                    torch.cuda.current_stream(dev).wait_event(ready[name])
+                return hook
+
+            handles = [subset[name].register_forward_pre_hook(gate(name)) for name in gptq]
+            lanes = _lane_streams(dev, min(len(feed), max(1, int(getattr(args, "reprop_lanes", 16)))))
+            for b in range(len(feed)):
+                lane = lanes[b % len(lanes)]
+                lane.wait_event(start)
+                with torch.cuda.stream(lane):
+                    x = feed.batch(b, lane)
+                    y = _layer_out(layer(x, **_replay_kwargs(layer_kwargs, x.shape[0])))
+                    feed.done(b, lane)
+                    _store_outputs(outs, b * fb, y.reshape(x.shape), dev)
+            for h in handles:
+                h.remove()
+        # the phase ends on the caller's stream when the last weight is in place
         for name in gptq:
             main.wait_event(ready[name])
     with timer.span("forward_repropagate"):
-        # ... and what the side streams still have to do after that is the exposed part of pass 2
-        for lane in lanes:
-            main.wait_stream(lane)
+        if overlap:
+            # what the side streams still have to do is the exposed part of pass 2
+            for lane in lanes:
+                main.wait_stream(lane)
+        else:
+            # ---- pass 2: re-propagate with the quantized weights (run.py:376-377) ----
+            for b in range(len(feed)):
+                x = feed.batch(b)
+                y = _layer_out(layer(x, **_replay_kwargs(layer_kwargs, x.shape[0])))
+                feed.done(b)
+                _store_outputs(outs, b * fb, y.reshape(x.shape), dev)
     for name in reversed(mine_order):
         if args.verbose:
             print(index, name)
@@ -740,10 +748,11 @@ def build_parser() -> argparse.ArgumentParser:
                    help="host-resident activations: a shard up to this size is copied in once per layer and kept "
                         "on the device for both passes")
     p.add_argument("--reprop_lanes", type=int, default=16,
-                   help="batches of the re-propagation pass that may be in flight (each on its own stream) while "
-                        "the layer's last linear is still being quantized; each holds one batch of intermediate activations")
-    p.add_argument("--no_reprop_overlap", dest="reprop_overlap", action="store_false",
-                   help="start the re-propagation pass only when every linear of the layer has been quantized")
+                   help="with --reprop_overlap: batches that may be in flight (each on its own stream); each holds "
+                        "one batch of intermediate activations")
+    p.add_argument("--reprop_overlap", action="store_true",
+                   help="start the forwards of the re-propagation pass (on side streams, gated per linear) while "
+                        "the layer's last linear is still being quantized")
     p.add_argument("--save_packed", type=str, default=None,
                    help="directory that receives the packed form (bit planes + scales) of every binarized linear")
     p.add_argument("--quiet", action="store_true")

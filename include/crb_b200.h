@@ -222,6 +222,14 @@ unsigned long long crb_launch_count(void);
  * (default 1 = on).  No counterpart in the reference (eager PyTorch launches).               */
 int crb_set_dependent_launch(int enable);
 
+/* The quantile selection of the block step as ONE cooperative kernel whose CTAs (one per SM at
+ * most, all resident) meet at three bounded grid barriers, instead of three stream-ordered
+ * kernels.  Same results; off by default: a cooperative launch needs all its CTAs resident at
+ * once, so it waits for the whole GPU whenever other streams are busy, which costs more in the
+ * layer loop (six linears on six streams) than the two kernel boundaries it saves.  Returns the
+ * previous setting.  No counterpart in the reference.                                        */
+int crb_set_fused_selection(int enable);
+
 /* ---- self-test of the bounded waits -----------------------------------------------
  * Every wait inside the tensor-core kernels gives up after a time limit, raises
  * CRB_FLAG_WAIT_LIMIT in the status word, drains its copies, frees its tensor memory and

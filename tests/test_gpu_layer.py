@@ -12,7 +12,7 @@ from tests import helpers as Hh
 pytestmark = pytest.mark.gpu
 
 
-def _run(concurrent: bool, arch: str, tech: str, offload: bool = False, stage_gib: float = 16.0):
+def _run(concurrent: bool, arch: str, tech: str, offload: bool = False, stage_gib: float = 16.0, **overrides):
     from crb_b200 import run as crun
     from crb_b200.synth import build_synthetic_model, synthetic_calibration
     model = build_synthetic_model(arch, n_layers=2, seed=3)
@@ -21,6 +21,8 @@ def _run(concurrent: bool, arch: str, tech: str, offload: bool = False, stage_gi
     args = crun.default_args(low_quant_method=tech, nsamples=8, forward_batch=4, verbose=False,
                              device="cuda:0", percdamp=0.1)
     args.concurrent_linears = concurrent
+    for k, v in overrides.items():
+        setattr(args, k, v)
     if offload:
         args.act_offload_gib = 0.0          # activations live in pinned host memory and stream through the device
         args.act_stage_gib = stage_gib      # 0: two batch-sized buffers, every batch copied in for both passes
@@ -44,6 +46,20 @@ def test_overlapped_linears_equal_sequential(arch, tech):
         assert ec == es
     assert torch.equal(out_c["final_hidden"].cpu(), out_s["final_hidden"].cpu())
     assert out_c["error_sum"] > 0
+
+
+@pytest.mark.parametrize("overrides", [dict(reprop_overlap=True), dict(reprop_overlap=True, reprop_lanes=1),
+                                       dict(reprop_overlap=True, reprop_lanes=2)])
+def test_repropagation_schedule_does_not_change_the_result(overrides):
+    """With `reprop_overlap` the forwards of the second pass run on side streams and wait, in front of
+    each linear, for that linear's binarized weight: whatever the number of streams, the outputs
+    are the same bits as with the pass held back until every linear is done."""
+    out_a, w_a = _run(True, "opt-tiny", "crb")
+    out_b, w_b = _run(True, "opt-tiny", "crb", **overrides)
+    for name in w_a:
+        assert torch.equal(w_a[name], w_b[name]), name
+    assert torch.equal(out_a["final_hidden"].cpu(), out_b["final_hidden"].cpu())
+    assert out_a["errors"] == out_b["errors"]
 
 
 @pytest.mark.parametrize("stage_gib", (16.0, 0.0))

@@ -453,6 +453,34 @@ def test_split_quantiles_match_numpy(ops):
             assert np.float32(tf["split_value"]) == np.float32(ref.trace.split_values[ref.trace.split_index])
 
 
+def test_fused_selection_gives_the_same_bits(ops):
+    """The cooperative one-kernel quantile selection and the three stream-ordered kernels are two
+    schedules of the same phases: split values, decisions and outputs agree bit for bit, also on
+    inputs with many equal values (whole bins of ties) and with exact zeros."""
+    g = torch.Generator().manual_seed(5)
+    for R, kind in ((33, "gauss"), (4096, "gauss"), (4096, "ties"), (16384 + 40, "gauss"), (2048, "zeros")):
+        W = torch.randn(R, 256, generator=g) * 0.02
+        if kind == "ties":
+            W = torch.round(W * 200) / 200                          # a few dozen distinct values
+        if kind == "zeros":
+            W[:, 128 + 3::4] = 0.0
+        d = 0.5 + torch.rand(256, generator=g)
+        U = torch.diag(d).to(DEV)
+        outs = []
+        for fused in (False, True):
+            old = ops.set_fused_selection(fused)
+            try:
+                Wd = W.to(DEV).clone()
+                o = ops.block_step(Wd, U, 1, "crb")
+                torch.cuda.synchronize()
+            finally:
+                ops.set_fused_selection(old)
+            assert ops.read_status(o["workspace"]) == 0
+            outs.append((Wd.cpu(), o["Err"].cpu(), o["codes"].cpu(), o["trace"].cpu()))
+        for a, b in zip(outs[0], outs[1]):
+            assert torch.equal(a, b), (R, kind)
+
+
 @pytest.fixture(scope="module")
 def variants(golden_dir):
     return np.load(os.path.join(golden_dir, "variants.npz"))
