@@ -259,12 +259,15 @@ def run_ours(args):
     model.seqlen = args.seqlen
     qargs = crun.default_args(model=args.model, low_quant_method=args.technique, nsamples=args.nsamples,
                               device=str(dev), forward_batch=args.forward_batch, verbose=False,
-                              reprop_overlap=args.reprop_overlap)
+                              reprop_overlap=None if args.reprop_overlap is None else bool(args.reprop_overlap))
     loader = synthetic_calibration(model.config.vocab_size, args.nsamples, args.seqlen, seed=0)
 
     # ---- layer-0 inputs of this rank's sequences, kept in pinned host memory ----
     layers, pre = crun._decoder_parts(model)
-    mine = parallel.shard_range(len(loader), rank, world)
+    shard_sizes = parallel.plan_shards(len(loader), world,
+                                       {n: tuple(m.weight.shape) for n, m in crun.find_layers(layers[0]).items()},
+                                       skew=not args.no_shard_skew)
+    mine = parallel.shard_range(len(loader), rank, world, shard_sizes)
     sink = {"inps": [], "kwargs": {}}
     with torch.no_grad():
         res = [crun._Resident(m, dev) for m in pre] + [crun._Resident(layers[0], dev)]
@@ -398,6 +401,8 @@ def run_ours(args):
     e2e_ms = parallel.max_over_ranks(e2e_ms, dev)
     launches = int(parallel.sum_over_ranks(float(launches), dev))
     err_sum = parallel.sum_over_ranks(float(sum(errors)), dev)
+    act_bytes = int(parallel.sum_over_ranks(float(act_bytes), dev))          # all ranks' shards
+    layer_bytes = layer_bytes * world                                         # every rank copies the layer
     ms_per_step = dev_ms / args.steps
     value = ms_per_step * MODEL_LAYERS / 1e3
     e2e_value = e2e_ms / args.steps * MODEL_LAYERS / 1e3
@@ -422,14 +427,14 @@ def run_ours(args):
                 "data": "synthetic", "config": workload_config(args),
                 "e2e": {"value": e2e_value, "unit": "s", "h2d_bytes_per_step": layer_bytes + act_bytes,
                         "d2h_bytes_per_step": layer_bytes + act_bytes + 8 * 6,
-                        "note": "same call on pinned host buffers; per step the layer's weights and this rank's "
-                                "activation shard are copied in once (the shard stays on the device for the "
+                        "note": "same call on pinned host buffers, bytes summed over ranks; per step the layer's weights "
+                                "and each rank's activation shard are copied in once (the shard stays on the device for the "
                                 "re-propagation pass) and the quantized weights and the layer outputs are copied "
                                 "out; copies overlap compute"},
                 "gpu_launches": launches, "clocks": clocks, "roofline": roof, "roofline_extra": roof_extra,
                 "cpu_baseline": cpu, "reference_eager_gpu": ref_gpu,
                 "phases_ms_per_step": {k: v / args.steps for k, v in phases.items()},
-                "per_rank_ms_per_step": per_rank,
+                "per_rank_ms_per_step": per_rank, "sequences_per_rank": shard_sizes,
                 "block_error_sum_per_layer": err_sum / args.steps, "wall_clock_s_timed_region": wall,
                 "peaks": peaks["source"]}
         print(json.dumps(line))
@@ -440,7 +445,7 @@ def run_ours(args):
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of k_hessian_umma_pair on fp16
 # X [T, C], from an ncu capture of exactly that launch (profiles/k_hessian_umma_pair_fp16.txt);
 # the algorithmic bytes of the launch are T*C*2 + 2 * 4 * C*(C+256)/2 = 1.63e9.
-HESSIAN_DRAM_BYTES = {(16384, 16384): 7966005504 + 552323840}
+HESSIAN_DRAM_BYTES = {(16384, 16384): 10915788544 + 560216064}
 
 
 def hessian_roofline(dev, d, f, args, peaks):
@@ -592,8 +597,11 @@ def main():
     ap.add_argument("--seqlen", type=int, default=SEQLEN)
     ap.add_argument("--forward_batch", type=int, default=8)
     ap.add_argument("--no_cpu_baseline", action="store_true")
-    ap.add_argument("--reprop_overlap", action="store_true",
-                    help="forwards of the re-propagation pass on side streams, gated per linear (measured: no gain)")
+    ap.add_argument("--reprop_overlap", type=int, default=None, choices=(0, 1),
+                    help="forwards of the re-propagation pass on side streams, gated per linear "
+                         "(default: on with three ranks or more; no gain on one GPU)")
+    ap.add_argument("--no_shard_skew", action="store_true",
+                    help="split the calibration sequences evenly even when one rank owns the critical linear")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

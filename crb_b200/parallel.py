@@ -14,7 +14,7 @@ GPUs, gloo in the CPU tests).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -27,8 +27,14 @@ def world() -> Tuple[int, int]:
     return 0, 1
 
 
-def shard_range(n: int, rank: int, world_size: int) -> range:
-    """Contiguous, balanced slice of range(n) owned by `rank` (first n % world ranks get one more)."""
+def shard_range(n: int, rank: int, world_size: int, sizes: Optional[Sequence[int]] = None) -> range:
+    """Contiguous slice of range(n) owned by `rank`: `sizes[r]` items for rank r, or a balanced split
+    (the first n % world ranks get one more) when no sizes are given."""
+    if sizes is not None:
+        if len(sizes) != world_size or sum(sizes) != n or min(sizes) < 0:
+            raise ValueError(f"shard sizes {list(sizes)} do not partition {n} items over {world_size} ranks")
+        start = sum(sizes[:rank])
+        return range(start, start + sizes[rank])
     base, extra = divmod(n, world_size)
     start = rank * base + min(rank, extra)
     return range(start, start + base + (1 if rank < extra else 0))
@@ -55,6 +61,42 @@ def assign_owners(shapes: Dict[str, Tuple[int, int]], world_size: int) -> Dict[s
         owners[name] = r
         load[r] += linear_cost(*shapes[name])
     return owners
+
+
+def plan_shards(n: int, world_size: int, shapes: Optional[Dict[str, Tuple[int, int]]] = None,
+                skew: bool = True) -> List[int]:
+    """Calibration sequences per rank.
+
+    Balanced, unless one linear dominates: when the layer's LAST linear (`shapes` lists the linears
+    in the order the layer calls them) is also its most expensive one and its owner would be busy
+    for more than 1.5 times as long as any other rank, that owner is the critical path of every
+    layer: the other ranks sit idle while it quantizes and can run the second pass of their
+    sequences up to that last linear in the meantime (`reprop_overlap` in run.quantize_layer), but
+    the owner can only start its own second pass afterwards.  So the owner gets fewer sequences:
+    as many as it can re-propagate in the time the others need for the remaining part of theirs
+    (the last linear's share of the forward work).  Needs three ranks or more: with two, what the
+    single other rank loses in the first pass outweighs what the owner gains."""
+    even = [len(shard_range(n, r, world_size)) for r in range(world_size)]
+    if not skew or world_size < 3 or not shapes or n < 2 * world_size:
+        return even
+    names = list(shapes)
+    last = names[-1]
+    cost = {k: linear_cost(*shapes[k]) for k in names}
+    if cost[last] < max(cost.values()):
+        return even
+    owners = assign_owners(shapes, world_size)
+    load = [0.0] * world_size
+    for k in names:
+        load[owners[k]] += cost[k]
+    heavy = owners[last]
+    if load[heavy] < 1.5 * max(v for r, v in enumerate(load) if r != heavy):
+        return even
+    work = {k: float(shapes[k][0]) * shapes[k][1] for k in names}
+    tail = work[last] / sum(work.values())
+    mine = min(even[heavy], int(n * tail / (world_size - 1 + tail)) + 2)      # + 2: the weight broadcast
+    sizes = [len(shard_range(n - mine, r, world_size - 1)) for r in range(world_size - 1)]
+    sizes.insert(heavy, mine)
+    return sizes
 
 
 def allreduce_sum_(tensors: Sequence[torch.Tensor]) -> None:

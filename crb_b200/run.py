@@ -56,7 +56,7 @@ def default_args(**overrides) -> SimpleNamespace:
                         partition=3, global_scale=False, disable_gptq=False, minlayer=-1, maxlayer=1000,
                         quant_only="", invert=False, corr_damp=0.1, lam=1e-5, coupling=0.5,
                         device="cuda:0", seqlen=None, forward_batch=8, act_offload_gib=64.0, act_stage_gib=16.0,
-                        reprop_lanes=16, reprop_overlap=False, verbose=True, save_packed=None)
+                        reprop_lanes=16, reprop_overlap=None, shard_skew=True, verbose=True, save_packed=None)
     for k, v in overrides.items():
         setattr(a, k, v)
     return a
@@ -544,11 +544,13 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
     # Each binarized weight is written into the layer's weight storage on the linear's stream (then
     # broadcast when there are several ranks) and an event marks it; the host does not wait for a
     # block loop before everything, the second pass included, has been enqueued.
-    # `reprop_overlap` (off by default) lets the forwards of the second pass start before the last
-    # linear is done: its batches run on side streams and wait, in front of every linear, for that
-    # linear's event, so a forward runs up to the first linear that is still being quantized.  On a
-    # B200 this moved no time: the block loops and the forwards' GEMMs both need whole SMs (shared
-    # memory), so they take turns on the SMs instead of sharing them.
+    # `reprop_overlap` lets the forwards of the second pass start before the last linear is done:
+    # its batches run on side streams and wait, in front of every linear, for that linear's event,
+    # so a forward runs up to the first linear that is still being quantized.  On ONE B200 this moved
+    # no time (the block loops and the forwards' GEMMs both need whole SMs - shared memory - so they
+    # take turns on the SMs instead of sharing them): it is off there.  With three ranks or more it is
+    # on: the ranks that do not own the layer's most expensive linear would otherwise sit idle
+    # while its owner works (see parallel.plan_shards for the other half of that arrangement).
     with timer.span("fasterquant"):
         start = torch.cuda.Event()
         start.record(main)
@@ -586,7 +588,8 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
                     ready[name] = torch.cuda.Event()
                     ready[name].record(bc)
 
-        overlap = bool(getattr(args, "reprop_overlap", False))
+        overlap = getattr(args, "reprop_overlap", None)
+        overlap = ws >= 3 if overlap is None else bool(overlap)
         feed = feed2
         lanes = []
         if overlap:
@@ -652,7 +655,10 @@ def quant_sequential(model, dataloader, dev, args=None) -> dict:
     dtype = next(iter(model.parameters())).dtype
     hidden = model.config.hidden_size
     batches = list(dataloader)[: args.nsamples]
-    mine = parallel.shard_range(len(batches), rank, ws)
+    shard_sizes = getattr(args, "shard_sizes", None) or parallel.plan_shards(
+        len(batches), ws, {n: tuple(m.weight.shape) for n, m in find_layers(layers[0]).items()},
+        skew=dev.type == "cuda" and bool(getattr(args, "shard_skew", True)))
+    mine = parallel.shard_range(len(batches), rank, ws, shard_sizes)
 
     # ---- capture the inputs of layer 0 for this rank's sequences (run.py:175-201) ----
     sink = {"inps": [], "kwargs": {}}
@@ -750,9 +756,11 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--reprop_lanes", type=int, default=16,
                    help="with --reprop_overlap: batches that may be in flight (each on its own stream); each holds "
                         "one batch of intermediate activations")
-    p.add_argument("--reprop_overlap", action="store_true",
-                   help="start the forwards of the re-propagation pass (on side streams, gated per linear) while "
-                        "the layer's last linear is still being quantized")
+    p.add_argument("--reprop_overlap", type=int, default=None, choices=(0, 1),
+                   help="1: start the forwards of the re-propagation pass (on side streams, gated per linear) while "
+                        "the layer's last linear is still being quantized; default: on with three ranks or more")
+    p.add_argument("--no_shard_skew", dest="shard_skew", action="store_false",
+                   help="always split the calibration sequences evenly over the ranks")
     p.add_argument("--save_packed", type=str, default=None,
                    help="directory that receives the packed form (bit planes + scales) of every binarized linear")
     p.add_argument("--quiet", action="store_true")

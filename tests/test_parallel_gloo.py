@@ -30,6 +30,33 @@ def test_shard_range_partitions_the_sequences():
             assert max(map(len, parts)) - min(map(len, parts)) <= 1
 
 
+def test_sized_shards_and_the_plan_for_a_dominant_last_linear():
+    assert [list(parallel.shard_range(7, r, 3, [1, 4, 2])) for r in range(3)] == [[0], [1, 2, 3, 4], [5, 6]]
+    with pytest.raises(ValueError):
+        parallel.shard_range(7, 0, 3, [1, 4, 1])
+    opt = {"self_attn.k_proj": (4096, 4096), "self_attn.v_proj": (4096, 4096), "self_attn.q_proj": (4096, 4096),
+           "self_attn.out_proj": (4096, 4096), "fc1": (16384, 4096), "fc2": (4096, 16384)}
+    # one or two ranks, no shapes, or skew switched off: balanced
+    assert parallel.plan_shards(128, 1, opt) == [128]
+    assert parallel.plan_shards(128, 2, opt) == [64, 64]
+    assert parallel.plan_shards(128, 8, None) == [16] * 8
+    assert parallel.plan_shards(128, 8, opt, skew=False) == [16] * 8
+    # fc2 is the last and by far the most expensive linear: its owner (rank 0) gets about a third of
+    # what the others get (fc2 is a third of the layer's forward work), the rest is balanced
+    for ws in (3, 4, 8):
+        sizes = parallel.plan_shards(128, ws, opt)
+        heavy = parallel.assign_owners(opt, ws)["fc2"]
+        assert sum(sizes) == 128 and len(sizes) == ws
+        others = [v for r, v in enumerate(sizes) if r != heavy]
+        assert max(others) - min(others) <= 1
+        assert others[0] / 3 <= sizes[heavy] <= others[0] / 3 + 3
+    # the last linear is not the most expensive one: balanced
+    flat = {"a": (4096, 16384), "b": (4096, 4096)}
+    assert parallel.plan_shards(128, 4, flat) == [32] * 4
+    # too few sequences to skew
+    assert parallel.plan_shards(6, 4, opt) == [2, 2, 1, 1]
+
+
 def test_owner_assignment_is_deterministic_and_balanced():
     shapes = {"self_attn.q_proj": (4096, 4096), "self_attn.k_proj": (4096, 4096), "self_attn.v_proj": (4096, 4096),
               "self_attn.out_proj": (4096, 4096), "fc1": (16384, 4096), "fc2": (4096, 16384)}
@@ -71,7 +98,7 @@ class _CpuGptq:
         self._S = None
 
 
-def _worker(rank, world, port, result_path):
+def _worker(rank, world, port, result_path, shard_sizes=None):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     if world > 1:
         dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -84,14 +111,20 @@ def _worker(rank, world, port, result_path):
     loader = synthetic_calibration(model.config.vocab_size, nsamples=8, seqlen=64, seed=1)
     args = crun.default_args(low_quant_method="braq", nsamples=8, forward_batch=2, verbose=False, device="cpu")
     args.percdamp = 0.1          # few calibration tokens: keep the tiny Hessians well conditioned
+    args.shard_sizes = shard_sizes
     out = crun.quant_sequential(model, loader, "cpu", args)
     layer = model.model.decoder.layers[0]
     weights = {n: m.weight.data.clone() for n, m in crun.find_layers(layer).items()}
     hidden = out["final_hidden"]
     if world > 1:
-        gathered = [torch.zeros_like(hidden) for _ in range(world)]
-        dist.all_gather(gathered, hidden)
-        hidden = torch.cat(gathered, 0)
+        # shards may differ in size: gather through a buffer of the largest one
+        n_max = int(parallel.max_over_ranks(float(hidden.shape[0]), "cpu"))
+        padded = torch.zeros((n_max,) + tuple(hidden.shape[1:]), dtype=hidden.dtype)
+        padded[:hidden.shape[0]] = hidden
+        gathered = [torch.zeros_like(padded) for _ in range(world)]
+        dist.all_gather(gathered, padded)
+        sizes = shard_sizes or [len(parallel.shard_range(8, r, world)) for r in range(world)]
+        hidden = torch.cat([g[:k] for g, k in zip(gathered, sizes)], 0)
     errors = {n: parallel.sum_over_ranks(e, "cpu") for n, e in out["errors"][0].items()}
     if rank == 0:
         torch.save({"weights": weights, "hidden": hidden, "error_sum": out["error_sum"],
@@ -117,6 +150,20 @@ def test_two_ranks_reproduce_the_single_rank_run(tmp_path):
     for n in a["errors"]:
         # every linear was quantized exactly once, on its owner, from the full (summed) Hessian:
         # a missing all-reduce or a wrong sample count would move these by a factor, not by rounding
+        assert abs(a["errors"][n] - b["errors"][n]) <= 2e-2 * abs(a["errors"][n]), (n, a["errors"][n], b["errors"][n])
+    assert a["hidden"].shape == b["hidden"].shape
+    rel = (a["hidden"] - b["hidden"]).norm() / a["hidden"].norm()
+    assert rel < 0.05, float(rel)
+
+
+@pytest.mark.timeout(600)
+def test_three_ranks_with_uneven_shards_reproduce_the_single_rank_run(tmp_path):
+    single, triple = str(tmp_path / "w1.pt"), str(tmp_path / "w3.pt")
+    mp.spawn(_worker, args=(1, _free_port(), single), nprocs=1, join=True)
+    mp.spawn(_worker, args=(3, _free_port(), triple, [1, 4, 3]), nprocs=3, join=True)
+    a, b = torch.load(single), torch.load(triple)
+    assert abs(a["error_sum"] - b["error_sum"]) <= 2e-3 * abs(a["error_sum"])
+    for n in a["errors"]:
         assert abs(a["errors"][n] - b["errors"][n]) <= 2e-2 * abs(a["errors"][n]), (n, a["errors"][n], b["errors"][n])
     assert a["hidden"].shape == b["hidden"].shape
     rel = (a["hidden"] - b["hidden"]).norm() / a["hidden"].norm()
