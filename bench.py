@@ -262,36 +262,46 @@ def run_ours(args):
                               reprop_overlap=None if args.reprop_overlap is None else bool(args.reprop_overlap))
     loader = synthetic_calibration(model.config.vocab_size, args.nsamples, args.seqlen, seed=0)
 
-    # ---- layer-0 inputs of this rank's sequences, kept in pinned host memory ----
+    # ---- layer-0 inputs of this rank's sequences, kept in pinned host memory.  The two arms shard the
+    # sequences differently from three ranks on: with device-resident activations the owner of the
+    # layer's dominant last linear gets fewer sequences (parallel.plan_shards); with host buffers the
+    # split stays even, because there the copies of a shard need the whole layer to hide behind ----
     layers, pre = crun._decoder_parts(model)
-    shard_sizes = parallel.plan_shards(len(loader), world,
-                                       {n: tuple(m.weight.shape) for n, m in crun.find_layers(layers[0]).items()},
-                                       skew=not args.no_shard_skew)
-    mine = parallel.shard_range(len(loader), rank, world, shard_sizes)
-    sink = {"inps": [], "kwargs": {}}
-    with torch.no_grad():
-        res = [crun._Resident(m, dev) for m in pre] + [crun._Resident(layers[0], dev)]
-        for r in res:
-            r.__enter__()
-        layers[0] = crun._Catcher(layers[0], sink)
-        for j in mine:
-            try:
-                model(loader[j][0].to(dev))
-            except ValueError:
-                pass
-        layers[0] = layers[0].module
-        for r in reversed(res):
-            r.__exit__()
+    shapes0 = {n: tuple(m.weight.shape) for n, m in crun.find_layers(layers[0]).items()}
+    shard_sizes = parallel.plan_shards(len(loader), world, shapes0, skew=not args.no_shard_skew)
+    shard_sizes_host = parallel.plan_shards(len(loader), world, shapes0, skew=False)
     hidden = model.config.hidden_size
     dtype = next(iter(model.parameters())).dtype
-    n_local = len(sink["inps"])
-    host_in = torch.empty((n_local, args.seqlen, hidden), dtype=dtype, pin_memory=True)
-    for j, x in enumerate(sink["inps"]):
-        host_in[j].copy_(x.reshape(args.seqlen, hidden))
-    host_out = torch.empty_like(host_in, pin_memory=True)
-    dev_in = torch.empty((n_local, args.seqlen, hidden), dtype=dtype, device=dev)
+    sink = {"inps": [], "kwargs": {}}
+
+    def capture(sizes):
+        mine = parallel.shard_range(len(loader), rank, world, sizes)
+        sink["inps"].clear()
+        with torch.no_grad():
+            res = [crun._Resident(m, dev) for m in pre] + [crun._Resident(layers[0], dev)]
+            for r in res:
+                r.__enter__()
+            layers[0] = crun._Catcher(layers[0], sink)
+            for j in mine:
+                try:
+                    model(loader[j][0].to(dev))
+                except ValueError:
+                    pass
+            layers[0] = layers[0].module
+            for r in reversed(res):
+                r.__exit__()
+        buf = torch.empty((len(sink["inps"]), args.seqlen, hidden), dtype=dtype, pin_memory=True)
+        for j, x in enumerate(sink["inps"]):
+            buf[j].copy_(x.reshape(args.seqlen, hidden))
+        return buf
+
+    first = capture(shard_sizes)
+    dev_in = torch.empty(tuple(first.shape), dtype=dtype, device=dev)
     dev_out = torch.empty_like(dev_in)
-    dev_in.copy_(host_in)
+    dev_in.copy_(first)
+    host_in = first if shard_sizes_host == shard_sizes else capture(shard_sizes_host)
+    del first
+    host_out = torch.empty_like(host_in, pin_memory=True)
     layer_kwargs = sink["kwargs"]
     sink["inps"].clear()
     layer_bytes = sum(p.numel() * p.element_size() for p in layers[0].parameters())
@@ -353,22 +363,27 @@ def run_ours(args):
     # pinned host memory and end there; quantize_layer streams the activations through the device
     # batch by batch (once in, once out) and the weights of the next / previous layer move while a
     # layer is being quantized.  Timed as a whole: first copy in to last copy out. ----
-    host_in.copy_(dev_in)
     torch.cuda.synchronize()
+    qargs_host = crun.default_args(**{**vars(qargs), "reprop_overlap": bool(args.reprop_overlap)})
 
     def host_steps(first, count):
         nonlocal host_in, host_out
         if count <= 0:
             return
-        nxt = crun._Resident(layers[first], dev).prefetch()
+        # one rank (a different one per layer) reads the layer from host memory, the others receive it
+        # over NVLink; the quantized layer goes back to rank 0's host copy
+        def resident(i):
+            return crun._Resident(layers[i], dev, loader=i % world, keeper=0)
+
+        nxt = resident(first).prefetch()
         leaving = None
         for i in range(first, first + count):
             res, nxt = nxt, None
             layer = res.__enter__()
             if i + 1 < first + count:
-                nxt = crun._Resident(layers[i + 1], dev).prefetch()
+                nxt = resident(i + 1).prefetch()
             with torch.no_grad():
-                crun.quantize_layer(layer, i, host_in, host_out, layer_kwargs, qargs, dev, None)
+                crun.quantize_layer(layer, i, host_in, host_out, layer_kwargs, qargs_host, dev, None)
             if leaving is not None:
                 leaving.finish()
             res.__exit__(defer=True)
@@ -402,7 +417,7 @@ def run_ours(args):
     launches = int(parallel.sum_over_ranks(float(launches), dev))
     err_sum = parallel.sum_over_ranks(float(sum(errors)), dev)
     act_bytes = int(parallel.sum_over_ranks(float(act_bytes), dev))          # all ranks' shards
-    layer_bytes = layer_bytes * world                                         # every rank copies the layer
+    # the layer itself crosses PCIe once each way whatever the number of ranks
     ms_per_step = dev_ms / args.steps
     value = ms_per_step * MODEL_LAYERS / 1e3
     e2e_value = e2e_ms / args.steps * MODEL_LAYERS / 1e3
@@ -428,6 +443,7 @@ def run_ours(args):
                 "e2e": {"value": e2e_value, "unit": "s", "h2d_bytes_per_step": layer_bytes + act_bytes,
                         "d2h_bytes_per_step": layer_bytes + act_bytes + 8 * 6,
                         "note": "same call on pinned host buffers, bytes summed over ranks; per step the layer's weights "
+                                "(read from host memory by one rank, passed on over NVLink) "
                                 "and each rank's activation shard are copied in once (the shard stays on the device for the "
                                 "re-propagation pass) and the quantized weights and the layer outputs are copied "
                                 "out; copies overlap compute"},
@@ -435,6 +451,7 @@ def run_ours(args):
                 "cpu_baseline": cpu, "reference_eager_gpu": ref_gpu,
                 "phases_ms_per_step": {k: v / args.steps for k, v in phases.items()},
                 "per_rank_ms_per_step": per_rank, "sequences_per_rank": shard_sizes,
+                "sequences_per_rank_e2e": shard_sizes_host,
                 "block_error_sum_per_layer": err_sum / args.steps, "wall_clock_s_timed_region": wall,
                 "peaks": peaks["source"]}
         print(json.dumps(line))

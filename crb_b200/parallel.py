@@ -136,10 +136,27 @@ def allreduce_hessians_(sums: Sequence[torch.Tensor]) -> None:
         off += n
 
 
-def broadcast_(tensor: torch.Tensor, src: int) -> None:
+def broadcast_(tensor: torch.Tensor, src: int, group=None) -> None:
     _, ws = world()
     if ws > 1:
-        dist.broadcast(tensor, src=src)
+        dist.broadcast(tensor, src=src, group=group)
+
+
+_WEIGHTS_GROUP = None
+
+
+def weights_group():
+    """A process group of all ranks used only for streaming layer weights in (run._Resident): its
+    collectives have their own communicator, so a weight broadcast that waits for a copy from host
+    memory never holds up the Hessian all-reduce or the broadcast of a finished linear.  Created on
+    first use; every rank reaches that point in the same program order."""
+    global _WEIGHTS_GROUP
+    _, ws = world()
+    if ws == 1:
+        return None
+    if _WEIGHTS_GROUP is None:
+        _WEIGHTS_GROUP = dist.new_group()
+    return _WEIGHTS_GROUP
 
 
 def max_over_ranks(value: float, device) -> float:

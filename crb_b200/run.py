@@ -56,7 +56,7 @@ def default_args(**overrides) -> SimpleNamespace:
                         partition=3, global_scale=False, disable_gptq=False, minlayer=-1, maxlayer=1000,
                         quant_only="", invert=False, corr_damp=0.1, lam=1e-5, coupling=0.5,
                         device="cuda:0", seqlen=None, forward_batch=8, act_offload_gib=64.0, act_stage_gib=16.0,
-                        reprop_lanes=16, reprop_overlap=None, shard_skew=True, verbose=True, save_packed=None)
+                        reprop_lanes=16, reprop_overlap=None, shard_skew=True, replicate_result=False, verbose=True, save_packed=None)
     for k, v in overrides.items():
         setattr(a, k, v)
     return a
@@ -130,26 +130,50 @@ class _Resident:
     the layer before); `__enter__` then only makes the current stream wait for them.
     `__exit__(defer=True)` starts the copies back on a side stream and returns at once; `finish()`
     waits for them.  The plain `with` form does both synchronously.
+
+    With several ranks every process holds the same model in host memory, and N copies of a layer
+    over PCIe cost the host N times the traffic.  `loader` names the one rank that reads its host
+    copy; the others receive the layer over NVLink (a broadcast on `parallel.weights_group()`).
+    `keeper` names the one rank whose host copy receives the (quantized) parameters at the end; on
+    the other ranks the module simply points at its untouched host tensors again.  Both default to
+    None: every rank copies in and out for itself.
     """
 
-    def __init__(self, module: nn.Module, dev):
+    def __init__(self, module: nn.Module, dev, loader: Optional[int] = None, keeper: Optional[int] = None):
         self.module, self.dev, self.host = module, dev, {}
         self._ready = None
         self._back = None
         self._keep = []
+        rank, ws = parallel.world()
+        shared = ws > 1 and torch.device(dev).type == "cuda"
+        self.loader = loader if shared else None
+        self.keeper = keeper if shared else None
+        self.rank = rank
 
     def _tensors(self):
         return list(self.module.named_parameters()) + list(self.module.named_buffers())
+
+    def _bring_in(self):
+        """Host -> device for every parameter still on the host, on the current stream."""
+        group = parallel.weights_group() if self.loader is not None else None
+        for name, p in self._tensors():
+            if p.device.type == "cuda":
+                continue
+            self.host[name] = p.data
+            shared = self.loader is not None and p.data.is_contiguous()     # same on every rank
+            if not shared or self.rank == self.loader:
+                p.data = p.data.to(self.dev, non_blocking=True)
+            else:
+                p.data = torch.empty(p.data.shape, dtype=p.data.dtype, device=self.dev)
+            if shared:
+                parallel.broadcast_(p.data, self.loader, group)
 
     def prefetch(self):
         if torch.device(self.dev).type != "cuda" or self._ready is not None:
             return self
         h2d = _copy_streams(self.dev)[0]
         with torch.cuda.stream(h2d):
-            for name, p in self._tensors():
-                if p.device.type != "cuda":
-                    self.host[name] = p.data
-                    p.data = p.data.to(self.dev, non_blocking=True)
+            self._bring_in()
             self._ready = torch.cuda.Event()
             self._ready.record(h2d)
         return self
@@ -160,10 +184,7 @@ class _Resident:
         if self._ready is not None:
             torch.cuda.current_stream(self.dev).wait_event(self._ready)
             return self.module
-        for name, p in self._tensors():
-            if p.device.type != "cuda":
-                self.host[name] = p.data
-                p.data = p.data.to(self.dev, non_blocking=True)
+        self._bring_in()
         return self.module
 
     def __exit__(self, *exc, defer=False):
@@ -174,10 +195,12 @@ class _Resident:
         stream = _copy_streams(self.dev)[1] if defer else main
         if defer:
             stream.wait_stream(main)
+        keep = self.keeper is None or self.rank == self.keeper
         with torch.cuda.stream(stream):
             for name, host in self.host.items():
                 p = tensors[name]
-                host.copy_(p.data, non_blocking=True)
+                if keep:
+                    host.copy_(p.data, non_blocking=True)
                 self._keep.append(p.data)            # the device copy lives until the copy back is done
                 p.data = host
             self._back = torch.cuda.Event()
@@ -549,8 +572,9 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
     # so a forward runs up to the first linear that is still being quantized.  On ONE B200 this moved
     # no time (the block loops and the forwards' GEMMs both need whole SMs - shared memory - so they
     # take turns on the SMs instead of sharing them): it is off there.  With three ranks or more it is
-    # on: the ranks that do not own the layer's most expensive linear would otherwise sit idle
-    # while its owner works (see parallel.plan_shards for the other half of that arrangement).
+    # on (for device-resident activations): the ranks that do not own the layer's most expensive
+    # linear would otherwise sit idle while its owner works (see parallel.plan_shards for the other
+    # half of that arrangement).
     with timer.span("fasterquant"):
         start = torch.cuda.Event()
         start.record(main)
@@ -589,7 +613,10 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
                     ready[name].record(bc)
 
         overlap = getattr(args, "reprop_overlap", None)
-        overlap = ws >= 3 if overlap is None else bool(overlap)
+        if overlap is None:
+            # host-resident activations: started early, the forwards would all end together and leave
+            # the copies of their outputs nothing to hide behind
+            overlap = ws >= 3 and inps.device.type == "cuda"
         feed = feed2
         lanes = []
         if overlap:
@@ -655,9 +682,12 @@ def quant_sequential(model, dataloader, dev, args=None) -> dict:
     dtype = next(iter(model.parameters())).dtype
     hidden = model.config.hidden_size
     batches = list(dataloader)[: args.nsamples]
+    # (uneven shards pay only while the activations stay on the device: the copies of host-resident
+    # shards need the whole layer to hide behind, see quantize_layer)
+    stays_on_device = (len(batches) / ws) * model.seqlen * hidden * 2 <= args.act_offload_gib * (1024 ** 3)
     shard_sizes = getattr(args, "shard_sizes", None) or parallel.plan_shards(
         len(batches), ws, {n: tuple(m.weight.shape) for n, m in find_layers(layers[0]).items()},
-        skew=dev.type == "cuda" and bool(getattr(args, "shard_skew", True)))
+        skew=dev.type == "cuda" and stays_on_device and bool(getattr(args, "shard_skew", True)))
     mine = parallel.shard_range(len(batches), rank, ws, shard_sizes)
 
     # ---- capture the inputs of layer 0 for this rank's sequences (run.py:175-201) ----
@@ -694,13 +724,21 @@ def quant_sequential(model, dataloader, dev, args=None) -> dict:
     t0 = time.time()
     # weights stream through the device: layer i + 1 is copied in and layer i - 1 copied out while
     # layer i is being quantized
-    nxt = _Resident(layers[0], dev).prefetch() if len(layers) else None
+    # (with several ranks one of them, a different one per layer, reads the layer from host memory and
+    # the others get it over NVLink; the result goes back to rank 0's host copy only, unless
+    # `replicate_result` asks for every rank's)
+    keeper = None if getattr(args, "replicate_result", False) else 0
+
+    def resident(i):
+        return _Resident(layers[i], dev, loader=i % ws, keeper=keeper)
+
+    nxt = resident(0).prefetch() if len(layers) else None
     leaving = None
     for i in range(len(layers)):
         res, nxt = nxt, None
         layer = res.__enter__()
         if i + 1 < len(layers):
-            nxt = _Resident(layers[i + 1], dev).prefetch()
+            nxt = resident(i + 1).prefetch()
         layer_traces = {} if getattr(args, "keep_traces", False) else None
         errs = quantize_layer(layer, i, inps, outs, layer_kwargs, args, dev, timer, layer_traces)
         all_traces.append(layer_traces)
@@ -759,6 +797,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--reprop_overlap", type=int, default=None, choices=(0, 1),
                    help="1: start the forwards of the re-propagation pass (on side streams, gated per linear) while "
                         "the layer's last linear is still being quantized; default: on with three ranks or more")
+    p.add_argument("--replicate_result", action="store_true",
+                   help="several ranks: write the binarized weights back into every rank's host copy of the model "
+                        "(default: rank 0's only)")
     p.add_argument("--no_shard_skew", dest="shard_skew", action="store_false",
                    help="always split the calibration sequences evenly over the ranks")
     p.add_argument("--save_packed", type=str, default=None,
