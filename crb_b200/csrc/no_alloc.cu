@@ -20,8 +20,10 @@
 //     the GPU (different streams, or different host threads without ordering) race on the
 //     array and give undefined results: serialise them;
 //   * the first call on each device resolves the device address of the array
-//     (cudaGetSymbolAddress, with that device current).  Make that first call outside any
-//     stream capture.
+//     (cudaGetSymbolAddress, with that device current); with lazy module loading this is
+//     also the call that places the library's device code and the array on that GPU, so the
+//     promise of no allocation holds from the second call on.  Make that first call outside
+//     any stream capture.
 #include <mutex>
 
 #include "common.cuh"

@@ -108,10 +108,13 @@ _STREAMS: Dict[object, list] = {}
 
 
 def _copy_streams(dev):
-    """(host->device, device->host, weight broadcast) side streams of a device, created once."""
+    """(activations host->device, device->host, weight broadcast, weights host->device) side streams
+    of a device, created once.  Layer weights have a stream of their own on the way in: the next
+    layer's 0.4 GB are requested when a layer starts, and on the activations' stream they would sit
+    in front of that layer's first calibration batch."""
     key = ("copy", torch.device(dev).index or 0)
     if key not in _STREAMS:
-        _STREAMS[key] = [torch.cuda.Stream(device=dev) for _ in range(3)]
+        _STREAMS[key] = [torch.cuda.Stream(device=dev) for _ in range(4)]
     return _STREAMS[key]
 
 
@@ -171,7 +174,7 @@ class _Resident:
     def prefetch(self):
         if torch.device(self.dev).type != "cuda" or self._ready is not None:
             return self
-        h2d = _copy_streams(self.dev)[0]
+        h2d = _copy_streams(self.dev)[3]
         with torch.cuda.stream(h2d):
             self._bring_in()
             self._ready = torch.cuda.Event()

@@ -138,8 +138,10 @@ int crb_block_step(float *W_dev, int R, int64_t ldw, const float *U_dev, int64_t
  *   - flags_out (optional, device): receives this call's status flags (CRB_FLAG_*);
  *   - all calls on one device share the array: calls that overlap on the GPU race, so order
  *     them on one stream (or with events);
- *   - the first call on each device looks up the array's device address; make that call
- *     before starting any stream capture.                                                   */
+ *   - the first call on each device looks up the array's device address, and where the CUDA
+ *     runtime loads modules lazily that look-up is also what loads the library's device code
+ *     (the array included) onto the GPU: "no allocation" holds from the second call on.  Make
+ *     that first call before starting any stream capture.                                   */
 #define CRB_STATIC_MAX_ROWS 16384
 int crb_block_step_static_max_rows(void);
 int crb_block_step_static(float *W_dev, int R, int64_t ldw, const float *U_dev, int64_t ldu, int block,
