@@ -55,6 +55,7 @@ SIGNATURES = {
     "crb_launch_count": (C.c_ulonglong, []),
     "crb_set_dependent_launch": (_i, [_i]),
     "crb_set_fused_selection": (_i, [_i]),
+    "crb_set_trailing_lookahead": (_i, [_i]),
     "crb_selftest_wait_limit": (_i, [_vp, _sz, C.c_uint, _vp, _vp]),
 }
 

@@ -8,6 +8,7 @@ namespace crb {
 std::atomic<unsigned long long> g_launches{0};
 std::atomic<int> g_dependent_launch{1};
 std::atomic<int> g_fused_selection{0};
+std::atomic<int> g_trailing_lookahead{1};
 
 // block_step.cu
 size_t block_workspace_bytes(int R);
@@ -60,6 +61,10 @@ const char* crb_status_string(int status) {
 
 int crb_set_dependent_launch(int enable) {
     return g_dependent_launch.exchange(enable ? 1 : 0);
+}
+
+int crb_set_trailing_lookahead(int mode) {
+    return g_trailing_lookahead.exchange(mode < 0 ? 0 : mode > 2 ? 2 : mode);
 }
 
 int crb_set_fused_selection(int enable) {
@@ -152,8 +157,14 @@ static_assert(CRB_GEMM_LOWER_ONLY == GEMM_LOWER_ONLY && CRB_GEMM_B_LOWER == GEMM
 
 size_t crb_linear_workspace_bytes(int R) {
     if (R <= 0) return 0;
-    return align256(block_workspace_bytes(R)) + align256(sizeof(float) * (size_t)R * kBlock * kGroup);
+    // block-step scratch + the errors of two groups of blocks (the current one, and the previous one
+    // while its trailing update may still be running beside the current group)
+    return align256(block_workspace_bytes(R)) + 2 * align256(sizeof(float) * (size_t)R * kBlock * kGroup);
 }
+
+// Grid of the far part of a trailing update when it runs beside the next group's block steps: the
+// rest of the SMs stays with the block steps and their in-group products.
+constexpr int kFarCtas = 64;      // measured at 4096 x 16384: 40 -> 20.8 ms per loop, 64 / 96 -> 18.6 ms (19.8 without look-ahead)
 
 int crb_quantize_linear(float* W, int R, int C, int64_t ldw, const float* U, int64_t ldu,
                         int technique, int orders, float lam, float corr_damp, int metric, float* Losses,
@@ -164,13 +175,28 @@ int crb_quantize_linear(float* W, int R, int C, int64_t ldw, const float* U, int
     if (workspace_bytes < crb_linear_workspace_bytes(R)) return CRB_ERR_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t bws = align256(block_workspace_bytes(R));
-    float* ErrG = reinterpret_cast<float*>(static_cast<char*>(workspace) + bws);      // [R, kGroup * 128]
+    const size_t group_bytes = align256(sizeof(float) * (size_t)R * kBlock * kGroup);
     const int64_t ld_err = (int64_t)kGroup * kBlock;
     unsigned* status = static_cast<unsigned*>(workspace);
     if (cudaMemsetAsync(workspace, 0, 64, st) != cudaSuccess) return CRB_ERR_LAUNCH;   // status word
     const int nblk = C / kBlock, grp = kGroup;
+    const int ngroups = (nblk + grp - 1) / grp;
+    // Look-ahead over the trailing updates.  After a group of 8 blocks every later column needs
+    // W -= Err_group U[group rows, column], but the next group only needs its own 1024 columns.
+    // Those are updated on the caller's stream; the rest (a large product at the GEMM's full rate)
+    // runs on a side stream with a capped grid beside the next group's block steps, which are
+    // chains of short kernels.  Every element still receives its updates group by group in the
+    // same order and from the same products, so the result is the same bit for bit.  It pays for
+    // wide, short weights (the trailing products are a quarter of the loop at 4096 x 16384); the
+    // block steps of tall weights need all SMs themselves.
+    const int mode = g_trailing_lookahead.load(std::memory_order_relaxed);
+    const bool ahead = ngroups > 2 && (mode == 2 || (mode == 1 && C >= 8192 && R <= 8192));
+    SideContext* sc = ahead ? side_context(st, (size_t)ngroups + 1) : nullptr;
+    if (ahead && !sc) return CRB_ERR_LAUNCH;
+    int far_pending = -1;           // group whose far update is in flight on the side stream (events[g] marks its end)
     for (int b = 0; b < nblk; ++b) {
-        const int g0 = b / grp * grp, g1 = g0 + grp < nblk ? g0 + grp : nblk;
+        const int g = b / grp, g0 = g * grp, g1 = g0 + grp < nblk ? g0 + grp : nblk;
+        float* ErrG = reinterpret_cast<float*>(static_cast<char*>(workspace) + bws + (size_t)(ahead ? g & 1 : 0) * group_bytes);
         float* Err = ErrG + (size_t)(b - g0) * kBlock;
         int rc = block_step_launch(W, R, ldw, U, ldu, b, technique, orders, lam, corr_damp, metric, Err, ld_err, Losses, codes,
                                    C, scales ? scales + (size_t)b * R * 8 : nullptr,
@@ -180,13 +206,35 @@ int crb_quantize_linear(float* W, int R, int C, int64_t ldw, const float* U, int
         rc = gemm_tf32x3(false, 0, R, g1 * kBlock - ed, kBlock, -1.0f, Err, ld_err,
                          U + (int64_t)b * kBlock * ldu + ed, ldu, 1.0f, W + ed, ldw, status, st);
         if (rc != CRB_OK) return rc;
-        if (b == g1 - 1 && g1 < nblk) {
-            const int gd = g1 * kBlock;
-            rc = gemm_tf32x3(false, 0, R, C - gd, (g1 - g0) * kBlock, -1.0f, ErrG, ld_err,
-                             U + (int64_t)g0 * kBlock * ldu + gd, ldu, 1.0f, W + gd, ldw, status, st);
+        if (b != g1 - 1 || g1 >= nblk) continue;
+        const int gd = g1 * kBlock, kk = (g1 - g0) * kBlock;
+        const float* Ug = U + (int64_t)g0 * kBlock * ldu;
+        if (!ahead) {
+            rc = gemm_tf32x3(false, 0, R, C - gd, kk, -1.0f, ErrG, ld_err, Ug + gd, ldu, 1.0f, W + gd, ldw, status, st);
             if (rc != CRB_OK) return rc;
+            continue;
         }
+        // the previous group's far update wrote the columns this one is about to update (and has
+        // read the error buffer the next group will overwrite)
+        if (far_pending >= 0 && cudaStreamWaitEvent(st, sc->events[far_pending], 0) != cudaSuccess) return CRB_ERR_LAUNCH;
+        far_pending = -1;
+        const int near = C - gd < grp * kBlock ? C - gd : grp * kBlock;
+        rc = gemm_tf32x3(false, 0, R, near, kk, -1.0f, ErrG, ld_err, Ug + gd, ldu, 1.0f, W + gd, ldw, status, st);
+        if (rc != CRB_OK) return rc;
+        const int far = C - gd - near;
+        if (far <= 0) continue;
+        // fork: the side stream starts once this group's errors are complete (they are: the near
+        // update above is ordered behind them on this stream)
+        if (cudaEventRecord(sc->events[ngroups], st) != cudaSuccess ||
+            cudaStreamWaitEvent(sc->side, sc->events[ngroups], 0) != cudaSuccess)
+            return CRB_ERR_LAUNCH;
+        rc = gemm_tf32x3(false, 0, R, far, kk, -1.0f, ErrG, ld_err, Ug + gd + near, ldu, 1.0f, W + gd + near, ldw,
+                         status, sc->side, nullptr, kFarCtas);
+        if (rc != CRB_OK) return rc;
+        if (cudaEventRecord(sc->events[g], sc->side) != cudaSuccess) return CRB_ERR_LAUNCH;
+        far_pending = g;
     }
+    if (far_pending >= 0 && cudaStreamWaitEvent(st, sc->events[far_pending], 0) != cudaSuccess) return CRB_ERR_LAUNCH;
     return CRB_OK;
 }
 

@@ -6,6 +6,7 @@
 
 #include <atomic>
 #include <mutex>
+#include <vector>
 
 #include "../../include/crb_b200.h"
 
@@ -151,6 +152,17 @@ __device__ __forceinline__ bool last_cta_done(unsigned* counter, unsigned total)
     return s_last;
 }
 
+// A second stream per (device, caller stream) with the caller stream's priority, and a pool of events
+// to fork to it and join it again (factor.cu keeps the table).  Used where a chain of small kernels
+// on the caller's stream can run beside work that only a later step needs.
+struct SideContext {
+    cudaStream_t side = nullptr;
+    std::vector<cudaEvent_t> events;
+};
+SideContext* side_context(cudaStream_t main, size_t n_events);
+
+extern std::atomic<int> g_trailing_lookahead;   // 0 off, 1 by shape (default), 2 always; crb_set_trailing_lookahead()
+
 // Shape flags of gemm_tf32x3 (gemm_tc.cu).
 constexpr int GEMM_LOWER_ONLY = 1;   // write only the 128 x 128 blocks of C on or below the diagonal
 constexpr int GEMM_B_LOWER = 2;      // the [K, N] operand B is lower triangular (zero for k < n)
@@ -164,6 +176,6 @@ struct GemmSelfTest {
 };
 int gemm_tf32x3(bool b_is_nk, int shape, int M, int N, int K, float alpha, const float* A, int64_t lda,
                 const float* B, int64_t ldb, float beta, float* C, int64_t ldc, unsigned* status,
-                cudaStream_t st, const GemmSelfTest* selftest = nullptr);
+                cudaStream_t st, const GemmSelfTest* selftest = nullptr, int max_ctas = 0);
 
 }  // namespace crb

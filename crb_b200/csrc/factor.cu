@@ -452,14 +452,10 @@ static int invert_panel_local(float* A, int C, int lo, int hi, int panel, float*
 // A second stream per caller stream, and events to fork to it and join it again.  The merges inside
 // an outer panel are chains of small, latency-bound products: they run there while the caller's
 // stream goes on with the next panels of the factorisation.
-struct SideContext {
-    cudaStream_t side = nullptr;
-    std::vector<cudaEvent_t> events;
-};
 static std::mutex g_side_lock;
 static std::map<std::pair<int, cudaStream_t>, SideContext> g_side;
 
-static SideContext* side_context(cudaStream_t main, size_t n_events) {
+SideContext* side_context(cudaStream_t main, size_t n_events) {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
     std::lock_guard<std::mutex> guard(g_side_lock);

@@ -366,12 +366,13 @@ k_gemm_tf32x3(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
 // C[M,N] = alpha * A[M,K] * op(B) + beta * C on the tensor cores.
 // Requirements: K % 16 == 0, N % 32 == 0, leading dimensions % 4 == 0, 16-byte aligned bases.
 // `status` (device, may be NULL) receives CRB_FLAG_WAIT_LIMIT if a bounded wait ran out.
+// `max_ctas` > 0 caps the persistent grid (default: one CTA per SM).
 // `shape` is a set of GEMM_* flags: GEMM_LOWER_ONLY writes only the 128 x 128 blocks on or below
 // the diagonal of C; GEMM_B_LOWER / GEMM_A_LOWER promise a lower-triangular [K, N] operand B /
 // [M, K] operand A, whose zero part is then not multiplied.
 int gemm_tf32x3(bool b_is_nk, int shape, int M, int N, int K, float alpha, const float* A, int64_t lda,
                 const float* B, int64_t ldb, float beta, float* C, int64_t ldc, unsigned* status,
-                cudaStream_t st, const GemmSelfTest* selftest) {
+                cudaStream_t st, const GemmSelfTest* selftest, int max_ctas) {
     if (M <= 0 || N <= 0) return CRB_OK;
     const bool lower_only = (shape & GEMM_LOWER_ONLY) != 0;
     if ((shape & GEMM_B_LOWER) && (b_is_nk || N > K)) return CRB_ERR_BAD_ARG;
@@ -424,7 +425,9 @@ int gemm_tf32x3(bool b_is_nk, int shape, int M, int N, int K, float alpha, const
     }, &sms);
     if (rc_setup != CRB_OK) return rc_setup;
     const int total = g.m_tiles * g.n_tiles;
-    launch_chained(k_gemm_tf32x3, total < sms ? total : sms, GT_THREADS, GT_SMEM, st, map_a, map_b, g);
+    int ctas = total < sms ? total : sms;
+    if (max_ctas > 0 && ctas > max_ctas) ctas = max_ctas;     // leave SMs to whatever runs beside this product
+    launch_chained(k_gemm_tf32x3, ctas, GT_THREADS, GT_SMEM, st, map_a, map_b, g);
     CRB_LAUNCHED();
     return CRB_OK;
 }

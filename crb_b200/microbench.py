@@ -65,7 +65,11 @@ def main(argv=None):
                     help="plain stream-ordered launches instead of programmatic dependent launch")
     ap.add_argument("--fused_selection", action="store_true",
                     help="quantile selection of the block step as one cooperative kernel")
+    ap.add_argument("--lookahead", type=int, default=None, choices=(0, 1, 2),
+                    help="trailing-update look-ahead of the linear loop: 0 off, 1 by shape (default), 2 always")
     a = ap.parse_args(argv)
+    if a.lookahead is not None:
+        ops.set_trailing_lookahead(a.lookahead)
     if a.fused_selection:
         ops.set_fused_selection(True)
     if a.no_dependent_launch:
@@ -73,7 +77,7 @@ def main(argv=None):
     dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator(device=dev).manual_seed(1)
     out = {"what": a.what, "R": a.R, "C": a.C, "T": a.T, "dependent_launch": not a.no_dependent_launch,
-           "fused_selection": a.fused_selection}
+           "fused_selection": a.fused_selection, "lookahead": a.lookahead}
     launches0 = ops.launch_count()
 
     if a.what == "hessian":

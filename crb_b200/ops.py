@@ -295,6 +295,12 @@ def selftest_wait_limit(device, limit_us: int = 1000) -> int:
     return int(status[0].item())
 
 
+def set_trailing_lookahead(mode: int) -> int:
+    """Look-ahead over the grouped trailing updates of `quantize_linear`: 0 off, 1 by shape (default),
+    2 whenever there are more than two groups of blocks; returns the old mode.  Same bits either way."""
+    return int(lib().crb_set_trailing_lookahead(int(mode)))
+
+
 def set_fused_selection(enable: bool) -> bool:
     """Quantile selection of the block step as one cooperative kernel (True) or three kernels (False,
     the default); returns the old setting."""

@@ -232,6 +232,14 @@ int crb_set_dependent_launch(int enable);
  * previous setting.  No counterpart in the reference.                                        */
 int crb_set_fused_selection(int enable);
 
+/* Look-ahead over the grouped trailing updates of crb_quantize_linear: after a group of 8 blocks
+ * only the next group's columns are updated on the caller's stream; the rest of the update runs
+ * on a side stream (capped grid) beside the next group's block steps.  Bit-identical results.
+ * mode 0: off; 1 (default): for wide, short weights (C >= 8192 and R <= 8192), where the trailing
+ * products are a quarter of the loop; 2: whenever there are more than two groups.  Returns the
+ * previous mode.  No counterpart in the reference (bigptq.py:264 updates everything at once).   */
+int crb_set_trailing_lookahead(int mode);
+
 /* ---- self-test of the bounded waits -----------------------------------------------
  * Every wait inside the tensor-core kernels gives up after a time limit, raises
  * CRB_FLAG_WAIT_LIMIT in the status word, drains its copies, frees its tensor memory and

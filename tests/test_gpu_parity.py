@@ -197,6 +197,30 @@ def test_grouped_linear_loop_matches_per_block_calls(ops):
         assert torch.allclose(out["losses"], loss_b, rtol=1e-4)
 
 
+def test_trailing_lookahead_gives_the_same_bits(ops):
+    """The far part of a group's trailing update on a side stream beside the next group's block steps:
+    every element receives the same products in the same order, so nothing may change."""
+    g = torch.Generator().manual_seed(23)
+    R, C = 320, 128 * 27                    # three full groups and a partial one
+    W = torch.randn(R, C, generator=g) * 0.02
+    U = torch.triu(torch.randn(C, C, generator=g) * (0.05 / C ** 0.5), 1) + torch.diag(0.5 + torch.rand(C, generator=g))
+    Ud = U.to(DEV).contiguous()
+    outs = []
+    for mode in (0, 2, 2):
+        old = ops.set_trailing_lookahead(mode)
+        try:
+            Wd = W.to(DEV).clone()
+            o = ops.quantize_linear(Wd, Ud, "crb", want_trace=True)
+            torch.cuda.synchronize()
+        finally:
+            ops.set_trailing_lookahead(old)
+        assert ops.read_status(o["workspace"]) == 0
+        outs.append((Wd.cpu(), o["losses"].cpu(), o["trace"].cpu()))
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            assert torch.equal(a, b)
+
+
 def test_trailing_update_matches_fp32_matmul(ops):
     g = torch.Generator().manual_seed(3)
     for R, C, blk in ((96, 384, 0), (257, 512, 2), (128, 256, 1)):
