@@ -56,6 +56,7 @@ SIGNATURES = {
     "crb_set_dependent_launch": (_i, [_i]),
     "crb_set_fused_selection": (_i, [_i]),
     "crb_set_trailing_lookahead": (_i, [_i]),
+    "crb_set_factor_lookahead": (_i, [_i]),
     "crb_selftest_wait_limit": (_i, [_vp, _sz, C.c_uint, _vp, _vp]),
 }
 

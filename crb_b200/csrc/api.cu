@@ -9,6 +9,7 @@ std::atomic<unsigned long long> g_launches{0};
 std::atomic<int> g_dependent_launch{1};
 std::atomic<int> g_fused_selection{0};
 std::atomic<int> g_trailing_lookahead{1};
+std::atomic<int> g_factor_lookahead{1};
 
 // block_step.cu
 size_t block_workspace_bytes(int R);
@@ -61,6 +62,10 @@ const char* crb_status_string(int status) {
 
 int crb_set_dependent_launch(int enable) {
     return g_dependent_launch.exchange(enable ? 1 : 0);
+}
+
+int crb_set_factor_lookahead(int enable) {
+    return g_factor_lookahead.exchange(enable ? 1 : 0);
 }
 
 int crb_set_trailing_lookahead(int mode) {

@@ -157,10 +157,12 @@ __device__ __forceinline__ bool last_cta_done(unsigned* counter, unsigned total)
 // on the caller's stream can run beside work that only a later step needs.
 struct SideContext {
     cudaStream_t side = nullptr;
+    cudaStream_t side2 = nullptr;     // a second one for work that must not queue behind the first
     std::vector<cudaEvent_t> events;
 };
 SideContext* side_context(cudaStream_t main, size_t n_events);
 
+extern std::atomic<int> g_factor_lookahead;     // 0 off, 1 on (default): look-ahead over the factorisation's rank-1024 updates
 extern std::atomic<int> g_trailing_lookahead;   // 0 off, 1 by shape (default), 2 always; crb_set_trailing_lookahead()
 
 // Shape flags of gemm_tf32x3 (gemm_tc.cu).

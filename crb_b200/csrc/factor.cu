@@ -452,6 +452,9 @@ static int invert_panel_local(float* A, int C, int lo, int hi, int panel, float*
 // A second stream per caller stream, and events to fork to it and join it again.  The merges inside
 // an outer panel are chains of small, latency-bound products: they run there while the caller's
 // stream goes on with the next panels of the factorisation.
+// Grid of a far update that runs beside the next panel's chain.  Measured at C = 16384 (ms per
+// factorisation, 25.6-25.8 without look-ahead): 64 CTAs 27.8, 96 25.1, 128 24.0, 140 24.2, 148 24.3.
+constexpr int kFactorFarCtas = 128;
 static std::mutex g_side_lock;
 static std::map<std::pair<int, cudaStream_t>, SideContext> g_side;
 
@@ -465,6 +468,7 @@ SideContext* side_context(cudaStream_t main, size_t n_events) {
         int prio = 0;
         if (cudaStreamGetPriority(main, &prio) != cudaSuccess) prio = 0;
         if (cudaStreamCreateWithPriority(&ctx.side, cudaStreamNonBlocking, prio) != cudaSuccess) return nullptr;
+        if (cudaStreamCreateWithPriority(&ctx.side2, cudaStreamNonBlocking, prio) != cudaSuccess) return nullptr;
     }
     while (ctx.events.size() < n_events) {
         cudaEvent_t e;
@@ -507,7 +511,13 @@ int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
     // K = 8 * 128 afterwards, which is compute bound instead of re-reading the whole trailing
     // matrix once per diagonal block.
     const int n_panels = (nb + kOuter - 1) / kOuter;
-    SideContext* sc = nb > kOuter ? side_context(st, (size_t)n_panels + 1) : nullptr;
+    SideContext* sc = nb > kOuter ? side_context(st, 2 * (size_t)n_panels + 2) : nullptr;
+    // Look-ahead over the rank-1024 updates: the next outer panel only needs its own 1024 columns,
+    // so those are updated on the caller's stream and the rest of the trailing matrix on a second
+    // side stream with a capped grid, beside the next panel's chain of small kernels.  Every element
+    // still receives the updates panel by panel in the same order: the factor is the same bit for bit.
+    const bool ahead = sc != nullptr && n_panels > 2 && g_factor_lookahead.load(std::memory_order_relaxed) != 0;
+    int far_pending = -1;             // panel whose far update is in flight (events[n_panels + 1 + p] marks its end)
     // scratch of the merges: H is free once it has been copied (the side stream's merges and the
     // final ones never run at the same time: each uses the start of its own half)
     float* tmp_side = H;
@@ -541,10 +551,34 @@ int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
         const int rem = C - k1 * FB;
         if (rem <= 0) break;
         const float* P = A + (int64_t)k1 * FB * C + (int64_t)k0 * FB;     // rows below the panel, the panel's columns
-        int rc = gemm_tf32x3(true, GEMM_LOWER_ONLY, rem, rem, (k1 - k0) * FB, -1.0f, P, C, P, C, 1.0f,
-                             A + (int64_t)k1 * FB * (C + 1), C, status, st);
+        float* T = A + (int64_t)k1 * FB * (C + 1);                        // the trailing matrix
+        const int kk = (k1 - k0) * FB;
+        if (!ahead) {
+            const int rc = gemm_tf32x3(true, GEMM_LOWER_ONLY, rem, rem, kk, -1.0f, P, C, P, C, 1.0f, T, C, status, st);
+            if (rc != CRB_OK) return rc;
+            continue;
+        }
+        const int p = k0 / kOuter;
+        // the previous panel's far update wrote the columns this one is about to update
+        if (far_pending >= 0 && cudaStreamWaitEvent(st, sc->events[n_panels + 1 + far_pending], 0) != cudaSuccess)
+            return CRB_ERR_LAUNCH;
+        far_pending = -1;
+        const int near = rem < kOuter * FB ? rem : kOuter * FB;
+        int rc = gemm_tf32x3(true, GEMM_LOWER_ONLY, rem, near, kk, -1.0f, P, C, P, C, 1.0f, T, C, status, st);
         if (rc != CRB_OK) return rc;
+        const int far = rem - near;
+        if (far <= 0) continue;
+        // the panel's columns are final (events[p], recorded above for the panel-local inverse)
+        if (cudaStreamWaitEvent(sc->side2, sc->events[p], 0) != cudaSuccess) return CRB_ERR_LAUNCH;
+        const float* Pf = P + (int64_t)near * C;
+        rc = gemm_tf32x3(true, GEMM_LOWER_ONLY, far, far, kk, -1.0f, Pf, C, Pf, C, 1.0f, T + (int64_t)near * (C + 1), C,
+                         status, sc->side2, nullptr, kFactorFarCtas);
+        if (rc != CRB_OK) return rc;
+        if (cudaEventRecord(sc->events[n_panels + 1 + p], sc->side2) != cudaSuccess) return CRB_ERR_LAUNCH;
+        far_pending = p;
     }
+    if (far_pending >= 0 && cudaStreamWaitEvent(st, sc->events[n_panels + 1 + far_pending], 0) != cudaSuccess)
+        return CRB_ERR_LAUNCH;
     if (sc) {
         if (cudaEventRecord(sc->events[n_panels], sc->side) != cudaSuccess ||
             cudaStreamWaitEvent(st, sc->events[n_panels], 0) != cudaSuccess)

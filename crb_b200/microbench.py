@@ -67,7 +67,11 @@ def main(argv=None):
                     help="quantile selection of the block step as one cooperative kernel")
     ap.add_argument("--lookahead", type=int, default=None, choices=(0, 1, 2),
                     help="trailing-update look-ahead of the linear loop: 0 off, 1 by shape (default), 2 always")
+    ap.add_argument("--no_factor_lookahead", action="store_true",
+                    help="factorisation: the whole rank-1024 update on the caller's stream")
     a = ap.parse_args(argv)
+    if a.no_factor_lookahead:
+        ops.set_factor_lookahead(False)
     if a.lookahead is not None:
         ops.set_trailing_lookahead(a.lookahead)
     if a.fused_selection:

@@ -295,6 +295,11 @@ def selftest_wait_limit(device, limit_us: int = 1000) -> int:
     return int(status[0].item())
 
 
+def set_factor_lookahead(enable: bool) -> bool:
+    """Look-ahead over the rank-1024 updates of the factorisation on or off; returns the old setting."""
+    return bool(lib().crb_set_factor_lookahead(int(bool(enable))))
+
+
 def set_trailing_lookahead(mode: int) -> int:
     """Look-ahead over the grouped trailing updates of `quantize_linear`: 0 off, 1 by shape (default),
     2 whenever there are more than two groups of blocks; returns the old mode.  Same bits either way."""

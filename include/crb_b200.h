@@ -240,6 +240,12 @@ int crb_set_fused_selection(int enable);
  * previous mode.  No counterpart in the reference (bigptq.py:264 updates everything at once).   */
 int crb_set_trailing_lookahead(int mode);
 
+/* The same look-ahead inside crb_hinv_upper_factor: after a 1024-column outer panel only the next
+ * panel's columns of the trailing matrix are updated on the caller's stream, the rest on a side
+ * stream beside the next panel's chain of diagonal blocks.  Bit-identical factor.  Default on
+ * (C > 2048); returns the previous setting.                                                    */
+int crb_set_factor_lookahead(int enable);
+
 /* ---- self-test of the bounded waits -----------------------------------------------
  * Every wait inside the tensor-core kernels gives up after a time limit, raises
  * CRB_FLAG_WAIT_LIMIT in the status word, drains its copies, frees its tensor memory and

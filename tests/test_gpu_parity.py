@@ -236,6 +236,27 @@ def test_trailing_update_matches_fp32_matmul(ops):
         assert torch.equal(Wd.cpu()[:, :ed], W[:, :ed])
 
 
+def test_factor_lookahead_gives_the_same_bits(ops):
+    """The rank-1024 updates split into the next panel's columns (caller's stream) and the rest (side
+    stream) apply the same products to every element in the same order: U must not change by a bit."""
+    C = 4096 + 1024                                          # five outer panels
+    g = torch.Generator().manual_seed(11)
+    X = torch.randn(2 * C, C, generator=g)
+    H0 = ((X.t() @ X) / C).to(DEV)
+    outs = []
+    for enable in (False, True, True):
+        old = ops.set_factor_lookahead(enable)
+        try:
+            H = H0.clone()
+            ops.hinv_upper_factor(H, None, 0.01, restore=lambda h: h.copy_(H0))
+            torch.cuda.synchronize()
+        finally:
+            ops.set_factor_lookahead(old)
+        outs.append(H.cpu())
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert torch.isfinite(outs[0]).all() and float(outs[0].diagonal().min()) > 0
+
+
 @pytest.mark.parametrize("C", (128, 384, 1024, 4096))      # 4096: four outer panels, two levels of merges across them
 def test_factor_matches_reference_chain(ops, C):
     g = torch.Generator().manual_seed(C)
