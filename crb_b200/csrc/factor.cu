@@ -412,49 +412,60 @@ size_t factor_workspace_bytes(int C) {
     return align256(sizeof(float) * (size_t)C * C) + 256 + align256((size_t)C);
 }
 
-// A range of diagonal blocks that lies inside one outer panel of the factorisation.
-static bool within_one_panel(int lo, int hi) { return lo / kOuter == (hi - 1) / kOuter; }
-
-// Inverse of the lower-triangular factor on the diagonal blocks [lo, hi), in place, by recursive
-// merges.  `skip_panel_local`: sub-ranges inside one outer panel are already inverted (the side
-// stream did them while the factorisation went on) and are left alone.
-static int invert_range(float* A, int C, int lo, int hi, float* tmp, unsigned* status, cudaStream_t st,
-                        bool skip_panel_local) {
-    if (hi - lo <= 1) return CRB_OK;
-    if (skip_panel_local && within_one_panel(lo, hi)) return CRB_OK;
-    const int mid = lo + (hi - lo) / 2;
-    int rc = invert_range(A, C, lo, mid, tmp, status, st, skip_panel_local);
-    if (rc != CRB_OK) return rc;
-    rc = invert_range(A, C, mid, hi, tmp, status, st, skip_panel_local);
-    if (rc != CRB_OK) return rc;
+// One merge of the recursion: with both halves of [lo, hi) inverted, the block below the diagonal
+// becomes  -D^-1 B A^-1.  Both inverses are lower triangular: their zero halves are not multiplied.
+static int merge_halves(float* A, int C, int lo, int mid, int hi, float* tmp, unsigned* status, cudaStream_t st,
+                        int max_ctas) {
     const int s1 = (mid - lo) * FB, s2 = (hi - mid) * FB;
     float* B = A + (int64_t)mid * FB * C + (int64_t)lo * FB;
     const float* Ainv = A + (int64_t)lo * FB * (C + 1);
     const float* Dinv = A + (int64_t)mid * FB * (C + 1);
-    // both inverses are lower triangular: their zero halves are not multiplied
-    rc = gemm_tf32x3(false, GEMM_B_LOWER, s2, s1, s1, 1.0f, B, C, Ainv, C, 0.0f, tmp, s1, status, st);      // T = B A^-1
+    int rc = gemm_tf32x3(false, GEMM_B_LOWER, s2, s1, s1, 1.0f, B, C, Ainv, C, 0.0f, tmp, s1, status, st, nullptr,
+                         max_ctas);                                                                         // T = B A^-1
     if (rc != CRB_OK) return rc;
-    return gemm_tf32x3(false, GEMM_A_LOWER, s2, s1, s2, -1.0f, Dinv, C, tmp, s1, 0.0f, B, C, status, st);   // B = -D^-1 T
+    return gemm_tf32x3(false, GEMM_A_LOWER, s2, s1, s2, -1.0f, Dinv, C, tmp, s1, 0.0f, B, C, status, st, nullptr,
+                       max_ctas);                                                                           // B = -D^-1 T
 }
 
-// The merges of the recursion tree over [lo, hi) that lie inside outer panel `panel`: the largest
-// such sub-ranges are inverted completely (their inputs are final once that panel is factored).
-static int invert_panel_local(float* A, int C, int lo, int hi, int panel, float* tmp, unsigned* status,
-                              cudaStream_t st) {
-    if (hi - lo <= 1 || panel < lo / kOuter || panel > (hi - 1) / kOuter) return CRB_OK;
-    if (within_one_panel(lo, hi)) return invert_range(A, C, lo, hi, tmp, status, st, false);
+// Inverse of the lower-triangular factor on the diagonal blocks [lo, hi), in place, by recursive
+// merges (the single-panel case: everything on the caller's stream after the factorisation).
+static int invert_range(float* A, int C, int lo, int hi, float* tmp, unsigned* status, cudaStream_t st) {
+    if (hi - lo <= 1) return CRB_OK;
     const int mid = lo + (hi - lo) / 2;
-    const int rc = invert_panel_local(A, C, lo, mid, panel, tmp, status, st);
+    int rc = invert_range(A, C, lo, mid, tmp, status, st);
     if (rc != CRB_OK) return rc;
-    return invert_panel_local(A, C, mid, hi, panel, tmp, status, st);
+    rc = invert_range(A, C, mid, hi, tmp, status, st);
+    if (rc != CRB_OK) return rc;
+    return merge_halves(A, C, lo, mid, hi, tmp, status, st, 0);
 }
 
-// A second stream per caller stream, and events to fork to it and join it again.  The merges inside
-// an outer panel are chains of small, latency-bound products: they run there while the caller's
-// stream goes on with the next panels of the factorisation.
+// The merges of the same recursion tree that become possible when outer panel `panel` has been
+// factored: every node whose last diagonal block lies in that panel (nodes that ended in an earlier
+// panel were merged by an earlier call).  Their inputs are final: the factor's columns of a panel
+// do not change after the panel's chain, and the block a merge overwrites is read by no update of
+// the factorisation that can still be in flight (an update of panel q reads the rows below panel
+// q + 1 from the side stream only while panel q + 1 is being factored).  Called panel by panel on the
+// side stream, this leaves only the merges that need the last panel for the end.
+static int invert_completed(float* A, int C, int lo, int hi, int panel, float* tmp, unsigned* status,
+                            cudaStream_t st, int max_ctas) {
+    if (hi - lo <= 1) return CRB_OK;
+    const int last = (hi - 1) / kOuter;
+    if (panel < lo / kOuter || panel > last) return CRB_OK;
+    const int mid = lo + (hi - lo) / 2;
+    int rc = invert_completed(A, C, lo, mid, panel, tmp, status, st, max_ctas);
+    if (rc != CRB_OK) return rc;
+    rc = invert_completed(A, C, mid, hi, panel, tmp, status, st, max_ctas);
+    if (rc != CRB_OK) return rc;
+    return last == panel ? merge_halves(A, C, lo, mid, hi, tmp, status, st, max_ctas) : (int)CRB_OK;
+}
+
+// Grid of the inverse merges that run beside the factorisation of later panels (the last panel's
+// merges, with nothing left to run beside, take the whole GPU).
+constexpr int kMergeCtasBeside = 64;
 // Grid of a far update that runs beside the next panel's chain.  Measured at C = 16384 (ms per
 // factorisation, 25.6-25.8 without look-ahead): 64 CTAs 27.8, 96 25.1, 128 24.0, 140 24.2, 148 24.3.
 constexpr int kFactorFarCtas = 128;
+// The side streams of a caller stream, and events to fork to them and join them again (common.cuh).
 static std::mutex g_side_lock;
 static std::map<std::pair<int, cudaStream_t>, SideContext> g_side;
 
@@ -518,10 +529,8 @@ int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
     // still receives the updates panel by panel in the same order: the factor is the same bit for bit.
     const bool ahead = sc != nullptr && n_panels > 2 && g_factor_lookahead.load(std::memory_order_relaxed) != 0;
     int far_pending = -1;             // panel whose far update is in flight (events[n_panels + 1 + p] marks its end)
-    // scratch of the merges: H is free once it has been copied (the side stream's merges and the
-    // final ones never run at the same time: each uses the start of its own half)
+    // scratch of the merges (at most C^2 / 4 floats, one merge at a time): H is free once it has been copied
     float* tmp_side = H;
-    float* tmp_main = H + (size_t)C * C / 2;
     for (int k0 = 0; k0 < nb; k0 += kOuter) {
         const int k1 = k0 + kOuter < nb ? k0 + kOuter : nb;
         for (int k = k0; k < k1; ++k) {
@@ -545,7 +554,8 @@ int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
             if (cudaEventRecord(sc->events[p], st) != cudaSuccess ||
                 cudaStreamWaitEvent(sc->side, sc->events[p], 0) != cudaSuccess)
                 return CRB_ERR_LAUNCH;
-            const int rc = invert_panel_local(A, C, 0, nb, p, tmp_side, status, sc->side);
+            const int rc = invert_completed(A, C, 0, nb, p, tmp_side, status, sc->side,
+                                            k1 < nb ? kMergeCtasBeside : 0);
             if (rc != CRB_OK) return rc;
         }
         const int rem = C - k1 * FB;
@@ -584,8 +594,10 @@ int factor_launch(float* H, int C, float* W, int R, int64_t ldw, float percdamp,
             cudaStreamWaitEvent(st, sc->events[n_panels], 0) != cudaSuccess)
             return CRB_ERR_LAUNCH;
     }
-    int rc = invert_range(A, C, 0, nb, tmp_main, status, st, sc != nullptr);   // the merges across panels
-    if (rc != CRB_OK) return rc;
+    if (!sc) {
+        const int rc = invert_range(A, C, 0, nb, tmp_side, status, st);         // a single outer panel
+        if (rc != CRB_OK) return rc;
+    }
     k_reverse_upper<<<dim3((C + 255) / 256, C), 256, 0, st>>>(A, C, H);
     CRB_LAUNCHED();
     return CRB_OK;

@@ -487,6 +487,10 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
     handles = [subset[name].register_forward_pre_hook(make_hook(name)) for name in gptq]
     n_local = inps.shape[0]
     fb = max(1, int(args.forward_batch))
+    if n_local > fb:
+        # same number of forwards, evenly filled (18 sequences: 6 + 6 + 6 instead of 8 + 8 + 2)
+        n_batches = (n_local + fb - 1) // fb
+        fb = (n_local + n_batches - 1) // n_batches
     with timer.span("forward_hessian"):
         feed = _Feeder(inps, fb, dev, keep_gib=float(getattr(args, "act_stage_gib", 16.0)))
         for b in range(len(feed)):
