@@ -461,7 +461,7 @@ static int invert_completed(float* A, int C, int lo, int hi, int panel, float* t
 
 // Grid of the inverse merges that run beside the factorisation of later panels (the last panel's
 // merges, with nothing left to run beside, take the whole GPU).
-constexpr int kMergeCtasBeside = 64;
+constexpr int kMergeCtasBeside = 64;     // measured at C = 16384: 32 CTAs 24.8 ms, 64 23.2, 96 23.4, 128 23.1
 // Grid of a far update that runs beside the next panel's chain.  Measured at C = 16384 (ms per
 // factorisation, 25.6-25.8 without look-ahead): 64 CTAs 27.8, 96 25.1, 128 24.0, 140 24.2, 148 24.3.
 constexpr int kFactorFarCtas = 128;
