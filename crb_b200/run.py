@@ -635,16 +635,18 @@ def quantize_layer(layer: nn.Module, index: int, inps: torch.Tensor, outs: torch
 
             handles = [subset[name].register_forward_pre_hook(gate(name)) for name in gptq]
             lanes = _lane_streams(dev, min(len(feed), max(1, int(getattr(args, "reprop_lanes", 16)))))
-            for b in range(len(feed)):
-                lane = lanes[b % len(lanes)]
-                lane.wait_event(start)
-                with torch.cuda.stream(lane):
-                    x = feed.batch(b, lane)
-                    y = _layer_out(layer(x, **_replay_kwargs(layer_kwargs, x.shape[0])))
-                    feed.done(b, lane)
-                    _store_outputs(outs, b * fb, y.reshape(x.shape), dev)
-            for h in handles:
-                h.remove()
+            try:
+                for b in range(len(feed)):
+                    lane = lanes[b % len(lanes)]
+                    lane.wait_event(start)
+                    with torch.cuda.stream(lane):
+                        x = feed.batch(b, lane)
+                        y = _layer_out(layer(x, **_replay_kwargs(layer_kwargs, x.shape[0])))
+                        feed.done(b, lane)
+                        _store_outputs(outs, b * fb, y.reshape(x.shape), dev)
+            finally:
+                for h in handles:
+                    h.remove()
         # the phase ends on the caller's stream when the last weight is in place
         for name in gptq:
             main.wait_event(ready[name])
