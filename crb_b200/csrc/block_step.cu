@@ -981,24 +981,20 @@ k_split_search_sorted(const float* __restrict__ sv, const unsigned char* __restr
 constexpr int kSalRows = 16;
 constexpr int kTopPitch = kSalLimit + 1;
 constexpr int kSalSmem = kSalRows * kRowPitch * (int)(sizeof(float) + 2 * sizeof(double)) +
-                         kSalRows * kTopPitch * (int)(2 * sizeof(float) + 2 * sizeof(double)) +
+                         kSalRows * kTopPitch * (int)(2 * sizeof(float) + 3 * sizeof(double)) +
                          kSalCand * kSalRows * (int)sizeof(double);
 
-__device__ __forceinline__ int lower_bound_d(const float* v, int n, double t) {
-    int lo = 0, len = n;                         // first index with v[idx] >= t
-    while (len > 0) {
-        const int half = len >> 1;
-        if ((double)v[lo + half] < t) { lo += half + 1; len -= half + 1; } else { len = half; }
-    }
-    return lo;
-}
+// Smallest float that is not below t.  For a float x:  x < t  <=>  x < float_not_below(t), and
+// x >= t  <=>  x >= float_not_below(t): comparisons of float data with a double threshold can
+// be made in float without changing a single outcome (and without a conversion per element).
+__device__ __forceinline__ float float_not_below(double t) { return __double2float_ru(t); }
 
 // The hole passes and the direct float32 evaluation of the i top values walk the same list: they
 // are fused pairwise (four passes over tv[0..i) in all; the plain sums come from per-row running
 // sums in score order).
 __device__ __forceinline__ double salient_candidate_err(const float* v, const double* P1, const double* P2,
-                                                        const float* tv, const double* hp1, const double* hp2,
-                                                        const float* fs, int i) {
+                                                        const float* tv, const double* tvd, const double* hp1,
+                                                        const double* hp2, const float* fs, int i) {
     const int n = kBlock - i;
     const float fi = (float)i;
     // sums of the i holes (complement) and of the salient values: running sums in score order,
@@ -1016,8 +1012,7 @@ __device__ __forceinline__ double salient_candidate_err(const float* v, const do
 #pragma unroll 4
     for (int h = 0; h < i; ++h) {
         const float t = tv[h];
-        const double td = (double)t;
-        if (t < mu1) { --n1; a1 -= td; b1 = fma(-td, td, b1); }
+        if (t < mu1) { const double td = tvd[h]; --n1; a1 -= td; b1 = fma(-td, td, b1); }
         a += fabsf(t - mu);
     }
     const double c1 = (double)n1;
@@ -1030,10 +1025,11 @@ __device__ __forceinline__ double salient_candidate_err(const float* v, const do
     const float mu2 = __fdiv_rn((float)sr, (float)n);
     const double tlo = (double)ylo + (double)mu2, thi = (double)yhi + (double)mu2;
     const double t1 = fmin(tlo, dmu1), t2 = fmax(thi, dmu1);
-    cf = lower_bound_d(v, kBlock, t1);
+    const float f1 = float_not_below(t1), f2 = float_not_below(t2);
+    cf = lower_bound_f(v, 0, kBlock, f1);
     int n2 = cf;
     double a2 = P1[cf];
-    cf = lower_bound_d(v, kBlock, t2);
+    cf = lower_bound_f(v, 0, kBlock, f2);
     int n3 = cf;
     double a3 = P1[cf];
     // pass 2: holes below the second-pass thresholds; residual mean of the salient group
@@ -1041,9 +1037,8 @@ __device__ __forceinline__ double salient_candidate_err(const float* v, const do
 #pragma unroll 4
     for (int h = 0; h < i; ++h) {
         const float x = tv[h];
-        const double t = (double)x;
-        if (t < t1) { --n2; a2 -= t; }
-        if (t < t2) { --n3; a3 -= t; }
+        if (x < f1) { --n2; a2 -= tvd[h]; }
+        if (x < f2) { --n3; a3 -= tvd[h]; }
         s += x - __fadd_rn(al * sgnf(x - mu), mu);
     }
     const double c2 = (double)n2;
@@ -1112,6 +1107,7 @@ k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __res
     float* s_fs = s_tv + kSalRows * kTopPitch;                               // [rows][kTopPitch] float32 running sum
     double* s_hp1 = reinterpret_cast<double*>(s_fs + kSalRows * kTopPitch);  // [rows][kTopPitch] running sum
     double* s_hp2 = s_hp1 + kSalRows * kTopPitch;                            // [rows][kTopPitch] running sum of squares
+    double* s_tvd = s_hp2 + kSalRows * kTopPitch;                            // [rows][kTopPitch] the top values as doubles
     __shared__ unsigned char s_rank[kBlock];
     __shared__ double s_tot[kSalCand];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -1139,7 +1135,10 @@ k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __res
                 vrow[4 * lane + q] = x[q];
                 l1 += (double)x[q]; l2 += (double)x[q] * (double)x[q];
                 const int rk = s_rank[cc[q]];
-                if (row < R && rk < kSalLimit) s_tv[r * kTopPitch + rk] = x[q];
+                if (row < R && rk < kSalLimit) {
+                    s_tv[r * kTopPitch + rk] = x[q];
+                    s_tvd[r * kTopPitch + rk] = (double)x[q];
+                }
             }
             double i1 = l1, i2 = l2;
 #pragma unroll
@@ -1190,7 +1189,7 @@ k_salient_search_sorted(const float* __restrict__ sv, const unsigned char* __res
                     if (i == 0) break;
                     s_acc[(i - 1) * kSalRows + r] += salient_candidate_err(
                         s_v + r * kRowPitch, s_P1 + r * kRowPitch, s_P2 + r * kRowPitch, s_tv + r * kTopPitch,
-                        s_hp1 + r * kTopPitch, s_hp2 + r * kTopPitch, s_fs + r * kTopPitch, i);
+                        s_tvd + r * kTopPitch, s_hp1 + r * kTopPitch, s_hp2 + r * kTopPitch, s_fs + r * kTopPitch, i);
                 }
             }
         }
