@@ -597,7 +597,7 @@ __device__ void select_in_bin(int R, int isal, int slot, const BlockWs& ws) {
     const int t0 = s_t0, t1 = s_t1;
     const unsigned bin1 = ws.tgt_bin1[t0];
     const unsigned zeros = bin1 == 0u ? (unsigned)R * (unsigned)isal : 0u;   // salient zeros: counted, not listed
-    for (unsigned k = tid; k < n; k += nthreads) atomicAdd(&s_hi[list[k] >> 8], 1u);
+    for (unsigned k = tid; k < n; k += nthreads) atomicAdd(&s_hi[__ldcg(list + k) >> 8], 1u);
     __syncthreads();
     const unsigned hi_cnt = owner ? s_hi[tid] : 0u;
     const unsigned hi_exc = scan_cta(hi_cnt);
@@ -616,7 +616,7 @@ __device__ void select_in_bin(int R, int isal, int slot, const BlockWs& ws) {
             if (owner) s_lo[tid] = 0u;
             __syncthreads();
             for (unsigned k = tid; k < n; k += nthreads) {
-                const unsigned e = list[k];
+                const unsigned e = __ldcg(list + k);
                 if ((e >> 8) == hi) atomicAdd(&s_lo[e & 255u], 1u);
             }
             __syncthreads();
